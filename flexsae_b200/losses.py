@@ -1,0 +1,190 @@
+"""The two fused decoder losses as ``torch.autograd.Function``s over the CUDA library.
+
+Public signature and autograd behaviour are those of ``flex_sae.triton_topk_sae_loss``
+(torch-ext/flex_sae/topk_kernels.py:213-223) and ``flex_sae.triton_hierarchical_sae_loss``
+(torch-ext/flex_sae/hierarchical_kernels.py:302-309):
+
+    loss = f(indices[B,K] int64, weight[F,D], vals[B,K], bias[D], target[B,D])   # 0-dim float32
+
+differentiable with respect to weight, vals and bias (gradients arrive in each parameter's own
+dtype), ``None`` for indices and target (hierarchical_kernels.py:299), any upstream scalar.
+Differences a caller can see: the loss value is run-to-run reproducible (the reference sums it
+with float atomics, hierarchical_kernels.py:80-85), inputs are validated, and the upstream
+gradient is applied inside the kernels instead of by three ``mul_`` passes
+(hierarchical_kernels.py:294-297).
+"""
+from __future__ import annotations
+
+import threading
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _native as nv
+
+_tls = threading.local()
+
+
+class config:
+    """Process-wide switches of the fused losses."""
+
+    #: "atomic" (vectorised fp32 reductions resolved in L2) or "deterministic" (sorted,
+    #: fixed-order sums: bitwise reproducible dweight)
+    dweight_mode: str = "atomic"
+    #: check the device status word after every forward (forces a host sync; for debugging)
+    check_indices: bool = False
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _prep(t: torch.Tensor) -> torch.Tensor:
+    """Dense row-major, 16-byte aligned view of ``t`` (copies only when it has to)."""
+    if not t.is_contiguous():
+        t = t.contiguous()
+    if t.data_ptr() % 16 != 0:
+        t = t.clone(memory_format=torch.contiguous_format)
+    return t
+
+
+def _validate(indices, weight, vals, bias, target) -> Tuple[int, int, int, int]:
+    if indices.dim() != 2 or weight.dim() != 2 or vals.dim() != 2 or bias.dim() != 1 or target.dim() != 2:
+        raise ValueError("expected indices[B,K], weight[F,D], vals[B,K], bias[D], target[B,D]")
+    B, K = indices.shape
+    F, D = weight.shape
+    if tuple(vals.shape) != (B, K) or tuple(bias.shape) != (D,) or tuple(target.shape) != (B, D):
+        raise ValueError(f"shape mismatch: indices {tuple(indices.shape)}, weight {tuple(weight.shape)}, "
+                         f"vals {tuple(vals.shape)}, bias {tuple(bias.shape)}, target {tuple(target.shape)}")
+    if indices.dtype != torch.int64:
+        raise TypeError(f"indices must be int64, got {indices.dtype}")
+    for name, t in (("weight", weight), ("vals", vals), ("bias", bias), ("target", target)):
+        if t.dtype not in nv.DTYPE_CODES:
+            raise TypeError(f"{name} must be float32, bfloat16 or float16, got {t.dtype}")
+    dev = weight.device
+    if dev.type != "cuda":
+        raise RuntimeError("the fused decoder losses run on CUDA tensors only "
+                           "(use topk_sae_loss / hierarchical_sae_loss for the eager torch path)")
+    for name, t in (("indices", indices), ("vals", vals), ("bias", bias), ("target", target)):
+        if t.device != dev:
+            raise RuntimeError(f"{name} is on {t.device}, weight is on {dev}")
+    return B, K, F, D
+
+
+def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """A per-device scratch buffer that is kept between calls (so that the fp32 gradient slab
+    keeps its L2 lines warm) and only ever grows.  All work of one device is assumed to be
+    enqueued on one stream at a time, like the rest of a training step."""
+    cache: Dict[int, torch.Tensor] = _tls.__dict__.setdefault("ws", {})
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    buf = cache.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)
+        cache[key] = buf
+    return buf
+
+
+def _status_word(dev: torch.device) -> torch.Tensor:
+    cache: Dict[int, torch.Tensor] = _tls.__dict__.setdefault("status", {})
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in cache:
+        cache[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return cache[key]
+
+
+def check_status(device=None) -> None:
+    """Raises if any fused-loss kernel on ``device`` met an out-of-range index since the last
+    check (such an index is read as row 0 instead of being dereferenced)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = _status_word(dev)
+    bits = int(word.item())
+    if bits:
+        word.zero_()
+        if bits & nv.STATUS_BAD_INDEX:
+            raise IndexError("flexsae_b200: indices outside [0, F) were passed to a fused loss")
+
+
+def fused_forward(kind: int, indices, weight, vals, bias, target, inv_norm: float = 0.0):
+    """Runs the forward kernels; returns (loss 0-dim float32, resid [B,D] float32, prepared inputs)."""
+    B, K, F, D = _validate(indices, weight, vals, bias, target)
+    lib = nv.load()
+    indices, weight, vals, bias, target = (_prep(t.detach()) for t in (indices, weight, vals, bias, target))
+    dev = weight.device
+    wdt = nv.DTYPE_CODES[weight.dtype]
+    with torch.cuda.device(dev):
+        need = lib.flexsae_fwd_workspace_bytes(kind, B, K, F, D, wdt)
+        if need == 0:
+            raise nv.FlexSaeNativeError("flexsae_loss_fwd: " + lib.flexsae_last_error().decode())
+        ws = _workspace(dev, need)
+        loss = torch.empty((), dtype=torch.float32, device=dev)
+        resid = torch.empty((B, D), dtype=torch.float32, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = lib.flexsae_loss_fwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(bias), _ptr(target),
+                                  _ptr(loss), _ptr(resid), _ptr(ws), ws.numel(), B, K, F, D, wdt,
+                                  nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias.dtype],
+                                  nv.DTYPE_CODES[target.dtype], float(inv_norm), _ptr(_status_word(dev)), stream)
+        nv.check(rc, "flexsae_loss_fwd")
+    if config.check_indices:
+        check_status(dev)
+    return loss, resid, (indices, weight, vals)
+
+
+def fused_backward(kind: int, indices, weight, vals, resid, grad_out, bias_dtype, inv_norm: float = 0.0,
+                   dweight_mode: Optional[str] = None):
+    """Runs the backward kernels; returns (dweight, dvals, dbias) in the parameters' dtypes."""
+    B, K = indices.shape
+    F, D = weight.shape
+    lib = nv.load()
+    dev = weight.device
+    wdt = nv.DTYPE_CODES[weight.dtype]
+    mode = {"atomic": nv.DW_ATOMIC, "deterministic": nv.DW_DETERMINISTIC}[dweight_mode or config.dweight_mode]
+    with torch.cuda.device(dev):
+        go = grad_out.detach().to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+        need = lib.flexsae_bwd_workspace_bytes(kind, B, K, F, D, wdt, mode)
+        if need == 0:
+            raise nv.FlexSaeNativeError("flexsae_loss_bwd: " + lib.flexsae_last_error().decode())
+        ws = _workspace(dev, need)
+        dweight = torch.empty((F, D), dtype=weight.dtype, device=dev)
+        dvals = torch.empty((B, K), dtype=vals.dtype, device=dev)
+        dbias = torch.empty((D,), dtype=bias_dtype, device=dev)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = lib.flexsae_loss_bwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(resid), _ptr(go),
+                                  _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(), B, K, F, D, wdt,
+                                  nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype], float(inv_norm), mode,
+                                  _ptr(_status_word(dev)), stream)
+        nv.check(rc, "flexsae_loss_bwd")
+    return dweight, dvals, dbias
+
+
+class _FusedDecoderLoss(torch.autograd.Function):
+    """Shared autograd glue; ``kind`` selects TopK or Hierarchical.  Plays the role of
+    HierarchicalSAELossFunction (hierarchical_kernels.py:273-299) and of xFormersEmbeddingBag
+    plus the eager tail around it (topk_kernels.py:188-223)."""
+
+    @staticmethod
+    @torch.amp.custom_fwd(device_type="cuda")
+    def forward(ctx, kind, inv_norm, indices, weight, vals, bias, target):
+        loss, resid, (idx_c, w_c, v_c) = fused_forward(kind, indices, weight, vals, bias, target, inv_norm)
+        ctx.kind, ctx.inv_norm, ctx.bias_dtype = kind, inv_norm, bias.dtype
+        ctx.save_for_backward(idx_c, w_c, v_c, resid)
+        return loss
+
+    @staticmethod
+    @torch.amp.custom_bwd(device_type="cuda")
+    def backward(ctx, grad):
+        idx_c, w_c, v_c, resid = ctx.saved_tensors
+        dweight, dvals, dbias = fused_backward(ctx.kind, idx_c, w_c, v_c, resid, grad, ctx.bias_dtype, ctx.inv_norm)
+        return None, None, None, dweight, dvals, dbias, None
+
+
+def triton_topk_sae_loss(indices: torch.Tensor, weight: torch.Tensor, vals: torch.Tensor, bias: torch.Tensor,
+                         target: torch.Tensor) -> torch.Tensor:
+    """Fused TopK decoder loss; drop-in for ``flex_sae.triton_topk_sae_loss`` (the name is kept
+    for callers; no Triton is involved)."""
+    return _FusedDecoderLoss.apply(nv.TOPK, 0.0, indices, weight, vals, bias, target)
+
+
+def triton_hierarchical_sae_loss(indices: torch.Tensor, weight: torch.Tensor, vals: torch.Tensor,
+                                 bias: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
+    """Fused Hierarchical-TopK decoder loss; drop-in for ``flex_sae.triton_hierarchical_sae_loss``."""
+    return _FusedDecoderLoss.apply(nv.HIER, 0.0, indices, weight, vals, bias, target)

@@ -1,0 +1,120 @@
+/*
+ * flexsae_b200 -- C ABI of the B200 (sm_100a) decoder-loss library.
+ *
+ * The library implements the two fused sparse-autoencoder decoder losses of flex_sae,
+ *
+ *   TopK          loss = mean_{b,d}   (bias + sum_k     vals[b,k] * weight[indices[b,k]] - target[b])^2
+ *   Hierarchical  loss = mean_{b,k,d} (bias + sum_{i<=k} vals[b,i] * weight[indices[b,i]] - target[b])^2
+ *
+ * and their gradients with respect to weight, vals and bias.  Every pointer below is a DEVICE
+ * pointer unless its name ends in _host; all tensors are dense row-major.  No entry point
+ * allocates or frees device memory, synchronises the stream or touches the default stream:
+ * work is enqueued on the stream handle passed in (a cudaStream_t cast to void*; NULL is the
+ * legacy default stream).  Scratch memory comes from the caller, sized by the *_workspace_bytes
+ * functions.  Return value: 0 on success, a negative FLEXSAE_E* code for rejected arguments,
+ * or the positive cudaError_t of a failed launch; flexsae_last_error() describes the last
+ * failure of the calling thread.
+ *
+ * Each entry point names the part of the reference it stands in for
+ * (paths are relative to the reference's repository root).
+ */
+#ifndef FLEXSAE_B200_H
+#define FLEXSAE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of weight / vals / bias / target */
+#define FLEXSAE_F32 0
+#define FLEXSAE_BF16 1
+#define FLEXSAE_F16 2
+
+/* loss kinds */
+#define FLEXSAE_TOPK 0
+#define FLEXSAE_HIER 1
+
+/* how dweight is accumulated */
+#define FLEXSAE_DW_ATOMIC 0        /* vectorised red.global.add.f32 into an L2-resident slab */
+#define FLEXSAE_DW_DETERMINISTIC 1 /* stable sort by decoder row + fixed-order segmented sums */
+
+/* error codes */
+#define FLEXSAE_EINVAL (-1)      /* bad shape, dtype code, null pointer or misaligned pointer */
+#define FLEXSAE_EWORKSPACE (-2)  /* workspace smaller than *_workspace_bytes() */
+#define FLEXSAE_EUNSUPPORTED (-3)/* shape outside what the kernels handle */
+
+/* bits of the optional device status word */
+#define FLEXSAE_STATUS_BAD_INDEX 1 /* an index outside [0,F) was met; it was read as row 0 */
+
+/* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
+int flexsae_version(void);
+
+/* Text of the last error on this thread ("" if none). No reference counterpart: the reference
+ * validates nothing and fails inside Triton. */
+const char* flexsae_last_error(void);
+
+/* Tuning knobs, process-wide: "lanes_fwd", "lanes_bwd" (8, 16, 32 lanes share one batch row;
+ * 0 = choose so that one column slab of the decoder and of the fp32 gradient slab stay in L2),
+ * "l2_budget_mb", "slab_pieces" (column pieces accumulated per backward launch).
+ * Stands in for the literal tile constants at the reference's launch sites
+ * (torch-ext/flex_sae/hierarchical_kernels.py:220-224,263-267; topk_kernels.py:64-66,181-183).
+ * Returns 0, or FLEXSAE_EINVAL for an unknown name or value. */
+int flexsae_set_option(const char* name, int64_t value);
+int64_t flexsae_get_option(const char* name);
+
+/* Scratch bytes the forward / backward need for this shape (0 on invalid arguments).
+ * Stands in for the torch.zeros / torch.empty temporaries the reference's launchers allocate
+ * (hierarchical_kernels.py:200-201,241-243; topk_kernels.py:146-166). */
+size_t flexsae_fwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, int64_t D,
+                                   int weight_dtype);
+size_t flexsae_bwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, int64_t D,
+                                   int weight_dtype, int dw_mode);
+
+/*
+ * Forward of either loss.
+ *   indices [B,K] int64, weight [F,D], vals [B,K], bias [D], target [B,D]
+ *   loss_out   one float32: the loss, already divided by the normaliser
+ *   resid_out  [B,D] float32: final reconstruction minus target, the state the backward starts from
+ *   inv_norm   1/(B*D) (TopK) or 1/(B*K*D) (Hierarchical); pass the GLOBAL batch size when B is
+ *              one shard of a larger batch; <= 0 means "derive from B"
+ *   status     optional int32 word, OR-ed with FLEXSAE_STATUS_* bits (may be NULL)
+ * kind = FLEXSAE_HIER replaces _hierarchical_sae_forward + hierarchical_sae_forward_kernel
+ *   (torch-ext/flex_sae/hierarchical_kernels.py:12-89,190-227);
+ * kind = FLEXSAE_TOPK replaces embedding_bag_forward + its kernel and the eager
+ *   bias/residual/square/mean tail (torch-ext/flex_sae/topk_kernels.py:15-68,220-222).
+ */
+int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const void* vals,
+                     const void* bias, const void* target, float* loss_out, float* resid_out,
+                     void* workspace, size_t workspace_bytes, int64_t B, int64_t K, int64_t F,
+                     int64_t D, int weight_dtype, int vals_dtype, int bias_dtype, int target_dtype,
+                     double inv_norm, int32_t* status, void* stream);
+
+/*
+ * Backward of either loss.
+ *   resid      [B,D] float32 written by flexsae_loss_fwd for the same inputs
+ *   grad_out   one float32 ON THE DEVICE: the upstream gradient of the scalar loss
+ *   dweight    [F,D] in weight_dtype, fully overwritten (untouched rows become 0)
+ *   dvals      [B,K] in vals_dtype, dbias [D] in bias_dtype, fully overwritten
+ *   dw_mode    FLEXSAE_DW_ATOMIC or FLEXSAE_DW_DETERMINISTIC
+ * kind = FLEXSAE_HIER replaces _hierarchical_sae_backward + hierarchical_sae_backward_kernel and
+ *   the dW.mul_(grad) passes (torch-ext/flex_sae/hierarchical_kernels.py:92-187,230-270,288-299);
+ * kind = FLEXSAE_TOPK replaces embedding_bag_backward with its three kernels and the autograd
+ *   backward of the eager tail (torch-ext/flex_sae/topk_kernels.py:71-185,200-210,220-222).
+ */
+int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const void* vals,
+                     const float* resid, const float* grad_out, void* dweight, void* dvals,
+                     void* dbias, void* workspace, size_t workspace_bytes, int64_t B, int64_t K,
+                     int64_t F, int64_t D, int weight_dtype, int vals_dtype, int bias_dtype,
+                     double inv_norm, int dw_mode, int32_t* status, void* stream);
+
+/* Number of kernels the last flexsae_loss_fwd / flexsae_loss_bwd call of this thread enqueued
+ * (for launch accounting in benchmarks). No reference counterpart. */
+int flexsae_last_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLEXSAE_B200_H */

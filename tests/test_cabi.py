@@ -1,0 +1,76 @@
+"""CPU: the C-ABI library builds, loads and exports exactly what include/flexsae_b200.h declares,
+the ctypes signatures agree with the header, and argument checks that need no GPU work."""
+import ctypes
+import os
+import re
+
+from flexsae_b200 import _native as nv
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_prototypes():
+    text = open(os.path.join(ROOT, "include", "flexsae_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    protos = {}
+    for m in re.finditer(r"([A-Za-z_][\w\s\*]*?)\b(flexsae_\w+)\s*\(([^;{]*?)\)\s*;", text):
+        args = m.group(3).strip()
+        n = 0 if args in ("", "void") else len(args.split(","))
+        protos[m.group(2)] = (n, args)
+    return protos
+
+
+def test_library_exports_every_declared_symbol():
+    lib = nv.load()
+    protos = header_prototypes()
+    assert len(protos) >= 9
+    for name in protos:
+        assert hasattr(lib, name), name
+
+
+def test_ctypes_signatures_match_header():
+    protos = header_prototypes()
+    assert set(protos) == set(nv.SIGNATURES)
+    for name, (n, args) in protos.items():
+        res, argtypes = nv.SIGNATURES[name]
+        assert len(argtypes) == n, (name, n, len(argtypes))
+        for decl, ct in zip(args.split(",") if n else [], argtypes):
+            decl = decl.strip()
+            if "*" in decl and "char" not in decl:
+                assert ct is ctypes.c_void_p, (name, decl)
+            elif decl.startswith("int64_t"):
+                assert ct is ctypes.c_int64, (name, decl)
+            elif decl.startswith("size_t"):
+                assert ct is ctypes.c_size_t, (name, decl)
+            elif decl.startswith("double"):
+                assert ct is ctypes.c_double, (name, decl)
+            elif decl.startswith("int "):
+                assert ct is ctypes.c_int, (name, decl)
+
+
+def test_options_and_workspace_sizes_without_gpu():
+    lib = nv.load()
+    assert lib.flexsae_version() >= 100
+    nv.set_option("lanes_bwd", 16)
+    assert nv.get_option("lanes_bwd") == 16
+    nv.set_option("lanes_bwd", 0)
+    assert lib.flexsae_set_option(b"lanes_bwd", 5) != 0 and b"lanes_bwd" in lib.flexsae_last_error()
+    assert lib.flexsae_set_option(b"no_such_option", 1) != 0
+    # headline shape: one [F, 256] fp32 slab + per-piece dvals partials + per-tile dbias partials
+    n = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2304, nv.BF16, nv.DW_ATOMIC)
+    assert 65536 * 256 * 4 <= n <= 65536 * 256 * 4 + 9 * 4096 * 128 * 4 + 512 * 2304 * 4 + 4096
+    assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2304, nv.BF16) >= 9 * 4096 * 4
+    # rejected shapes give 0 and an explanation
+    assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2301, nv.BF16) == 0
+    assert b"multiple" in lib.flexsae_last_error()
+    assert lib.flexsae_fwd_workspace_bytes(7, 1, 1, 1, 8, nv.BF16) == 0
+
+
+def test_null_pointers_are_rejected_before_any_launch():
+    lib = nv.load()
+    rc = lib.flexsae_loss_fwd(nv.HIER, None, None, None, None, None, None, None, None, 0, 4, 4, 16, 256,
+                              nv.F32, nv.F32, nv.F32, nv.F32, 0.0, None, None)
+    assert rc == -1 and b"null" in lib.flexsae_last_error()
+    rc = lib.flexsae_loss_bwd(nv.HIER, None, None, None, None, None, None, None, None, None, 0, 4, 4, 16, 256,
+                              nv.F32, nv.F32, nv.F32, 0.0, nv.DW_ATOMIC, None, None)
+    assert rc == -1

@@ -1,0 +1,231 @@
+"""GPU parity of the fused CUDA losses (called through the C ABI by the autograd Functions)
+against the oracle, the committed reference outputs and the reference's own parity matrix."""
+import numpy as np
+import pytest
+import torch
+
+import flexsae_b200 as fx
+from flexsae_b200 import _native as nv
+from flexsae_b200.workloads import CONFIGS, Workload, make_inputs
+from oracle import flexsae_oracle as orc
+from oracle import torch_reference as tref
+from tests.helpers import REFERENCE_TOLS, golden_files, inputs_as_numpy, load_golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+FUSED = {"topk": fx.triton_topk_sae_loss, "hier": fx.triton_hierarchical_sae_loss}
+# relative (max-abs-error / max-abs-value) bounds of a float32-accumulating kernel against float64
+TIGHT = {"float32": 2e-5, "bfloat16": 6e-3, "float16": 8e-4}   # 16-bit: one rounding of the output
+
+
+def run_fused(kind, x, dev="cuda", grad_out=None):
+    idx = x["indices"].to(dev)
+    w = x["weight"].to(dev).requires_grad_(True)
+    v = x["vals"].to(dev).requires_grad_(True)
+    b = x["bias"].to(dev).requires_grad_(True)
+    t = x["target"].to(dev)
+    loss = FUSED[kind](idx, w, v, b, t)
+    go = x["grad_out"] if grad_out is None else grad_out
+    loss.backward(go.to(dev))
+    assert idx.grad is None and t.grad is None
+    assert loss.dtype == torch.float32 and loss.dim() == 0
+    assert w.grad.dtype == w.dtype and v.grad.dtype == v.dtype and b.grad.dtype == b.dtype
+    return {"loss": float(loss), "dweight": w.grad.float().cpu().numpy(), "dvals": v.grad.float().cpu().numpy(),
+            "dbias": b.grad.float().cpu().numpy()}
+
+
+def assert_close_to_oracle(got, want, tol, loss_tol=1e-5):
+    assert abs(got["loss"] - float(want["loss"])) <= loss_tol * abs(float(want["loss"]))
+    for k in ("dvals", "dbias", "dweight"):
+        assert rel_err(got[k], want[k]) < tol, k
+
+
+@pytest.fixture(autouse=True)
+def _auto_options():
+    for name in ("lanes_fwd", "lanes_bwd"):
+        nv.set_option(name, 0)
+    nv.set_option("slab_pieces", 1)
+    yield
+    fx.check_status()
+
+
+@pytest.mark.parametrize("path", golden_files(), ids=lambda p: p.split("/")[-1][:-4])
+def test_fused_matches_oracle_and_reference_outputs(path):
+    w, kind, gold = load_golden(path)
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+    # and the reference's own outputs, within the reference's own tolerances
+    tols = REFERENCE_TOLS[w.weight_dtype]
+    np.testing.assert_allclose(got["loss"], float(gold["loss"]), **tols)
+    np.testing.assert_allclose(got["dvals"], gold["dvals"], **tols)
+    np.testing.assert_allclose(got["dbias"], gold["dbias"], **tols)
+    d = orc.digest(got["dweight"].astype(np.float64))
+    assert np.array_equal(d["dweight_rows_idx"], gold["dweight_rows_idx"])
+    np.testing.assert_allclose(d["dweight_rows"], gold["dweight_rows"], **tols)
+
+
+@pytest.mark.parametrize("lanes", [8, 16, 32])
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("name", ["ragged_rows_float32", "mixed_bf16w_f32v", "t16_16_64_512_float16"])
+def test_every_lane_group_width(name, kind, lanes):
+    path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
+    w, kind, gold = load_golden(path)
+    nv.set_option("lanes_fwd", lanes)
+    nv.set_option("lanes_bwd", lanes)
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+
+
+@pytest.mark.parametrize("slab_pieces", [2, 64])
+def test_several_pieces_per_backward_launch(slab_pieces):
+    path = [p for p in golden_files() if p.endswith("t16_64_128_1024_bfloat16__hier.npz")][0]
+    w, kind, gold = load_golden(path)
+    nv.set_option("lanes_bwd", 8)
+    nv.set_option("slab_pieces", slab_pieces)
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+
+
+EDGE = [
+    Workload("k5", B=9, K=5, F=50, D=264, weight_dtype="bfloat16", indices="dup", seed=21),       # K, D odd-shaped
+    Workload("k13", B=33, K=13, F=77, D=1000, indices="dup", seed=22),
+    Workload("k300", B=5, K=300, F=64, D=512, indices="dup", seed=23),                           # K > F
+    Workload("b1", B=1, K=2, F=3, D=4, indices="dup", seed=24),
+    Workload("wide", B=4, K=8, F=32, D=8200, weight_dtype="float16", vals_dtype="float16", indices="distinct", seed=25),
+]
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("w", EDGE, ids=lambda w: w.name)
+def test_edge_shapes(w, kind):
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+
+
+# ---- the reference's own parity matrix (tests/test_setup.py:5-41, tests/test_all_kernels.py:20-50)
+REF_PARAMS = [
+    (16, 16, 64, 512), (16, 32, 96, 768), (16, 64, 128, 1024), (32, 16, 128, 512), (32, 32, 160, 768),
+    (32, 64, 192, 1024), (48, 32, 176, 1024), (48, 64, 224, 1280), (64, 16, 192, 768), (64, 32, 224, 1024),
+    (64, 128, 256, 2048), (80, 32, 240, 1280), (80, 64, 256, 1536), (96, 32, 256, 1536), (96, 64, 288, 2048),
+    (96, 128, 320, 3072), (112, 64, 320, 2048), (112, 128, 352, 2560), (128, 32, 256, 1024), (128, 64, 320, 1536),
+    (128, 128, 384, 3072), (160, 64, 320, 1536), (160, 128, 384, 2560), (192, 64, 384, 2048), (192, 128, 448, 3072),
+    (192, 256, 512, 4096),
+]
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "float16"])
+@pytest.mark.parametrize("B,K,F,D", REF_PARAMS)
+def test_reference_parity_matrix(B, K, F, D, dtype, kind):
+    """Same protocol as the reference's run_funcs: one dtype for every tensor, repeated indices,
+    unsorted vals, random upstream scalar, the reference's tolerances, torch reference on the GPU."""
+    w = Workload("m", B=B, K=K, F=F, D=D, weight_dtype=dtype, vals_dtype=dtype, indices="dup", seed=1234)
+    x = make_inputs(w, "cuda")
+    got = run_fused(kind, x)
+    ref = tref.chunked_loss_and_grads(kind, x["indices"], x["weight"], x["vals"], x["bias"], x["target"],
+                                      grad_out=float(x["grad_out"]), chunk_rows=B)
+    tols = REFERENCE_TOLS[dtype]
+    np.testing.assert_allclose(got["loss"], ref["loss"], **tols)
+    np.testing.assert_allclose(got["dvals"], ref["dvals"].float().cpu().numpy(), **tols)
+    np.testing.assert_allclose(got["dweight"], ref["dweight"].float().cpu().numpy(), **tols)
+    np.testing.assert_allclose(got["dbias"], ref["dbias"].float().cpu().numpy(), **tols)
+    # and, scale-free, against the float32-upcast reference (what fp32 accumulation should match)
+    up = tref.chunked_loss_and_grads(kind, x["indices"], x["weight"], x["vals"], x["bias"], x["target"],
+                                     grad_out=float(x["grad_out"]), chunk_rows=B, upcast=True)
+    for k in ("dvals", "dweight", "dbias"):
+        assert rel_err(got[k], up[k].float().cpu().numpy()) < max(TIGHT[dtype], 1e-4), k
+
+
+def _compare_with_torch_reference_on_gpu(w: Workload, kind: str, tol: float, loss_tol: float, chunk_rows=256):
+    x = make_inputs(w, "cuda")
+    # a large upstream gradient undoes the 2/(B*K*D) factor, so absolute tolerances cannot pass vacuously
+    go = torch.tensor(float(w.B * w.D) / 2.0 * (w.K if kind == "hier" else 1.0) * 0.37)
+    got = run_fused(kind, x, grad_out=go)
+    ref = tref.chunked_loss_and_grads(kind, x["indices"], x["weight"], x["vals"], x["bias"], x["target"],
+                                      grad_out=float(go), chunk_rows=chunk_rows, upcast=True)
+    assert abs(got["loss"] - ref["loss"]) <= loss_tol * abs(ref["loss"])
+    for k in ("dvals", "dbias", "dweight"):
+        want = ref[k].float().cpu().numpy()
+        assert rel_err(got[k], want) < tol, k
+    return got, ref
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+def test_config1_fp32_tolerances(kind):
+    """B=64 K=32 F=4096 D=256 fp32: loss within 1e-5 relative, gradients rtol 1e-4 / atol 1e-6."""
+    w = CONFIGS["c1"]
+    x = make_inputs(w, "cpu")
+    for go in (x["grad_out"], torch.tensor(-3.0e5)):
+        got = run_fused(kind, x, grad_out=go)
+        want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(go))
+        assert abs(got["loss"] - want["loss"]) <= 1e-5 * abs(want["loss"])
+        for k in ("dvals", "dbias", "dweight"):
+            if abs(float(go)) < 10:      # natural gradient scale: the stated elementwise tolerances
+                np.testing.assert_allclose(got[k], want[k], rtol=1e-4, atol=1e-6)
+            assert rel_err(got[k], want[k]) < 2e-5   # scale-free, bites at any gradient magnitude
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+def test_config2_fp32_full_size(kind):
+    """B=2048 K=256 F=131072 D=1024 fp32 (the reference benchmark script's shape)."""
+    _compare_with_torch_reference_on_gpu(CONFIGS["c2"], kind, tol=1e-4, loss_tol=1e-5, chunk_rows=128)
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("name", ["c3_k32", "c3_k64", "c3_k128"])
+def test_config3_bf16_full_size(name, kind):
+    """F=65536 D=2304 B=4096 bf16 storage, fp32 vals and accumulation: within 1e-2 relative."""
+    _compare_with_torch_reference_on_gpu(CONFIGS[name], kind, tol=1e-2, loss_tol=1e-5, chunk_rows=128)
+
+
+def test_out_of_range_index_is_reported_not_dereferenced():
+    w = Workload("bad", B=8, K=4, F=16, D=256, indices="dup", seed=31)
+    x = make_inputs(w, "cuda")
+    x["indices"][3, 2] = 16
+    x["indices"][5, 0] = -7
+    loss = fx.triton_hierarchical_sae_loss(x["indices"], x["weight"], x["vals"], x["bias"], x["target"])
+    torch.cuda.synchronize()
+    with pytest.raises(IndexError):
+        fx.check_status()
+    assert torch.isfinite(loss)
+
+
+def test_no_grad_and_non_contiguous_inputs():
+    w = Workload("nc", B=24, K=8, F=64, D=512, indices="dup", seed=32)
+    x = make_inputs(w, "cuda")
+    wide = torch.zeros(w.F, 2 * w.D, device="cuda")
+    wide[:, ::2] = x["weight"]
+    with torch.no_grad():
+        a = fx.triton_topk_sae_loss(x["indices"], wide[:, ::2], x["vals"], x["bias"], x["target"])
+        b = fx.triton_topk_sae_loss(x["indices"], x["weight"], x["vals"], x["bias"], x["target"])
+    assert a.requires_grad is False and float(a) == float(b)
+
+
+def test_loss_is_run_to_run_reproducible():
+    w = CONFIGS["c3_k32"].replace(B=512, F=8192)
+    x = make_inputs(w, "cuda")
+    vals = [float(fx.triton_hierarchical_sae_loss(x["indices"], x["weight"], x["vals"], x["bias"], x["target"]))
+            for _ in range(3)]
+    assert vals[0] == vals[1] == vals[2]
+
+
+def test_rejected_arguments():
+    w = Workload("rej", B=4, K=4, F=16, D=256, indices="dup", seed=33)
+    x = make_inputs(w, "cuda")
+    with pytest.raises(TypeError):
+        fx.triton_topk_sae_loss(x["indices"].int(), x["weight"], x["vals"], x["bias"], x["target"])
+    with pytest.raises(ValueError):
+        fx.triton_topk_sae_loss(x["indices"], x["weight"], x["vals"][:, :2], x["bias"], x["target"])
+    with pytest.raises(RuntimeError):
+        fx.triton_topk_sae_loss(x["indices"].cpu(), x["weight"].cpu(), x["vals"].cpu(), x["bias"].cpu(), x["target"].cpu())
+    with pytest.raises(nv.FlexSaeNativeError):     # D not a multiple of the 16-byte row piece
+        fx.triton_topk_sae_loss(x["indices"], x["weight"][:, :254].contiguous(), x["vals"], x["bias"][:254].contiguous(),
+                                x["target"][:, :254].contiguous())
