@@ -30,9 +30,12 @@ SIGNATURES = {
     "flexsae_get_option": (_c_i64, [ctypes.c_char_p]),
     "flexsae_fwd_workspace_bytes": (_c_sz, [_c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_int]),
     "flexsae_bwd_workspace_bytes": (_c_sz, [_c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_int, _c_int]),
-    "flexsae_loss_fwd": (_c_int, [_c_int] + [_c_vp] * 8 + [_c_sz] + [_c_i64] * 4 + [_c_int] * 4 + [_c_dbl, _c_vp, _c_vp]),
-    "flexsae_loss_bwd": (_c_int, [_c_int] + [_c_vp] * 9 + [_c_sz] + [_c_i64] * 4 + [_c_int] * 3
-                         + [_c_dbl, _c_int, _c_vp, _c_vp]),
+    "flexsae_choose_segments": (_c_int, [_c_int, _c_i64, _c_i64, _c_i64, _c_i64, _c_int]),
+    "flexsae_state_bytes": (_c_sz, [_c_int, _c_i64, _c_i64, _c_i64, _c_int]),
+    "flexsae_loss_fwd": (_c_int, [_c_int] + [_c_vp] * 7 + [_c_int, _c_vp, _c_sz] + [_c_i64] * 4 + [_c_int] * 4
+                         + [_c_dbl, _c_vp, _c_vp]),
+    "flexsae_loss_bwd": (_c_int, [_c_int] + [_c_vp] * 4 + [_c_int] + [_c_vp] * 5 + [_c_sz] + [_c_i64] * 4
+                         + [_c_int] * 3 + [_c_dbl, _c_int, _c_vp, _c_vp]),
 }
 
 _lib: Optional[ctypes.CDLL] = None

@@ -31,7 +31,7 @@ struct Options {
   int lanes_fwd = 0;      // 0 = auto
   int lanes_bwd = 0;      // 0 = auto
   int l2_budget_mb = 96;  // bytes of one piece's decoder columns (+ fp32 slab) kept under this
-  int slab_pieces = 1;    // column pieces accumulated per backward launch
+  int segments = 0;       // K-segments per batch row in the backward; 0 = auto
 };
 static Options g_opt;
 
@@ -50,12 +50,23 @@ static size_t dtype_size(int dt) { return dt == FLEXSAE_F32 ? 4 : 2; }
 static bool dtype_ok(int dt) { return dt == FLEXSAE_F32 || dt == FLEXSAE_BF16 || dt == FLEXSAE_F16; }
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// warps per CTA for a lane-group width: 8 batch rows (G=32) or 16 (G=16, G=8) per CTA
-__host__ __device__ constexpr int warps_per_cta(int G) { return G == 8 ? 4 : 8; }
-__host__ __device__ constexpr int rows_per_cta(int G) { return warps_per_cta(G) * (32 / G); }
+#ifndef FLEXSAE_BWD_MINB
+#define FLEXSAE_BWD_MINB 6  // resident CTAs per SM the backward is compiled for (register cap 80)
+#endif
+#ifndef FLEXSAE_FWD_MINB
+#define FLEXSAE_FWD_MINB 6
+#endif
+constexpr int kThreads = 128;  // 4 warps per CTA: 16 / 8 / 4 lane groups for G = 8 / 16 / 32
+constexpr int kUnroll = 8;     // decoder-row loads in flight per lane; segment lengths are multiples of it
+__host__ __device__ constexpr int groups_per_cta(int G) { return kThreads / G; }
 
-constexpr int kUnroll = 8;  // decoder-row loads in flight per lane
-
+// Saved row state ("state" below), float32, written by the forward and read by the backward:
+//   TopK          [B, D]            final residual (reconstruction - target)
+//   Hierarchical  [2, NS, B, D]     part 0: residual after the last k of each K-segment,
+//                                   part 1: running sum of the prefix residuals up to there.
+// A K-segment is KS consecutive values of k (KS a multiple of kUnroll, NS = ceil(K / KS)).
+// The backward of one batch row is independent per segment given these two vectors, which is
+// what lets a small batch still fill the machine: suffix(k >= e) = total - running_sum(e - 1).
 struct FwdArgs {
   const int64_t* indices;
   const void* weight;
@@ -63,69 +74,73 @@ struct FwdArgs {
   const void* bias;
   const void* target;
   float* loss_part;  // [pieces, B]
-  float* resid;      // [B, D]
+  float* state;
   int32_t* status;
   int B, K, F, D;
   int vals_dtype, bias_dtype, target_dtype;
+  int KS, NS;
 };
 
 struct BwdArgs {
   const int64_t* indices;
   const void* weight;
   const void* vals;
-  const float* resid;     // [B, D]
+  const float* state;
   const float* grad_out;  // device scalar
-  float* slab;            // [slab_pieces, F, PW] fp32, zero on entry
+  float* slab;            // [F, PW] fp32 accumulation slab of this launch's column piece, zero on entry
+  float* conv_slab;       // the other slab: finished piece `conv_piece`, converted by trailing CTAs
+  void* dweight;          // [F, D] in the decoder's storage type
   float* dv_part;         // [pieces, B, K]
-  float* db_part;         // [row tiles, D]
   int32_t* status;
   int B, K, F, D;
   int vals_dtype;
-  int piece0;   // first column piece of this launch
-  float scale;  // 2 * inv_norm
+  int piece;       // column piece accumulated by this launch (-1: none, conversion only)
+  int conv_piece;  // column piece converted by this launch (-1: none)
+  int unit_blocks; // CTAs [0, unit_blocks) walk (row, segment) units, the rest convert
+  float scale;     // 2 * inv_norm
+  int KS, NS;
 };
 
-// Stage the CTA's indices (as int32, range-checked) and vals (as fp32) in shared memory.
-template <int RPC>
-__device__ __forceinline__ void stage_rows(const int64_t* __restrict__ indices, const void* __restrict__ vals,
-                                           int vals_dtype, int row0, int B, int K, int F, int* sidx,
-                                           float* sval, int32_t* status) {
-  const int n = RPC * K;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int r = i / K;
-    const int b = row0 + r;
-    int id = 0;
-    float v = 0.f;
-    if (b < B) {
-      const size_t g = (size_t)row0 * K + i;
-      int64_t x = indices[g];
-      if ((uint64_t)x >= (uint64_t)F) {  // never dereference an index outside the table
-        x = 0;
-        if (status) atomicOr(status, FLEXSAE_STATUS_BAD_INDEX);
-      }
-      id = (int)x;
-      v = load_scalar(vals, vals_dtype, g);
-    }
-    sidx[i] = id;
-    sval[i] = v;
+// One staged (index, value) pair: the index range-checked and narrowed, the value widened.
+__device__ __forceinline__ int2 stage_pair(const int64_t* __restrict__ indices, const void* __restrict__ vals,
+                                           int vals_dtype, size_t g, int F, int32_t* status) {
+  int64_t x = indices[g];
+  if ((uint64_t)x >= (uint64_t)F) {  // never dereference an index outside the table
+    x = 0;
+    if (status) atomicOr(status, FLEXSAE_STATUS_BAD_INDEX);
   }
+  return make_int2((int)x, __float_as_int(load_scalar(vals, vals_dtype, g)));
+}
+
+__device__ __forceinline__ void load_f32(const float* p, float* out, int n4) {
+  const float4* q = reinterpret_cast<const float4*>(p);
+  for (int i = 0; i < n4; i++) {
+    float4 t = __ldg(q + i);
+    out[4 * i] = t.x; out[4 * i + 1] = t.y; out[4 * i + 2] = t.z; out[4 * i + 3] = t.w;
+  }
+}
+
+__device__ __forceinline__ void store_f32(float* p, const float* v, int n4) {
+  float4* q = reinterpret_cast<float4*>(p);
+  for (int i = 0; i < n4; i++) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
 }
 
 // ---- forward -----------------------------------------------------------------------------------
 template <typename T, int G, bool HIER>
-__global__ void __launch_bounds__(warps_per_cta(G) * 32)
-    decoder_loss_fwd_kernel(const FwdArgs a) {
+__global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_kernel(const FwdArgs a) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
-  constexpr int RPC = rows_per_cta(G);
+  constexpr int RPC = groups_per_cta(G);
   constexpr int U = kUnroll;
-  extern __shared__ int smem_i[];
-  int* sidx = smem_i;
-  float* sval = reinterpret_cast<float*>(smem_i + RPC * a.K);
-
+  extern __shared__ int2 staged[];  // [RPC][K]
+  const int K = a.K;
   const int row0 = blockIdx.x * RPC;
   const int piece = blockIdx.y;
-  stage_rows<RPC>(a.indices, a.vals, a.vals_dtype, row0, a.B, a.K, a.F, sidx, sval, a.status);
+  for (int i = threadIdx.x; i < RPC * K; i += kThreads) {
+    const int b = row0 + i / K;
+    staged[i] = (b < a.B) ? stage_pair(a.indices, a.vals, a.vals_dtype, (size_t)row0 * K + i, a.F, a.status)
+                          : make_int2(0, 0);
+  }
   __syncthreads();
 
   const int gid = threadIdx.x / G;
@@ -134,12 +149,9 @@ __global__ void __launch_bounds__(warps_per_cta(G) * 32)
   const int col = piece * PW + lig * VEC;
   const bool active = (b < a.B) && (col < a.D);
 
-  float r[VEC], acc[VEC];
+  float r[VEC], acc[VEC], csum[VEC];
 #pragma unroll
-  for (int j = 0; j < VEC; j++) {
-    r[j] = 0.f;
-    acc[j] = 0.f;
-  }
+  for (int j = 0; j < VEC; j++) r[j] = acc[j] = csum[j] = 0.f;
   if (active) {
     float bv[VEC], tv[VEC];
     load_elems<VEC>(a.bias, a.bias_dtype, (size_t)col, bv);
@@ -150,29 +162,44 @@ __global__ void __launch_bounds__(warps_per_cta(G) * 32)
 
   const char* wcol = reinterpret_cast<const char*>(a.weight) + (size_t)col * sizeof(T);
   const size_t row_bytes = (size_t)a.D * sizeof(T);
-  const int* myidx = sidx + gid * a.K;
-  const float* myval = sval + gid * a.K;
-  const int K = a.K;
+  const int2* mine = staged + gid * K;
+  float* st_r = a.state + (size_t)b * a.D + col;                          // + s * B * D per segment
+  float* st_c = st_r + (size_t)a.NS * a.B * a.D;
+  const size_t seg_stride = (size_t)a.B * a.D;
+  int seg = 0, seg_end = a.KS;
 
   for (int k0 = 0; k0 < K; k0 += U) {
     uint4 w[U];
+    int2 e[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
+      e[u] = (k0 + u < K) ? mine[k0 + u] : make_int2(0, 0);
       w[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (active && k0 + u < K) w[u] = ld_row_piece(wcol + (size_t)myidx[k0 + u] * row_bytes);
+      if (active && k0 + u < K) w[u] = ld_row_piece(wcol + (size_t)e[u].x * row_bytes);
     }
 #pragma unroll
     for (int u = 0; u < U; u++) {
       if (k0 + u < K) {
-        const float v = myval[k0 + u];
+        const float v = __int_as_float(e[u].y);
         float wf[VEC];
         Pack<T>::unpack(w[u], wf);
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
-          r[j] = fmaf(v, wf[j], r[j]);                    // residual of the k-th prefix
-          if (HIER) acc[j] = fmaf(r[j], r[j], acc[j]);   // every prefix is penalised
+          r[j] = fmaf(v, wf[j], r[j]);  // residual of the k-th prefix
+          if (HIER) {
+            acc[j] = fmaf(r[j], r[j], acc[j]);  // every prefix is penalised
+            csum[j] += r[j];
+          }
         }
       }
+    }
+    if (HIER && (k0 + U == seg_end) && (k0 + U < K)) {  // a segment ends inside the row
+      if (active) {
+        store_f32(st_r + seg * seg_stride, r, VEC / 4);
+        store_f32(st_c + seg * seg_stride, csum, VEC / 4);
+      }
+      seg++;
+      seg_end += a.KS;
     }
   }
   if (!HIER) {
@@ -185,9 +212,8 @@ __global__ void __launch_bounds__(warps_per_cta(G) * 32)
   s = group_sum<G>(s);
   if (lig == 0 && b < a.B) a.loss_part[(size_t)piece * a.B + b] = s;
   if (active) {
-    float4* out = reinterpret_cast<float4*>(a.resid + (size_t)b * a.D + col);
-#pragma unroll
-    for (int i = 0; i < VEC / 4; i++) out[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+    store_f32(st_r + seg * seg_stride, r, VEC / 4);  // HIER: seg == NS - 1 here; TopK: seg == 0
+    if (HIER) store_f32(st_c + seg * seg_stride, csum, VEC / 4);
   }
 }
 
@@ -207,147 +233,215 @@ __global__ void __launch_bounds__(1024) loss_finalize_kernel(const float* __rest
 }
 
 // ---- backward (atomic slab) ----------------------------------------------------------------------
+// Sums each of 8 per-lane values over the G lanes of a group with 8 (G=16) shuffles instead of
+// 8*log2(G): every exchange step halves the number of values a lane is responsible for.
+// Returns, on every lane, the group total of value number (lig & 7).
+template <int G>
+__device__ __forceinline__ float group_sum8(const float* d, int lig) {
+  float e[4], f[2];
+  const bool b2 = lig & 4, b1 = lig & 2, b0 = lig & 1;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const float send = b2 ? d[i] : d[i + 4];
+    const float keep = b2 ? d[i + 4] : d[i];
+    e[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const float send = b1 ? e[i] : e[i + 2];
+    const float keep = b1 ? e[i + 2] : e[i];
+    f[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+  float g = (b0 ? f[1] : f[0]) + __shfl_xor_sync(0xffffffffu, b0 ? f[0] : f[1], 1);
+#pragma unroll
+  for (int m = 8; m < G; m <<= 1) g += __shfl_xor_sync(0xffffffffu, g, m);
+  return g;
+}
+
+// fp32 slab -> the dweight columns of one piece in the decoder's storage type; clears the slab.
+// Run by the trailing CTAs of the launch that accumulates the NEXT piece into the other slab,
+// so the conversion streams through L2 while the atomic units are busy with that piece.
+template <typename T, int G>
+__device__ __forceinline__ void convert_slab(float* __restrict__ slab, void* __restrict__ dweight, int F, int D, int piece,
+                                             int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = 4;  // independent items in flight per thread
+  const size_t total = (size_t)F * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    float4 lo[IL], hi[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* s = slab + (i / G) * PW + (i % G) * 4;
+        lo[q] = *reinterpret_cast<const float4*>(s);
+        if (VEC == 8) hi[q] = *reinterpret_cast<const float4*>(s + G * 4);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        const size_t f = i / G;
+        const int lig = (int)(i % G);
+        float* s = slab + f * PW + lig * 4;
+        *reinterpret_cast<float4*>(s) = zero;
+        float v[8] = {lo[q].x, lo[q].y, lo[q].z, lo[q].w, 0.f, 0.f, 0.f, 0.f};
+        if (VEC == 8) {
+          *reinterpret_cast<float4*>(s + G * 4) = zero;
+          v[4] = hi[q].x; v[5] = hi[q].y; v[6] = hi[q].z; v[7] = hi[q].w;
+        }
+        const int col = piece * PW + lig * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(dweight) + f * D + col) = Pack<T>::pack(v);
+      }
+    }
+  }
+}
+
 // Slab column order: a lane's elements 0..3 live at column lig*4 and, for 8-element packs,
 // elements 4..7 at column G*4 + lig*4, so that each red.v4 instruction of a lane group covers
 // whole contiguous 32-byte sectors (a lane-contiguous 32-byte layout would make every sector
 // the target of two separate instructions and halve the L2 atomic throughput).
+//
+// One lane group owns one (batch row, K-segment) unit and walks the segment from its last k
+// down to its first: suffix += residual; dweight[idx] += vals * suffix; dvals = <row, suffix>;
+// residual -= vals * row  (the reverse walk of hierarchical_kernels.py:147-173).
 template <typename T, int G, bool HIER>
-__global__ void __launch_bounds__(warps_per_cta(G) * 32)
-    decoder_loss_bwd_kernel(const BwdArgs a) {
+__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_kernel(const BwdArgs a) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
-  constexpr int RPC = rows_per_cta(G);
+  constexpr int UPC = groups_per_cta(G);
   constexpr int U = kUnroll;
-  extern __shared__ int smem_i[];
-  int* sidx = smem_i;
-  float* sval = reinterpret_cast<float*>(smem_i + RPC * a.K);
-
-  const int row0 = blockIdx.x * RPC;
-  const int piece = a.piece0 + blockIdx.y;
-  stage_rows<RPC>(a.indices, a.vals, a.vals_dtype, row0, a.B, a.K, a.F, sidx, sval, a.status);
+  extern __shared__ int2 staged[];  // [UPC][KS]
+  if ((int)blockIdx.x >= a.unit_blocks) {
+    convert_slab<T, G>(a.conv_slab, a.dweight, a.F, a.D, a.conv_piece, blockIdx.x - a.unit_blocks,
+                       gridDim.x - a.unit_blocks);
+    return;
+  }
+  const int K = a.K, KS = a.KS, NS = a.NS;
+  const int unit0 = blockIdx.x * UPC;
+  const int nunits = a.B * NS;
+  const int piece = a.piece;
+  for (int i = threadIdx.x; i < UPC * KS; i += kThreads) {
+    const int lu = i / KS;
+    const int j = i - lu * KS;
+    const int u = unit0 + lu;
+    int2 e = make_int2(0, 0);
+    if (u < nunits) {
+      const int row = u / NS;
+      const int k = (u - row * NS) * KS + j;
+      if (k < K) e = stage_pair(a.indices, a.vals, a.vals_dtype, (size_t)row * K + k, a.F, a.status);
+    }
+    staged[i] = e;
+  }
   __syncthreads();
 
   const int gid = threadIdx.x / G;
   const int lig = threadIdx.x % G;
-  const int b = row0 + gid;
+  const int unit = unit0 + gid;
+  const bool live = unit < nunits;
+  const int row = live ? unit / NS : 0;
+  const int seg = live ? unit - row * NS : 0;
+  const int k_first = seg * KS;
+  const int n = live ? min(KS, K - k_first) : 0;  // k's in this segment
   const int col = piece * PW + lig * VEC;
-  const bool active = (b < a.B) && (col < a.D);
+  const bool active = live && (col < a.D);
   const float coef = __ldg(a.grad_out) * a.scale;
 
   float r[VEC], suf[VEC];
 #pragma unroll
-  for (int j = 0; j < VEC; j++) r[j] = 0.f;
+  for (int j = 0; j < VEC; j++) r[j] = suf[j] = 0.f;
   if (active) {
-    const float4* in = reinterpret_cast<const float4*>(a.resid + (size_t)b * a.D + col);
+    const size_t seg_stride = (size_t)a.B * a.D;
+    const float* st = a.state + (size_t)row * a.D + col;
+    load_f32(st + (HIER ? seg : 0) * seg_stride, r, VEC / 4);
+    if (!HIER) {
 #pragma unroll
-    for (int i = 0; i < VEC / 4; i++) {
-      float4 t = __ldg(in + i);
-      r[4 * i] = t.x;
-      r[4 * i + 1] = t.y;
-      r[4 * i + 2] = t.z;
-      r[4 * i + 3] = t.w;
+      for (int j = 0; j < VEC; j++) suf[j] = r[j];  // TopK: every k sees the same residual
+    } else if (seg != NS - 1) {
+      float c_here[VEC], c_all[VEC];
+      load_f32(st + (size_t)(NS + seg) * seg_stride, c_here, VEC / 4);
+      load_f32(st + (size_t)(2 * NS - 1) * seg_stride, c_all, VEC / 4);
+#pragma unroll
+      for (int j = 0; j < VEC; j++) suf[j] = c_all[j] - c_here[j];  // residuals of all later k
     }
   }
-#pragma unroll
-  for (int j = 0; j < VEC; j++) suf[j] = HIER ? 0.f : r[j];
 
   const char* wcol = reinterpret_cast<const char*>(a.weight) + (size_t)col * sizeof(T);
   const size_t row_bytes = (size_t)a.D * sizeof(T);
-  const int* myidx = sidx + gid * a.K;
-  const float* myval = sval + gid * a.K;
-  const int K = a.K;
-  float* slab = a.slab + (size_t)blockIdx.y * a.F * PW + lig * 4;
-  float* dv = a.dv_part + ((size_t)piece * a.B + (b < a.B ? b : 0)) * K;
+  const int2* mine = staged + gid * KS;
+  float* slab = a.slab + lig * 4;
+  float* dv = a.dv_part + ((size_t)piece * a.B + row) * K + k_first;
 
-  for (int kb = K - 1; kb >= 0; kb -= U) {
+  for (int jb = KS - 1; jb >= 0; jb -= U) {  // KS is a multiple of U
     uint4 w[U];
+    int2 e[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
+      e[u] = mine[jb - u];
       w[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (active && kb - u >= 0) w[u] = ld_row_piece(wcol + (size_t)myidx[kb - u] * row_bytes);
+      if (active && jb - u < n) w[u] = ld_row_piece(wcol + (size_t)e[u].x * row_bytes);
     }
+    float d[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
-      const int k = kb - u;
-      if (k >= 0) {
-        const float v = myval[k];
-        const float c = v * coef;
-        float wf[VEC];
-        Pack<T>::unpack(w[u], wf);
-        if (HIER) {
+      const bool in_seg = jb - u < n;
+      const float v = __int_as_float(e[u].y);
+      const float c = v * coef;
+      float wf[VEC];
+      Pack<T>::unpack(w[u], wf);
+      if (HIER && in_seg) {
 #pragma unroll
-          for (int j = 0; j < VEC; j++) suf[j] += r[j];  // S_k = sum_{j>=k} residual_j
-        }
-        if (active) {
-          float* dst = slab + (size_t)myidx[k] * PW;
-          red_add_v4(dst, suf[0] * c, suf[1] * c, suf[2] * c, suf[3] * c);
-          if (VEC == 8) red_add_v4(dst + G * 4, suf[VEC - 4] * c, suf[VEC - 3] * c, suf[VEC - 2] * c, suf[VEC - 1] * c);
-        }
-        float dot = 0.f;
+        for (int j = 0; j < VEC; j++) suf[j] += r[j];  // S_k = sum_{j>=k} residual_j
+      }
+      if (active && in_seg) {
+        float* dst = slab + (size_t)e[u].x * PW;
+        red_add_v4(dst, suf[0] * c, suf[1] * c, suf[2] * c, suf[3] * c);
+        if (VEC == 8) red_add_v4(dst + G * 4, suf[VEC - 4] * c, suf[VEC - 3] * c, suf[VEC - 2] * c, suf[VEC - 1] * c);
+      }
+      float dot = 0.f;
 #pragma unroll
-        for (int j = 0; j < VEC; j++) dot = fmaf(wf[j], suf[j], dot);
-        dot = group_sum<G>(dot);
-        if (lig == 0 && b < a.B) dv[k] = dot * coef;
-        if (HIER) {
+      for (int j = 0; j < VEC; j++) dot = fmaf(wf[j], suf[j], dot);
+      d[u] = dot;  // rows outside the segment were loaded as zeros
+      if (HIER) {
 #pragma unroll
-          for (int j = 0; j < VEC; j++) r[j] = fmaf(-v, wf[j], r[j]);  // step back to prefix k-1
-        }
+        for (int j = 0; j < VEC; j++) r[j] = fmaf(-v, wf[j], r[j]);  // step back to prefix k-1
       }
     }
-  }
-
-  // dbias: column sums of S_0 over this CTA's rows, one partial row per row tile
-  __syncthreads();
-  float* red = reinterpret_cast<float*>(smem_i);  // [RPC][PW], aliases the staged indices
-#pragma unroll
-  for (int j = 0; j < VEC; j++) red[gid * PW + lig * VEC + j] = suf[j];
-  __syncthreads();
-  if ((int)threadIdx.x < PW) {
-    const int c = piece * PW + threadIdx.x;
-    if (c < a.D) {
-      float s = 0.f;
-#pragma unroll
-      for (int g = 0; g < RPC; g++) s += red[g * PW + threadIdx.x];
-      a.db_part[(size_t)blockIdx.x * a.D + c] = s * coef;
-    }
+    const float tot = group_sum8<G>(d, lig);
+    const int j = jb - (lig & 7);
+    if (live && lig < 8 && j < n) dv[j] = tot * coef;
   }
 }
 
-// fp32 slab -> dweight columns of one piece in the decoder's storage type; clears the slab.
-template <typename T, int G>
-__global__ void __launch_bounds__(256) slab_to_dweight_kernel(float* __restrict__ slab, void* __restrict__ dweight, int F, int D,
-                                                              int piece0, int npieces) {
-  constexpr int VEC = Pack<T>::VEC;
-  constexpr int PW = G * VEC;
-  const size_t total = (size_t)npieces * F * G;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-    const int lig = (int)(i % G);
-    const size_t fr = i / G;  // piece-in-launch * F + f
-    const int pl = (int)(fr / F);
-    const int f = (int)(fr - (size_t)pl * F);
-    float* s = slab + fr * PW + lig * 4;
-    float v[VEC];
-    float4 t0 = *reinterpret_cast<float4*>(s);
-    v[0] = t0.x; v[1] = t0.y; v[2] = t0.z; v[3] = t0.w;
-    *reinterpret_cast<float4*>(s) = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (VEC == 8) {
-      float4 t1 = *reinterpret_cast<float4*>(s + G * 4);
-      v[VEC - 4] = t1.x; v[VEC - 3] = t1.y; v[VEC - 2] = t1.z; v[VEC - 1] = t1.w;
-      *reinterpret_cast<float4*>(s + G * 4) = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    const int col = (piece0 + pl) * PW + lig * VEC;
-    if (col < D) {
-      uint4* out = reinterpret_cast<uint4*>(reinterpret_cast<T*>(dweight) + (size_t)f * D + col);
-      *out = Pack<T>::pack(v);
-    }
+// Column sums of a [B, D] fp32 matrix over row blocks: part[rb][d] = sum of rows of block rb.
+// dbias is coef * (column sums of the final residual (TopK) / of the summed prefix residuals).
+__global__ void __launch_bounds__(128) column_sums_kernel(const float* __restrict__ x, int B, int D, int rows_per_block,
+                                                         float* __restrict__ part) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  const int r0 = blockIdx.y * rows_per_block;
+  const int r1 = min(B, r0 + rows_per_block);
+  float acc[8];
+#pragma unroll
+  for (int q = 0; q < 8; q++) acc[q] = 0.f;
+  for (int r = r0; r < r1; r += 8) {
+#pragma unroll
+    for (int q = 0; q < 8; q++)
+      if (r + q < r1) acc[q] += x[(size_t)(r + q) * D + d];
   }
+  part[(size_t)blockIdx.y * D + d] = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
 }
 
-// dvals = sum over column pieces (fixed order), dbias = sum over row tiles (fixed order).
+// dvals = sum over column pieces (fixed order), dbias = coef * sum over row blocks (fixed order).
 __global__ void __launch_bounds__(256) grads_finalize_kernel(const float* __restrict__ dv_part, int pieces, size_t BK,
                                                             void* __restrict__ dvals, int vals_dtype,
-                                                            const float* __restrict__ db_part, int tiles, int D,
-                                                            void* __restrict__ dbias, int bias_dtype, int dv_blocks) {
+                                                            const float* __restrict__ db_part, int row_blocks, int D,
+                                                            void* __restrict__ dbias, int bias_dtype, int dv_blocks,
+                                                            const float* __restrict__ grad_out, float scale) {
   if ((int)blockIdx.x < dv_blocks) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < BK) {
@@ -359,8 +453,8 @@ __global__ void __launch_bounds__(256) grads_finalize_kernel(const float* __rest
     const int d = (blockIdx.x - dv_blocks) * blockDim.x + threadIdx.x;
     if (d < D) {
       float s = 0.f;
-      for (int t = 0; t < tiles; t++) s += db_part[(size_t)t * D + d];
-      store_scalar(dbias, bias_dtype, (size_t)d, s);
+      for (int t = 0; t < row_blocks; t++) s += db_part[(size_t)t * D + d];
+      store_scalar(dbias, bias_dtype, (size_t)d, s * (__ldg(grad_out) * scale));
     }
   }
 }
@@ -379,7 +473,7 @@ static int check_shape(int kind, const Shape& s, int wdt) {
   const int vec = 16 / (int)dtype_size(wdt);
   if (s.D % vec != 0)
     return fail(FLEXSAE_EUNSUPPORTED, "D=%lld must be a multiple of %d (16-byte row pieces)", (long long)s.D, vec);
-  if (s.F > (1ll << 30) || s.D > (1ll << 20) || s.B > (1ll << 30) || s.B * s.K > (1ll << 31) - 1)
+  if (s.F > (1ll << 30) || s.D > (1ll << 20) || s.B > (1ll << 27) || s.B * s.K > (1ll << 31) - 1)
     return fail(FLEXSAE_EUNSUPPORTED, "shape too large for 32-bit row/position arithmetic");
   // indices and vals of a CTA's rows are staged in shared memory: 16 rows * K * 8 bytes
   if (s.K > 1600) return fail(FLEXSAE_EUNSUPPORTED, "K=%lld above the supported maximum of 1600", (long long)s.K);
@@ -398,9 +492,50 @@ static int choose_lanes(int64_t F, int wdt, bool with_slab, int forced) {
   return 32;  // nothing fits: stream from HBM with the widest (most coalesced) row pieces
 }
 
+static int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// segment length for a requested number of K-segments, and the count that length gives
+static void segment_layout(int K, int want, int* KS, int* NS) {
+  if (want < 1) want = 1;
+  int ks = round_up((K + want - 1) / want, kUnroll);
+  *KS = ks;
+  *NS = (K + ks - 1) / ks;
+}
+
+// K-segments so that one column piece of the backward offers about a full machine of warps
+static int choose_segments(const Shape& s, int wdt) {
+  int want = g_opt.segments;
+  if (want <= 0) {
+    const int G = choose_lanes(s.F, wdt, true, g_opt.lanes_bwd);
+    const double warps = (double)s.B * G / 32.0;
+    const double target = 148.0 * 32.0;
+    want = (int)((target + warps - 1) / warps);
+    if (want > 8) want = 8;
+  }
+  int KS, NS;
+  segment_layout((int)s.K, want, &KS, &NS);
+  return NS;
+}
+
+static size_t state_floats(int kind, const Shape& s, int NS) {
+  return (size_t)s.B * s.D * (kind == FLEXSAE_HIER ? 2 * (size_t)NS : 1);
+}
+
+static int check_segments(int kind, const Shape& s, int segments, int* KS, int* NS) {
+  if (segments < 1) return fail(FLEXSAE_EINVAL, "segments must be >= 1 (got %d)", segments);
+  segment_layout((int)s.K, segments, KS, NS);
+  if (*NS != segments)
+    return fail(FLEXSAE_EINVAL, "segments=%d is not a layout of K=%lld (use flexsae_choose_segments; nearest is %d)",
+                segments, (long long)s.K, *NS);
+  return 0;
+}
+
+constexpr int kMaxRowBlocks = 128;  // partial rows of the dbias column sums
+constexpr int kConvertBlocks = 148 * 3;  // trailing CTAs that convert the previous piece's slab
+
 struct BwdPlan {
-  int G, PW, pieces, tiles, slab_pieces;
-  size_t off_slab, off_dv, off_db, total;
+  int G, PW, pieces, row_blocks, rows_per_block;
+  size_t slab_bytes, off_slab, off_dv, off_db, total;
 };
 
 static BwdPlan plan_bwd(const Shape& s, int wdt) {
@@ -409,15 +544,17 @@ static BwdPlan plan_bwd(const Shape& s, int wdt) {
   p.G = choose_lanes(s.F, wdt, true, g_opt.lanes_bwd);
   p.PW = p.G * vec;
   p.pieces = (int)((s.D + p.PW - 1) / p.PW);
-  p.tiles = (int)((s.B + rows_per_cta(p.G) - 1) / rows_per_cta(p.G));
-  p.slab_pieces = g_opt.slab_pieces < 1 ? 1 : (g_opt.slab_pieces > p.pieces ? p.pieces : g_opt.slab_pieces);
+  p.rows_per_block = (int)((s.B + kMaxRowBlocks - 1) / kMaxRowBlocks);
+  if (p.rows_per_block < 32) p.rows_per_block = 32;
+  p.row_blocks = (int)((s.B + p.rows_per_block - 1) / p.rows_per_block);
   size_t off = 0;
-  p.off_slab = off;
-  off = align_up(off + (size_t)p.slab_pieces * s.F * p.PW * 4, 256);
+  p.off_slab = off;  // two slabs: one accumulating, one being converted
+  p.slab_bytes = align_up((size_t)s.F * p.PW * 4, 256);
+  off += 2 * p.slab_bytes;
   p.off_dv = off;
   off = align_up(off + (size_t)p.pieces * s.B * s.K * 4, 256);
   p.off_db = off;
-  off = align_up(off + (size_t)p.tiles * s.D * 4, 256);
+  off = align_up(off + (size_t)p.row_blocks * s.D * 4, 256);
   p.total = off;
   return p;
 }
@@ -437,51 +574,46 @@ static FwdPlan plan_fwd(const Shape& s, int wdt) {
   return p;
 }
 
+template <typename K>
+static cudaError_t allow_smem(K kern, size_t smem) {
+  if (smem <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+}
+
 template <typename T, int G, bool HIER>
 static cudaError_t launch_fwd(const FwdArgs& a, int pieces, cudaStream_t st) {
-  constexpr int RPC = rows_per_cta(G);
-  const size_t smem = (size_t)RPC * a.K * 8;
+  constexpr int RPC = groups_per_cta(G);
+  const size_t smem = (size_t)RPC * a.K * sizeof(int2);
   auto kern = decoder_loss_fwd_kernel<T, G, HIER>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-  }
+  if (cudaError_t e = allow_smem(kern, smem)) return e;
   dim3 grid((a.B + RPC - 1) / RPC, pieces);
-  kern<<<grid, warps_per_cta(G) * 32, smem, st>>>(a);
+  kern<<<grid, kThreads, smem, st>>>(a);
   t_launches++;
   return cudaGetLastError();
 }
 
 template <typename T, int G, bool HIER>
-static cudaError_t launch_bwd(const BwdArgs& a, int npieces, cudaStream_t st) {
-  constexpr int RPC = rows_per_cta(G);
-  constexpr int PW = G * Pack<T>::VEC;
-  size_t smem = (size_t)RPC * a.K * 8;
-  if (smem < (size_t)RPC * PW * 4) smem = (size_t)RPC * PW * 4;
+static cudaError_t launch_bwd(BwdArgs a, cudaStream_t st) {
+  constexpr int UPC = groups_per_cta(G);
+  const size_t smem = (size_t)UPC * a.KS * sizeof(int2);
   auto kern = decoder_loss_bwd_kernel<T, G, HIER>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
+  if (cudaError_t e = allow_smem(kern, smem)) return e;
+  const long long units = (long long)a.B * a.NS;
+  a.unit_blocks = a.piece >= 0 ? (int)((units + UPC - 1) / UPC) : 0;
+  int conv_blocks = 0;
+  if (a.conv_piece >= 0) {
+    const long long items = (long long)a.F * G;
+    conv_blocks = (int)((items + kThreads * 4 - 1) / (kThreads * 4));
+    const int cap = a.piece >= 0 ? kConvertBlocks : kConvertBlocks * 4;
+    if (conv_blocks > cap) conv_blocks = cap;
   }
-  dim3 grid((a.B + RPC - 1) / RPC, npieces);
-  kern<<<grid, warps_per_cta(G) * 32, smem, st>>>(a);
-  t_launches++;
-  return cudaGetLastError();
-}
-
-template <typename T, int G>
-static cudaError_t launch_convert(float* slab, void* dweight, int F, int D, int piece0, int npieces, cudaStream_t st) {
-  const size_t total = (size_t)npieces * F * G;
-  size_t blocks = (total + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  slab_to_dweight_kernel<T, G><<<(unsigned)blocks, 256, 0, st>>>(slab, dweight, F, D, piece0, npieces);
+  kern<<<a.unit_blocks + conv_blocks, kThreads, smem, st>>>(a);
   t_launches++;
   return cudaGetLastError();
 }
 
 // dispatch over (element type, lanes, loss kind)
-#define FLEXSAE_DISPATCH_G(T, G, kind, CALL)          \
-  ((kind) == FLEXSAE_HIER ? CALL(T, G, true) : CALL(T, G, false))
+#define FLEXSAE_DISPATCH_G(T, G, kind, CALL) ((kind) == FLEXSAE_HIER ? CALL(T, G, true) : CALL(T, G, false))
 #define FLEXSAE_DISPATCH_T(T, G, kind, CALL)                                                       \
   ((G) == 32 ? FLEXSAE_DISPATCH_G(T, 32, kind, CALL)                                               \
              : ((G) == 16 ? FLEXSAE_DISPATCH_G(T, 16, kind, CALL) : FLEXSAE_DISPATCH_G(T, 8, kind, CALL)))
@@ -498,7 +630,7 @@ using namespace flexsae;
 
 extern "C" {
 
-int flexsae_version(void) { return 100; }
+int flexsae_version(void) { return 200; }
 
 const char* flexsae_last_error(void) { return t_err; }
 
@@ -510,7 +642,7 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "lanes_fwd") && lanes_ok) { g_opt.lanes_fwd = (int)value; return 0; }
   if (!strcmp(name, "lanes_bwd") && lanes_ok) { g_opt.lanes_bwd = (int)value; return 0; }
   if (!strcmp(name, "l2_budget_mb") && value >= 1 && value <= 4096) { g_opt.l2_budget_mb = (int)value; return 0; }
-  if (!strcmp(name, "slab_pieces") && value >= 1 && value <= 65535) { g_opt.slab_pieces = (int)value; return 0; }
+  if (!strcmp(name, "segments") && value >= 0 && value <= 256) { g_opt.segments = (int)value; return 0; }
   return fail(FLEXSAE_EINVAL, "unknown option or value: %s=%lld", name, (long long)value);
 }
 
@@ -519,8 +651,20 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "lanes_fwd")) return g_opt.lanes_fwd;
   if (!strcmp(name, "lanes_bwd")) return g_opt.lanes_bwd;
   if (!strcmp(name, "l2_budget_mb")) return g_opt.l2_budget_mb;
-  if (!strcmp(name, "slab_pieces")) return g_opt.slab_pieces;
+  if (!strcmp(name, "segments")) return g_opt.segments;
   return -1;
+}
+
+int flexsae_choose_segments(int kind, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype) {
+  Shape s{B, K, F, D};
+  if (check_shape(kind, s, weight_dtype)) return 0;
+  return choose_segments(s, weight_dtype);
+}
+
+size_t flexsae_state_bytes(int kind, int64_t B, int64_t K, int64_t D, int segments) {
+  if ((kind != FLEXSAE_TOPK && kind != FLEXSAE_HIER) || B < 1 || K < 1 || D < 1 || segments < 1) return 0;
+  Shape s{B, K, 1, D};
+  return state_floats(kind, s, segments) * sizeof(float);
 }
 
 size_t flexsae_fwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype) {
@@ -532,23 +676,28 @@ size_t flexsae_fwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, in
 size_t flexsae_bwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype, int dw_mode) {
   Shape s{B, K, F, D};
   if (check_shape(kind, s, weight_dtype)) return 0;
-  if (dw_mode != FLEXSAE_DW_ATOMIC) return 0;
+  if (dw_mode != FLEXSAE_DW_ATOMIC) {
+    fail(FLEXSAE_EUNSUPPORTED, "dweight mode %d is not available", dw_mode);
+    return 0;
+  }
   return plan_bwd(s, weight_dtype).total;
 }
 
 int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const void* vals, const void* bias,
-                     const void* target, float* loss_out, float* resid_out, void* workspace, size_t workspace_bytes,
-                     int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype, int vals_dtype, int bias_dtype,
-                     int target_dtype, double inv_norm, int32_t* status, void* stream) {
+                     const void* target, float* loss_out, float* state_out, int segments, void* workspace,
+                     size_t workspace_bytes, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
+                     int vals_dtype, int bias_dtype, int target_dtype, double inv_norm, int32_t* status, void* stream) {
   t_launches = 0;
   Shape s{B, K, F, D};
   if (int rc = check_shape(kind, s, weight_dtype)) return rc;
   if (!dtype_ok(vals_dtype) || !dtype_ok(bias_dtype) || !dtype_ok(target_dtype))
     return fail(FLEXSAE_EINVAL, "unknown dtype code (vals %d, bias %d, target %d)", vals_dtype, bias_dtype, target_dtype);
-  if (!indices || !weight || !vals || !bias || !target || !loss_out || !resid_out || !workspace)
+  int KS, NS;
+  if (int rc = check_segments(kind, s, segments, &KS, &NS)) return rc;
+  if (!indices || !weight || !vals || !bias || !target || !loss_out || !state_out || !workspace)
     return fail(FLEXSAE_EINVAL, "null pointer argument");
-  if (!aligned16(weight) || !aligned16(bias) || !aligned16(target) || !aligned16(resid_out) || !aligned16(workspace))
-    return fail(FLEXSAE_EINVAL, "weight, bias, target, resid and workspace must be 16-byte aligned");
+  if (!aligned16(weight) || !aligned16(bias) || !aligned16(target) || !aligned16(state_out) || !aligned16(workspace))
+    return fail(FLEXSAE_EINVAL, "weight, bias, target, state and workspace must be 16-byte aligned");
   const FwdPlan p = plan_fwd(s, weight_dtype);
   if (workspace_bytes < p.total)
     return fail(FLEXSAE_EWORKSPACE, "forward workspace too small: %zu < %zu bytes", workspace_bytes, p.total);
@@ -558,9 +707,11 @@ int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const
   FwdArgs a;
   a.indices = indices; a.weight = weight; a.vals = vals; a.bias = bias; a.target = target;
   a.loss_part = reinterpret_cast<float*>(workspace);
-  a.resid = resid_out; a.status = status;
+  a.state = state_out; a.status = status;
   a.B = (int)B; a.K = (int)K; a.F = (int)F; a.D = (int)D;
   a.vals_dtype = vals_dtype; a.bias_dtype = bias_dtype; a.target_dtype = target_dtype;
+  a.KS = (kind == FLEXSAE_HIER) ? KS : round_up((int)K, kUnroll);
+  a.NS = (kind == FLEXSAE_HIER) ? NS : 1;
 
 #define CALL_FWD(T, G, H) launch_fwd<T, G, H>(a, p.pieces, st)
   cudaError_t e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_FWD);
@@ -573,8 +724,8 @@ int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const
   return 0;
 }
 
-int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const void* vals, const float* resid,
-                     const float* grad_out, void* dweight, void* dvals, void* dbias, void* workspace,
+int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const void* vals, const float* state,
+                     int segments, const float* grad_out, void* dweight, void* dvals, void* dbias, void* workspace,
                      size_t workspace_bytes, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
                      int vals_dtype, int bias_dtype, double inv_norm, int dw_mode, int32_t* status, void* stream) {
   t_launches = 0;
@@ -584,10 +735,12 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
     return fail(FLEXSAE_EINVAL, "unknown dtype code (vals %d, bias %d)", vals_dtype, bias_dtype);
   if (dw_mode != FLEXSAE_DW_ATOMIC)
     return fail(FLEXSAE_EUNSUPPORTED, "dweight mode %d is not available", dw_mode);
-  if (!indices || !weight || !vals || !resid || !grad_out || !dweight || !dvals || !dbias || !workspace)
+  int KS, NS;
+  if (int rc = check_segments(kind, s, segments, &KS, &NS)) return rc;
+  if (!indices || !weight || !vals || !state || !grad_out || !dweight || !dvals || !dbias || !workspace)
     return fail(FLEXSAE_EINVAL, "null pointer argument");
-  if (!aligned16(weight) || !aligned16(resid) || !aligned16(dweight) || !aligned16(workspace))
-    return fail(FLEXSAE_EINVAL, "weight, resid, dweight and workspace must be 16-byte aligned");
+  if (!aligned16(weight) || !aligned16(state) || !aligned16(dweight) || !aligned16(workspace))
+    return fail(FLEXSAE_EINVAL, "weight, state, dweight and workspace must be 16-byte aligned");
   const BwdPlan p = plan_bwd(s, weight_dtype);
   if (workspace_bytes < p.total)
     return fail(FLEXSAE_EWORKSPACE, "backward workspace too small: %zu < %zu bytes", workspace_bytes, p.total);
@@ -596,35 +749,47 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   char* ws = reinterpret_cast<char*>(workspace);
 
   BwdArgs a;
-  a.indices = indices; a.weight = weight; a.vals = vals; a.resid = resid; a.grad_out = grad_out;
-  a.slab = reinterpret_cast<float*>(ws + p.off_slab);
+  a.indices = indices; a.weight = weight; a.vals = vals; a.state = state; a.grad_out = grad_out;
+  float* slabs[2] = {reinterpret_cast<float*>(ws + p.off_slab), reinterpret_cast<float*>(ws + p.off_slab + p.slab_bytes)};
+  a.dweight = dweight;
   a.dv_part = reinterpret_cast<float*>(ws + p.off_dv);
-  a.db_part = reinterpret_cast<float*>(ws + p.off_db);
   a.status = status;
   a.B = (int)B; a.K = (int)K; a.F = (int)F; a.D = (int)D;
   a.vals_dtype = vals_dtype;
   a.scale = (float)(2.0 * inv_norm);
+  a.KS = KS; a.NS = NS;
+  float* db_part = reinterpret_cast<float*>(ws + p.off_db);
 
-  // The slab is cleared once here; afterwards every conversion pass leaves it cleared.
-  cudaError_t e = cudaMemsetAsync(a.slab, 0, (size_t)p.slab_pieces * F * p.PW * 4, st);
+  // dbias only needs what the forward left behind: column sums of the final residual (TopK) or
+  // of the summed prefix residuals (Hierarchical: part 1 of the state, last segment).
+  const float* colsrc = state + (kind == FLEXSAE_HIER ? (size_t)(2 * NS - 1) * B * D : 0);
+  column_sums_kernel<<<dim3((unsigned)((D + 127) / 128), p.row_blocks), 128, 0, st>>>(colsrc, (int)B, (int)D,
+                                                                                      p.rows_per_block, db_part);
+  t_launches++;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail((int)e, "column sums launch failed: %s", cudaGetErrorString(e));
+
+  // Both slabs are cleared once here; afterwards every conversion leaves its slab cleared.
+  // Launch i accumulates piece i into slab i%2 and converts piece i-1 out of the other slab;
+  // one more launch converts the last piece.
+  e = cudaMemsetAsync(slabs[0], 0, 2 * p.slab_bytes, st);
   if (e != cudaSuccess) return fail((int)e, "slab clear failed: %s", cudaGetErrorString(e));
-  for (int p0 = 0; p0 < p.pieces; p0 += p.slab_pieces) {
-    const int np = (p.pieces - p0 < p.slab_pieces) ? p.pieces - p0 : p.slab_pieces;
-    a.piece0 = p0;
-#define CALL_BWD(T, G, H) launch_bwd<T, G, H>(a, np, st)
+  for (int i = 0; i <= p.pieces; i++) {
+    a.piece = i < p.pieces ? i : -1;
+    a.conv_piece = i - 1;
+    a.slab = slabs[i & 1];
+    a.conv_slab = slabs[(i & 1) ^ 1];
+#define CALL_BWD(T, G, H) launch_bwd<T, G, H>(a, st)
     e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_BWD);
 #undef CALL_BWD
     if (e != cudaSuccess) return fail((int)e, "backward launch failed: %s", cudaGetErrorString(e));
-#define CALL_CVT(T, G, H) launch_convert<T, G>(a.slab, dweight, (int)F, (int)D, p0, np, st)
-    e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_CVT);
-#undef CALL_CVT
-    if (e != cudaSuccess) return fail((int)e, "slab conversion launch failed: %s", cudaGetErrorString(e));
   }
   const size_t BK = (size_t)B * K;
   const int dv_blocks = (int)((BK + 255) / 256);
   const int db_blocks = (int)((D + 255) / 256);
-  grads_finalize_kernel<<<dv_blocks + db_blocks, 256, 0, st>>>(a.dv_part, p.pieces, BK, dvals, vals_dtype, a.db_part,
-                                                             p.tiles, (int)D, dbias, bias_dtype, dv_blocks);
+  grads_finalize_kernel<<<dv_blocks + db_blocks, 256, 0, st>>>(a.dv_part, p.pieces, BK, dvals, vals_dtype, db_part,
+                                                             p.row_blocks, (int)D, dbias, bias_dtype, dv_blocks,
+                                                             grad_out, a.scale);
   t_launches++;
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail((int)e, "gradient finalize launch failed: %s", cudaGetErrorString(e));

@@ -105,7 +105,7 @@ def check_status(device=None) -> None:
 
 
 def fused_forward(kind: int, indices, weight, vals, bias, target, inv_norm: float = 0.0):
-    """Runs the forward kernels; returns (loss 0-dim float32, resid [B,D] float32, prepared inputs)."""
+    """Runs the forward kernels; returns (loss 0-dim float32, (state, segments), prepared inputs)."""
     B, K, F, D = _validate(indices, weight, vals, bias, target)
     lib = nv.load()
     indices, weight, vals, bias, target = (_prep(t.detach()) for t in (indices, weight, vals, bias, target))
@@ -117,23 +117,25 @@ def fused_forward(kind: int, indices, weight, vals, bias, target, inv_norm: floa
             raise nv.FlexSaeNativeError("flexsae_loss_fwd: " + lib.flexsae_last_error().decode())
         ws = _workspace(dev, need)
         loss = torch.empty((), dtype=torch.float32, device=dev)
-        resid = torch.empty((B, D), dtype=torch.float32, device=dev)
+        segments = lib.flexsae_choose_segments(kind, B, K, F, D, wdt)
+        state = torch.empty(lib.flexsae_state_bytes(kind, B, K, D, segments) // 4, dtype=torch.float32, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
         rc = lib.flexsae_loss_fwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(bias), _ptr(target),
-                                  _ptr(loss), _ptr(resid), _ptr(ws), ws.numel(), B, K, F, D, wdt,
+                                  _ptr(loss), _ptr(state), segments, _ptr(ws), ws.numel(), B, K, F, D, wdt,
                                   nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias.dtype],
                                   nv.DTYPE_CODES[target.dtype], float(inv_norm), _ptr(_status_word(dev)), stream)
         nv.check(rc, "flexsae_loss_fwd")
     if config.check_indices:
         check_status(dev)
-    return loss, resid, (indices, weight, vals)
+    return loss, (state, segments), (indices, weight, vals)
 
 
-def fused_backward(kind: int, indices, weight, vals, resid, grad_out, bias_dtype, inv_norm: float = 0.0,
+def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype, inv_norm: float = 0.0,
                    dweight_mode: Optional[str] = None):
     """Runs the backward kernels; returns (dweight, dvals, dbias) in the parameters' dtypes."""
     B, K = indices.shape
     F, D = weight.shape
+    state, segments = saved
     lib = nv.load()
     dev = weight.device
     wdt = nv.DTYPE_CODES[weight.dtype]
@@ -148,7 +150,7 @@ def fused_backward(kind: int, indices, weight, vals, resid, grad_out, bias_dtype
         dvals = torch.empty((B, K), dtype=vals.dtype, device=dev)
         dbias = torch.empty((D,), dtype=bias_dtype, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        rc = lib.flexsae_loss_bwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(resid), _ptr(go),
+        rc = lib.flexsae_loss_bwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(state), segments, _ptr(go),
                                   _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(), B, K, F, D, wdt,
                                   nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype], float(inv_norm), mode,
                                   _ptr(_status_word(dev)), stream)
@@ -164,16 +166,17 @@ class _FusedDecoderLoss(torch.autograd.Function):
     @staticmethod
     @torch.amp.custom_fwd(device_type="cuda")
     def forward(ctx, kind, inv_norm, indices, weight, vals, bias, target):
-        loss, resid, (idx_c, w_c, v_c) = fused_forward(kind, indices, weight, vals, bias, target, inv_norm)
-        ctx.kind, ctx.inv_norm, ctx.bias_dtype = kind, inv_norm, bias.dtype
-        ctx.save_for_backward(idx_c, w_c, v_c, resid)
+        loss, (state, segments), (idx_c, w_c, v_c) = fused_forward(kind, indices, weight, vals, bias, target, inv_norm)
+        ctx.kind, ctx.inv_norm, ctx.bias_dtype, ctx.segments = kind, inv_norm, bias.dtype, segments
+        ctx.save_for_backward(idx_c, w_c, v_c, state)
         return loss
 
     @staticmethod
     @torch.amp.custom_bwd(device_type="cuda")
     def backward(ctx, grad):
-        idx_c, w_c, v_c, resid = ctx.saved_tensors
-        dweight, dvals, dbias = fused_backward(ctx.kind, idx_c, w_c, v_c, resid, grad, ctx.bias_dtype, ctx.inv_norm)
+        idx_c, w_c, v_c, state = ctx.saved_tensors
+        dweight, dvals, dbias = fused_backward(ctx.kind, idx_c, w_c, v_c, (state, ctx.segments), grad, ctx.bias_dtype,
+                                               ctx.inv_norm)
         return None, None, None, dweight, dvals, dbias, None
 
 

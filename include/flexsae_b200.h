@@ -58,12 +58,24 @@ const char* flexsae_last_error(void);
 
 /* Tuning knobs, process-wide: "lanes_fwd", "lanes_bwd" (8, 16, 32 lanes share one batch row;
  * 0 = choose so that one column slab of the decoder and of the fp32 gradient slab stay in L2),
- * "l2_budget_mb", "slab_pieces" (column pieces accumulated per backward launch).
+ * "l2_budget_mb" (working set one column piece may occupy), "segments"
+ * (what flexsae_choose_segments answers; 0 = derive from the shape).
  * Stands in for the literal tile constants at the reference's launch sites
  * (torch-ext/flex_sae/hierarchical_kernels.py:220-224,263-267; topk_kernels.py:64-66,181-183).
  * Returns 0, or FLEXSAE_EINVAL for an unknown name or value. */
 int flexsae_set_option(const char* name, int64_t value);
 int64_t flexsae_get_option(const char* name);
+
+/* The backward of one batch row can be cut into independent K-segments when the forward leaves
+ * the running state at each segment boundary; small batches need that to fill the GPU.
+ * flexsae_choose_segments answers how many segments to use for a shape (0 on invalid arguments);
+ * the same number must be given to the forward, the backward and flexsae_state_bytes, which
+ * answers the size of the float32 state buffer the forward writes for the backward:
+ * B*D floats (TopK) or 2*segments*B*D floats (Hierarchical).
+ * Stands in for final_recon[B,D] saved by the reference forward
+ * (torch-ext/flex_sae/hierarchical_kernels.py:201,285). */
+int flexsae_choose_segments(int kind, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype);
+size_t flexsae_state_bytes(int kind, int64_t B, int64_t K, int64_t D, int segments);
 
 /* Scratch bytes the forward / backward need for this shape (0 on invalid arguments).
  * Stands in for the torch.zeros / torch.empty temporaries the reference's launchers allocate
@@ -77,7 +89,9 @@ size_t flexsae_bwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, in
  * Forward of either loss.
  *   indices [B,K] int64, weight [F,D], vals [B,K], bias [D], target [B,D]
  *   loss_out   one float32: the loss, already divided by the normaliser
- *   resid_out  [B,D] float32: final reconstruction minus target, the state the backward starts from
+ *   state_out  flexsae_state_bytes() of float32: reconstruction minus target at the end of every
+ *              K-segment (and, Hierarchical, the running sum of those residuals over k)
+ *   segments   from flexsae_choose_segments (1 is always valid)
  *   inv_norm   1/(B*D) (TopK) or 1/(B*K*D) (Hierarchical); pass the GLOBAL batch size when B is
  *              one shard of a larger batch; <= 0 means "derive from B"
  *   status     optional int32 word, OR-ed with FLEXSAE_STATUS_* bits (may be NULL)
@@ -87,14 +101,14 @@ size_t flexsae_bwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, in
  *   bias/residual/square/mean tail (torch-ext/flex_sae/topk_kernels.py:15-68,220-222).
  */
 int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const void* vals,
-                     const void* bias, const void* target, float* loss_out, float* resid_out,
-                     void* workspace, size_t workspace_bytes, int64_t B, int64_t K, int64_t F,
-                     int64_t D, int weight_dtype, int vals_dtype, int bias_dtype, int target_dtype,
-                     double inv_norm, int32_t* status, void* stream);
+                     const void* bias, const void* target, float* loss_out, float* state_out,
+                     int segments, void* workspace, size_t workspace_bytes, int64_t B, int64_t K,
+                     int64_t F, int64_t D, int weight_dtype, int vals_dtype, int bias_dtype,
+                     int target_dtype, double inv_norm, int32_t* status, void* stream);
 
 /*
  * Backward of either loss.
- *   resid      [B,D] float32 written by flexsae_loss_fwd for the same inputs
+ *   state      what flexsae_loss_fwd wrote for the same inputs and the same `segments`
  *   grad_out   one float32 ON THE DEVICE: the upstream gradient of the scalar loss
  *   dweight    [F,D] in weight_dtype, fully overwritten (untouched rows become 0)
  *   dvals      [B,K] in vals_dtype, dbias [D] in bias_dtype, fully overwritten
@@ -105,10 +119,10 @@ int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const
  *   backward of the eager tail (torch-ext/flex_sae/topk_kernels.py:71-185,200-210,220-222).
  */
 int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const void* vals,
-                     const float* resid, const float* grad_out, void* dweight, void* dvals,
-                     void* dbias, void* workspace, size_t workspace_bytes, int64_t B, int64_t K,
-                     int64_t F, int64_t D, int weight_dtype, int vals_dtype, int bias_dtype,
-                     double inv_norm, int dw_mode, int32_t* status, void* stream);
+                     const float* state, int segments, const float* grad_out, void* dweight,
+                     void* dvals, void* dbias, void* workspace, size_t workspace_bytes, int64_t B,
+                     int64_t K, int64_t F, int64_t D, int weight_dtype, int vals_dtype,
+                     int bias_dtype, double inv_norm, int dw_mode, int32_t* status, void* stream);
 
 /* Number of kernels the last flexsae_loss_fwd / flexsae_loss_bwd call of this thread enqueued
  * (for launch accounting in benchmarks). No reference counterpart. */

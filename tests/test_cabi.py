@@ -56,9 +56,11 @@ def test_options_and_workspace_sizes_without_gpu():
     nv.set_option("lanes_bwd", 0)
     assert lib.flexsae_set_option(b"lanes_bwd", 5) != 0 and b"lanes_bwd" in lib.flexsae_last_error()
     assert lib.flexsae_set_option(b"no_such_option", 1) != 0
-    # headline shape: one [F, 256] fp32 slab + per-piece dvals partials + per-tile dbias partials
+    # headline shape: two [F, 256] fp32 slabs + per-piece dvals partials + dbias partial rows
+    nv.set_option("lanes_bwd", 32)
     n = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2304, nv.BF16, nv.DW_ATOMIC)
-    assert 65536 * 256 * 4 <= n <= 65536 * 256 * 4 + 9 * 4096 * 128 * 4 + 512 * 2304 * 4 + 4096
+    nv.set_option("lanes_bwd", 0)
+    assert 2 * 65536 * 256 * 4 <= n <= 2 * 65536 * 256 * 4 + 9 * 4096 * 128 * 4 + 512 * 2304 * 4 + 4096
     assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2304, nv.BF16) >= 9 * 4096 * 4
     # rejected shapes give 0 and an explanation
     assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2301, nv.BF16) == 0
@@ -68,9 +70,27 @@ def test_options_and_workspace_sizes_without_gpu():
 
 def test_null_pointers_are_rejected_before_any_launch():
     lib = nv.load()
-    rc = lib.flexsae_loss_fwd(nv.HIER, None, None, None, None, None, None, None, None, 0, 4, 4, 16, 256,
+    rc = lib.flexsae_loss_fwd(nv.HIER, None, None, None, None, None, None, None, 1, None, 0, 4, 4, 16, 256,
                               nv.F32, nv.F32, nv.F32, nv.F32, 0.0, None, None)
     assert rc == -1 and b"null" in lib.flexsae_last_error()
-    rc = lib.flexsae_loss_bwd(nv.HIER, None, None, None, None, None, None, None, None, None, 0, 4, 4, 16, 256,
+    rc = lib.flexsae_loss_bwd(nv.HIER, None, None, None, None, 1, None, None, None, None, None, 0, 4, 4, 16, 256,
                               nv.F32, nv.F32, nv.F32, 0.0, nv.DW_ATOMIC, None, None)
     assert rc == -1
+    # a segment count that is not a layout of K is refused (K=4 only has the one-segment layout)
+    rc = lib.flexsae_loss_fwd(nv.HIER, None, None, None, None, None, None, None, 3, None, 0, 4, 4, 16, 256,
+                              nv.F32, nv.F32, nv.F32, nv.F32, 0.0, None, None)
+    assert rc == -1 and b"segments" in lib.flexsae_last_error()
+
+
+def test_segment_layouts():
+    lib = nv.load()
+    nv.set_option("segments", 0)
+    # small batch: several segments so that one column piece fills the GPU; large batch: one
+    assert lib.flexsae_choose_segments(nv.HIER, 4096, 128, 65536, 2304, nv.BF16) >= 2
+    assert lib.flexsae_choose_segments(nv.HIER, 65536, 128, 131072, 4096, nv.BF16) == 1
+    assert lib.flexsae_choose_segments(nv.HIER, 8, 4, 16, 256, nv.F32) == 1      # K < 8: one segment
+    for K in (1, 8, 9, 100, 128, 300):
+        ns = lib.flexsae_choose_segments(nv.HIER, 64, K, 1024, 512, nv.F32)
+        assert 1 <= ns <= max(1, (K + 7) // 8)
+    assert lib.flexsae_state_bytes(nv.HIER, 10, 16, 256, 2) == 2 * 2 * 10 * 256 * 4
+    assert lib.flexsae_state_bytes(nv.TOPK, 10, 16, 256, 2) == 10 * 256 * 4

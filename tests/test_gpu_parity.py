@@ -42,9 +42,8 @@ def assert_close_to_oracle(got, want, tol, loss_tol=1e-5):
 
 @pytest.fixture(autouse=True)
 def _auto_options():
-    for name in ("lanes_fwd", "lanes_bwd"):
+    for name in ("lanes_fwd", "lanes_bwd", "segments"):
         nv.set_option(name, 0)
-    nv.set_option("slab_pieces", 1)
     yield
     fx.check_status()
 
@@ -80,12 +79,13 @@ def test_every_lane_group_width(name, kind, lanes):
     assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
 
 
-@pytest.mark.parametrize("slab_pieces", [2, 64])
-def test_several_pieces_per_backward_launch(slab_pieces):
-    path = [p for p in golden_files() if p.endswith("t16_64_128_1024_bfloat16__hier.npz")][0]
+@pytest.mark.parametrize("segments", [1, 2, 3, 8])
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("name", ["t16_64_128_1024_float32", "c1", "mixed_bf16w_f32v"])
+def test_every_segment_count(name, kind, segments):
+    path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
     w, kind, gold = load_golden(path)
-    nv.set_option("lanes_bwd", 8)
-    nv.set_option("slab_pieces", slab_pieces)
+    nv.set_option("segments", segments)
     x = make_inputs(w, "cpu")
     got = run_fused(kind, x)
     want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
