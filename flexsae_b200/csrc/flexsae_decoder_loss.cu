@@ -30,7 +30,7 @@ namespace flexsae {
 struct Options {
   int lanes_fwd = 0;      // 0 = auto
   int lanes_bwd = 0;      // 0 = auto
-  int l2_budget_mb = 96;  // bytes of one piece's decoder columns (+ fp32 slab) kept under this
+  int l2_budget_mb = 80;  // one piece of decoder columns (+ one fp32 slab) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
 };
 static Options g_opt;

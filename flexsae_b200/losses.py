@@ -24,6 +24,9 @@ from . import _native as nv
 
 _tls = threading.local()
 
+#: kernels enqueued by the fused losses since the counter was last reset (benchmark accounting)
+launch_count = 0
+
 
 class config:
     """Process-wide switches of the fused losses."""
@@ -125,6 +128,8 @@ def fused_forward(kind: int, indices, weight, vals, bias, target, inv_norm: floa
                                   nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias.dtype],
                                   nv.DTYPE_CODES[target.dtype], float(inv_norm), _ptr(_status_word(dev)), stream)
         nv.check(rc, "flexsae_loss_fwd")
+        global launch_count
+        launch_count += lib.flexsae_last_launch_count()
     if config.check_indices:
         check_status(dev)
     return loss, (state, segments), (indices, weight, vals)
@@ -155,6 +160,8 @@ def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype
                                   nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype], float(inv_norm), mode,
                                   _ptr(_status_word(dev)), stream)
         nv.check(rc, "flexsae_loss_bwd")
+        global launch_count
+        launch_count += lib.flexsae_last_launch_count()
     return dweight, dvals, dbias
 
 
