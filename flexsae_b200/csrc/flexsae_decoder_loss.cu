@@ -19,6 +19,8 @@
 // and, with the prefix removed, embedding_bag_forward_kernel and the TopK gradient
 // (torch-ext/flex_sae/topk_kernels.py:15-41,97-137).
 #include <stdarg.h>
+
+#include <mutex>
 #include <stdio.h>
 #include <string.h>
 
@@ -794,6 +796,53 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail((int)e, "gradient finalize launch failed: %s", cudaGetErrorString(e));
   return 0;
+}
+
+// ---- forward for callers that cannot provide scratch memory ------------------------------------
+// The per-(piece, row) partial losses of the forward normally live in caller memory.  Here they
+// live in a fixed array inside the library image: every GPU that loads the library carries these
+// bytes until the process exits.
+#define FLEXSAE_STATIC_PARTIALS (1u << 18) /* floats: 1 MiB */
+static __device__ __align__(256) float g_static_loss_partials[FLEXSAE_STATIC_PARTIALS];
+
+static std::mutex g_static_mutex;
+static float* g_static_partials_addr[64];  // device ordinal -> device address of the array above
+
+int flexsae_loss_fwd_static_scratch(int kind, const int64_t* indices, const void* weight, const void* vals,
+                                    const void* bias, const void* target, float* loss_out, float* state_out,
+                                    int segments, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
+                                    int vals_dtype, int bias_dtype, int target_dtype, double inv_norm,
+                                    int32_t* status, void* stream) {
+  Shape s{B, K, F, D};
+  if (int rc = check_shape(kind, s, weight_dtype)) return rc;
+  const size_t need = plan_fwd(s, weight_dtype).total;
+  const size_t have = sizeof(float) * FLEXSAE_STATIC_PARTIALS;
+  if (need > have)
+    return fail(FLEXSAE_EUNSUPPORTED,
+                "the built-in scratch holds %zu bytes but this shape needs %zu (column pieces x B = %lld partial "
+                "sums; at most %u): use flexsae_loss_fwd with caller memory",
+                have, need, (long long)(need / sizeof(float)), (unsigned)FLEXSAE_STATIC_PARTIALS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail((int)e, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(FLEXSAE_EUNSUPPORTED, "device ordinal %d outside [0, 64)", dev);
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_partials_addr[dev]) {
+      // In host code the array's name is only a handle; the address the kernels need is asked
+      // from the runtime once per device, with that device current.
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_loss_partials);
+      if (e != cudaSuccess) return fail((int)e, "cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      g_static_partials_addr[dev] = reinterpret_cast<float*>(p);
+    }
+    scratch = g_static_partials_addr[dev];
+  }
+  // Every partial the final sum reads is written by this call's forward kernel first, so nothing
+  // left over from an earlier call is ever read and nothing needs clearing.
+  return flexsae_loss_fwd(kind, indices, weight, vals, bias, target, loss_out, state_out, segments, scratch, have, B, K,
+                          F, D, weight_dtype, vals_dtype, bias_dtype, target_dtype, inv_norm, status, stream);
 }
 
 }  // extern "C"

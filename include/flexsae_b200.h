@@ -124,6 +124,41 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
                      int64_t K, int64_t F, int64_t D, int weight_dtype, int vals_dtype,
                      int bias_dtype, double inv_norm, int dw_mode, int32_t* status, void* stream);
 
+/*
+ * flexsae_loss_fwd for callers that must not allocate device memory.  It has no counterpart in
+ * the reference (whose launchers allocate with torch on every call).
+ *
+ * Who needs it: code that runs where cudaMalloc is off limits -- a plug-in whose host
+ * application owns every device allocation and hands the plug-in only its inputs and outputs, a
+ * process whose memory pool was given out in full at start-up, a latency-critical loop in which
+ * the implicit synchronisation of an allocation is not acceptable, or a host callback running on
+ * a thread where CUDA allocation calls are not permitted.  Such
+ * a caller has nowhere to get the forward's scratch buffer from, so this variant keeps that
+ * scratch (the per-(column piece, row) partial losses) in a fixed 1 MiB array that is part of the
+ * library image.  Inputs and outputs are still the caller's.
+ *
+ *  - Limit: column pieces x B <= 262144 partial sums, i.e. flexsae_fwd_workspace_bytes(...) <=
+ *    1 MiB (the headline shape needs 9 x 4096 = 36864).  Larger shapes are refused with
+ *    FLEXSAE_EUNSUPPORTED and a message that states both sizes.
+ *  - Cost: each GPU that loads the library holds the 1 MiB until the process exits.
+ *  - The first call on a device looks the array's device address up (cudaGetSymbolAddress, with
+ *    that device current, result cached per device ordinal).  Make that first call during set-up,
+ *    before any stream capture begins.  The device that is current at the call must be the one
+ *    the tensors and the stream belong to.
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - All calls on one device share the array, and it keeps whatever the last call left there.
+ *    Nothing has to be cleared: the kernel writes every partial before the final sum reads it.
+ *    Two calls whose kernels overlap on the same GPU (different streams, no ordering between
+ *    them) race on the array and give wrong losses; order them.
+ * Arguments and result are those of flexsae_loss_fwd without workspace / workspace_bytes.
+ */
+int flexsae_loss_fwd_static_scratch(int kind, const int64_t* indices, const void* weight,
+                                    const void* vals, const void* bias, const void* target,
+                                    float* loss_out, float* state_out, int segments, int64_t B,
+                                    int64_t K, int64_t F, int64_t D, int weight_dtype,
+                                    int vals_dtype, int bias_dtype, int target_dtype,
+                                    double inv_norm, int32_t* status, void* stream);
+
 /* Number of kernels the last flexsae_loss_fwd / flexsae_loss_bwd call of this thread enqueued
  * (for launch accounting in benchmarks). No reference counterpart. */
 int flexsae_last_launch_count(void);
