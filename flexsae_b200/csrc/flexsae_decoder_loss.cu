@@ -25,6 +25,7 @@
 #include <string.h>
 
 #include "flexsae_common.cuh"
+#include "flexsae_deterministic.cuh"
 
 namespace flexsae {
 
@@ -93,6 +94,8 @@ struct BwdArgs {
   float* conv_slab;       // the other slab: finished piece `conv_piece`, converted by trailing CTAs
   void* dweight;          // [F, D] in the decoder's storage type
   float* dv_part;         // [pieces, B, K]
+  float* stage;           // deterministic mode: [B*K, PW] contribution rows in sorted-slot order
+  const int* slot_of;     // deterministic mode: [B*K] sorted slot of each (b, k)
   int32_t* status;
   int B, K, F, D;
   int vals_dtype;
@@ -311,14 +314,14 @@ __device__ __forceinline__ void convert_slab(float* __restrict__ slab, void* __r
 // One lane group owns one (batch row, K-segment) unit and walks the segment from its last k
 // down to its first: suffix += residual; dweight[idx] += vals * suffix; dvals = <row, suffix>;
 // residual -= vals * row  (the reverse walk of hierarchical_kernels.py:147-173).
-template <typename T, int G, bool HIER>
+template <typename T, int G, bool HIER, bool DET>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_kernel(const BwdArgs a) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
   constexpr int UPC = groups_per_cta(G);
   constexpr int U = kUnroll;
-  extern __shared__ int2 staged[];  // [UPC][KS]
-  if ((int)blockIdx.x >= a.unit_blocks) {
+  extern __shared__ int2 staged[];  // [UPC][KS], then (deterministic mode) int slots[UPC][KS]
+  if (!DET && (int)blockIdx.x >= a.unit_blocks) {
     convert_slab<T, G>(a.conv_slab, a.dweight, a.F, a.D, a.conv_piece, blockIdx.x - a.unit_blocks,
                        gridDim.x - a.unit_blocks);
     return;
@@ -332,12 +335,17 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
     const int j = i - lu * KS;
     const int u = unit0 + lu;
     int2 e = make_int2(0, 0);
+    int slot = 0;
     if (u < nunits) {
       const int row = u / NS;
       const int k = (u - row * NS) * KS + j;
-      if (k < K) e = stage_pair(a.indices, a.vals, a.vals_dtype, (size_t)row * K + k, a.F, a.status);
+      if (k < K) {
+        e = stage_pair(a.indices, a.vals, a.vals_dtype, (size_t)row * K + k, a.F, a.status);
+        if (DET) slot = a.slot_of[(size_t)row * K + k];
+      }
     }
     staged[i] = e;
+    if (DET) reinterpret_cast<int*>(staged + UPC * KS)[i] = slot;
   }
   __syncthreads();
 
@@ -375,6 +383,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
   const char* wcol = reinterpret_cast<const char*>(a.weight) + (size_t)col * sizeof(T);
   const size_t row_bytes = (size_t)a.D * sizeof(T);
   const int2* mine = staged + gid * KS;
+  const int* myslot = reinterpret_cast<const int*>(staged + UPC * KS) + gid * KS;
   float* slab = a.slab + lig * 4;
   float* dv = a.dv_part + ((size_t)piece * a.B + row) * K + k_first;
 
@@ -400,9 +409,15 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
         for (int j = 0; j < VEC; j++) suf[j] += r[j];  // S_k = sum_{j>=k} residual_j
       }
       if (active && in_seg) {
-        float* dst = slab + (size_t)e[u].x * PW;
-        red_add_v4(dst, suf[0] * c, suf[1] * c, suf[2] * c, suf[3] * c);
-        if (VEC == 8) red_add_v4(dst + G * 4, suf[VEC - 4] * c, suf[VEC - 3] * c, suf[VEC - 2] * c, suf[VEC - 1] * c);
+        if (DET) {  // the contribution row goes to its sorted slot; it is added later, in slot order
+          float4* dst = reinterpret_cast<float4*>(a.stage + (size_t)myslot[jb - u] * PW + lig * VEC);
+          __stcs(dst, make_float4(suf[0] * c, suf[1] * c, suf[2] * c, suf[3] * c));
+          if (VEC == 8) __stcs(dst + 1, make_float4(suf[VEC - 4] * c, suf[VEC - 3] * c, suf[VEC - 2] * c, suf[VEC - 1] * c));
+        } else {
+          float* dst = slab + (size_t)e[u].x * PW;
+          red_add_v4(dst, suf[0] * c, suf[1] * c, suf[2] * c, suf[3] * c);
+          if (VEC == 8) red_add_v4(dst + G * 4, suf[VEC - 4] * c, suf[VEC - 3] * c, suf[VEC - 2] * c, suf[VEC - 1] * c);
+        }
       }
       float dot = 0.f;
 #pragma unroll
@@ -537,10 +552,10 @@ constexpr int kConvertBlocks = 148 * 3;  // trailing CTAs that convert the previ
 
 struct BwdPlan {
   int G, PW, pieces, row_blocks, rows_per_block;
-  size_t slab_bytes, off_slab, off_dv, off_db, total;
+  size_t slab_bytes, off_slab, off_dv, off_db, off_index, off_stage, off_part, total;
 };
 
-static BwdPlan plan_bwd(const Shape& s, int wdt) {
+static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   BwdPlan p;
   const int vec = 16 / (int)dtype_size(wdt);
   p.G = choose_lanes(s.F, wdt, true, g_opt.lanes_bwd);
@@ -551,8 +566,17 @@ static BwdPlan plan_bwd(const Shape& s, int wdt) {
   p.row_blocks = (int)((s.B + p.rows_per_block - 1) / p.rows_per_block);
   size_t off = 0;
   p.off_slab = off;  // two slabs: one accumulating, one being converted
-  p.slab_bytes = align_up((size_t)s.F * p.PW * 4, 256);
+  p.slab_bytes = dw_mode == FLEXSAE_DW_ATOMIC ? align_up((size_t)s.F * p.PW * 4, 256) : 0;
   off += 2 * p.slab_bytes;
+  p.off_index = p.off_stage = p.off_part = off;
+  if (dw_mode == FLEXSAE_DW_DETERMINISTIC) {
+    const int64_t n = s.B * s.K;
+    off += det_index_bytes(n, s.F);
+    p.off_stage = off;
+    off = align_up(off + (size_t)n * p.PW * 4, 256);
+    p.off_part = off;
+    off = align_up(off + det_part_rows(n, s.F) * p.PW * 4, 256);
+  }
   p.off_dv = off;
   off = align_up(off + (size_t)p.pieces * s.B * s.K * 4, 256);
   p.off_db = off;
@@ -595,10 +619,23 @@ static cudaError_t launch_fwd(const FwdArgs& a, int pieces, cudaStream_t st) {
 }
 
 template <typename T, int G, bool HIER>
+static cudaError_t launch_bwd_det(BwdArgs a, cudaStream_t st) {
+  constexpr int UPC = groups_per_cta(G);
+  const size_t smem = (size_t)UPC * a.KS * (sizeof(int2) + sizeof(int));
+  auto kern = decoder_loss_bwd_kernel<T, G, HIER, true>;
+  if (cudaError_t e = allow_smem(kern, smem)) return e;
+  const long long units = (long long)a.B * a.NS;
+  a.unit_blocks = (int)((units + UPC - 1) / UPC);
+  kern<<<a.unit_blocks, kThreads, smem, st>>>(a);
+  t_launches++;
+  return cudaGetLastError();
+}
+
+template <typename T, int G, bool HIER>
 static cudaError_t launch_bwd(BwdArgs a, cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
   const size_t smem = (size_t)UPC * a.KS * sizeof(int2);
-  auto kern = decoder_loss_bwd_kernel<T, G, HIER>;
+  auto kern = decoder_loss_bwd_kernel<T, G, HIER, false>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   const long long units = (long long)a.B * a.NS;
   a.unit_blocks = a.piece >= 0 ? (int)((units + UPC - 1) / UPC) : 0;
@@ -678,11 +715,11 @@ size_t flexsae_fwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, in
 size_t flexsae_bwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype, int dw_mode) {
   Shape s{B, K, F, D};
   if (check_shape(kind, s, weight_dtype)) return 0;
-  if (dw_mode != FLEXSAE_DW_ATOMIC) {
-    fail(FLEXSAE_EUNSUPPORTED, "dweight mode %d is not available", dw_mode);
+  if (dw_mode != FLEXSAE_DW_ATOMIC && dw_mode != FLEXSAE_DW_DETERMINISTIC) {
+    fail(FLEXSAE_EINVAL, "unknown dweight mode %d", dw_mode);
     return 0;
   }
-  return plan_bwd(s, weight_dtype).total;
+  return plan_bwd(s, weight_dtype, dw_mode).total;
 }
 
 int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const void* vals, const void* bias,
@@ -735,15 +772,15 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   if (int rc = check_shape(kind, s, weight_dtype)) return rc;
   if (!dtype_ok(vals_dtype) || !dtype_ok(bias_dtype))
     return fail(FLEXSAE_EINVAL, "unknown dtype code (vals %d, bias %d)", vals_dtype, bias_dtype);
-  if (dw_mode != FLEXSAE_DW_ATOMIC)
-    return fail(FLEXSAE_EUNSUPPORTED, "dweight mode %d is not available", dw_mode);
+  if (dw_mode != FLEXSAE_DW_ATOMIC && dw_mode != FLEXSAE_DW_DETERMINISTIC)
+    return fail(FLEXSAE_EINVAL, "unknown dweight mode %d", dw_mode);
   int KS, NS;
   if (int rc = check_segments(kind, s, segments, &KS, &NS)) return rc;
   if (!indices || !weight || !vals || !state || !grad_out || !dweight || !dvals || !dbias || !workspace)
     return fail(FLEXSAE_EINVAL, "null pointer argument");
   if (!aligned16(weight) || !aligned16(state) || !aligned16(dweight) || !aligned16(workspace))
     return fail(FLEXSAE_EINVAL, "weight, state, dweight and workspace must be 16-byte aligned");
-  const BwdPlan p = plan_bwd(s, weight_dtype);
+  const BwdPlan p = plan_bwd(s, weight_dtype, dw_mode);
   if (workspace_bytes < p.total)
     return fail(FLEXSAE_EWORKSPACE, "backward workspace too small: %zu < %zu bytes", workspace_bytes, p.total);
   if (inv_norm <= 0.0) inv_norm = 1.0 / ((double)B * (double)D * (kind == FLEXSAE_HIER ? (double)K : 1.0));
@@ -754,6 +791,8 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   a.indices = indices; a.weight = weight; a.vals = vals; a.state = state; a.grad_out = grad_out;
   float* slabs[2] = {reinterpret_cast<float*>(ws + p.off_slab), reinterpret_cast<float*>(ws + p.off_slab + p.slab_bytes)};
   a.dweight = dweight;
+  a.stage = nullptr;
+  a.slot_of = nullptr;
   a.dv_part = reinterpret_cast<float*>(ws + p.off_dv);
   a.status = status;
   a.B = (int)B; a.K = (int)K; a.F = (int)F; a.D = (int)D;
@@ -771,6 +810,28 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail((int)e, "column sums launch failed: %s", cudaGetErrorString(e));
 
+  if (dw_mode == FLEXSAE_DW_DETERMINISTIC) {
+    // Sort the (decoder row, position) pairs once; then per column piece: the same reverse walk,
+    // but every contribution row is stored to its sorted slot, and the rows of each decoder row
+    // are added in slot order straight into dweight.
+    DetIndex ix;
+    e = det_prepare(indices, B * K, F, ws + p.off_index, &ix, st, &t_launches);
+    if (e != cudaSuccess) return fail((int)e, "sort launches failed: %s", cudaGetErrorString(e));
+    a.stage = reinterpret_cast<float*>(ws + p.off_stage);
+    a.slot_of = ix.slot_of;
+    a.slab = a.conv_slab = nullptr;
+    a.conv_piece = -1;
+    float* part = reinterpret_cast<float*>(ws + p.off_part);
+    for (int i = 0; i < p.pieces; i++) {
+      a.piece = i;
+#define CALL_DET(T, G, H) launch_bwd_det<T, G, H>(a, st)
+      e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_DET);
+#undef CALL_DET
+      if (e != cudaSuccess) return fail((int)e, "backward launch failed: %s", cudaGetErrorString(e));
+      e = det_reduce_piece(weight_dtype, p.G, a.stage, ix, (int)F, (int)D, i, part, dweight, st, &t_launches);
+      if (e != cudaSuccess) return fail((int)e, "ordered sum launch failed: %s", cudaGetErrorString(e));
+    }
+  } else {
   // Both slabs are cleared once here; afterwards every conversion leaves its slab cleared.
   // Launch i accumulates piece i into slab i%2 and converts piece i-1 out of the other slab;
   // one more launch converts the last piece.
@@ -785,6 +846,7 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
     e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_BWD);
 #undef CALL_BWD
     if (e != cudaSuccess) return fail((int)e, "backward launch failed: %s", cudaGetErrorString(e));
+  }
   }
   const size_t BK = (size_t)B * K;
   const int dv_blocks = (int)((BK + 255) / 256);

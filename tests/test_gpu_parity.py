@@ -20,9 +20,9 @@ TIGHT = {"float32": 2e-5, "bfloat16": 6e-3, "float16": 8e-4}   # 16-bit: one rou
 
 def run_fused(kind, x, dev="cuda", grad_out=None):
     idx = x["indices"].to(dev)
-    w = x["weight"].to(dev).requires_grad_(True)
-    v = x["vals"].to(dev).requires_grad_(True)
-    b = x["bias"].to(dev).requires_grad_(True)
+    w = x["weight"].to(dev).detach().clone().requires_grad_(True)
+    v = x["vals"].to(dev).detach().clone().requires_grad_(True)
+    b = x["bias"].to(dev).detach().clone().requires_grad_(True)
     t = x["target"].to(dev)
     loss = FUSED[kind](idx, w, v, b, t)
     go = x["grad_out"] if grad_out is None else grad_out
@@ -229,3 +229,68 @@ def test_rejected_arguments():
     with pytest.raises(nv.FlexSaeNativeError):     # D not a multiple of the 16-byte row piece
         fx.triton_topk_sae_loss(x["indices"], x["weight"][:, :254].contiguous(), x["vals"], x["bias"][:254].contiguous(),
                                 x["target"][:, :254].contiguous())
+
+
+# ---- deterministic dweight mode -----------------------------------------------------------------------
+@pytest.fixture
+def deterministic_mode():
+    fx.config.dweight_mode = "deterministic"
+    yield
+    fx.config.dweight_mode = "atomic"
+
+
+@pytest.mark.parametrize("path", golden_files(), ids=lambda p: p.split("/")[-1][:-4])
+def test_deterministic_mode_matches_oracle(path, deterministic_mode):
+    w, kind, gold = load_golden(path)
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+
+
+DET_CASES = [
+    Workload("det_uniform", B=512, K=64, F=4096, D=768, weight_dtype="bfloat16", indices="distinct", sort_vals=True,
+             normalise_weight=True, seed=51),
+    # a few decoder rows receive thousands of contributions: segments far longer than one 32-slot item
+    Workload("det_zipf", B=2048, K=32, F=512, D=512, weight_dtype="bfloat16", indices="zipf", sort_vals=True,
+             normalise_weight=True, seed=52),
+    Workload("det_one_row_table", B=300, K=8, F=1, D=256, indices="dup", seed=53),     # every pair hits row 0
+    Workload("det_f32_wide_table", B=64, K=16, F=70000, D=128, indices="dup", seed=54),  # three radix passes not needed, 17 bits
+]
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("w", DET_CASES, ids=lambda w: w.name)
+def test_deterministic_mode_is_bitwise_reproducible_and_right(w, kind, deterministic_mode):
+    x = make_inputs(w, "cuda")
+    runs = []
+    for _ in range(3):
+        wt = x["weight"].clone().requires_grad_(True)
+        v = x["vals"].clone().requires_grad_(True)
+        b = x["bias"].clone().requires_grad_(True)
+        loss = FUSED[kind](x["indices"], wt, v, b, x["target"])
+        loss.backward(x["grad_out"])
+        runs.append((loss.detach().clone(), wt.grad.clone(), v.grad.clone(), b.grad.clone()))
+    for r in runs[1:]:
+        for a, b_ in zip(runs[0], r):
+            assert torch.equal(a, b_)            # bit for bit, run to run
+    ref = tref.chunked_loss_and_grads(kind, x["indices"], x["weight"], x["vals"], x["bias"], x["target"],
+                                      grad_out=float(x["grad_out"]), chunk_rows=256, upcast=True)
+    assert abs(float(runs[0][0]) - ref["loss"]) <= 1e-5 * abs(ref["loss"])
+    for got, name in zip(runs[0][1:], ("dweight", "dvals", "dbias")):
+        assert rel_err(got.float().cpu().numpy(), ref[name].float().cpu().numpy()) < TIGHT[w.weight_dtype], name
+
+
+def test_atomic_and_deterministic_modes_agree():
+    w = CONFIGS["c3_k32"].replace(B=1024, F=16384)
+    x = make_inputs(w, "cuda")
+    out = {}
+    for mode in ("atomic", "deterministic"):
+        fx.config.dweight_mode = mode
+        try:
+            out[mode] = run_fused("hier", x)
+        finally:
+            fx.config.dweight_mode = "atomic"
+    assert out["atomic"]["loss"] == out["deterministic"]["loss"]
+    assert np.array_equal(out["atomic"]["dvals"], out["deterministic"]["dvals"])
+    assert rel_err(out["atomic"]["dweight"], out["deterministic"]["dweight"]) < 6e-3   # one bf16 rounding apart at most
