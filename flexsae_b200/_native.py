@@ -16,6 +16,7 @@ F32, BF16, F16 = 0, 1, 2
 TOPK, HIER = 0, 1
 DW_ATOMIC, DW_DETERMINISTIC = 0, 1
 STATUS_BAD_INDEX = 1
+STATUS_PIPELINE_TIMEOUT = 2
 
 DTYPE_CODES = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 

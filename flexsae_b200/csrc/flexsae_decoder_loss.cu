@@ -35,6 +35,8 @@ struct Options {
   int lanes_bwd = 0;      // 0 = auto
   int l2_budget_mb = 80;  // one piece of decoder columns (+ one fp32 slab) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
+  int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
+  int convert_offset_pct = 25;  // where, inside a piece's unit blocks, the previous piece's converters sit
 };
 static Options g_opt;
 
@@ -101,7 +103,9 @@ struct BwdArgs {
   int vals_dtype;
   int piece;       // column piece accumulated by this launch (-1: none, conversion only)
   int conv_piece;  // column piece converted by this launch (-1: none)
-  int unit_blocks; // CTAs [0, unit_blocks) walk (row, segment) units, the rest convert
+  int unit_blocks; // CTAs that walk (row, segment) units
+  int conv_blocks; // CTAs that convert; every conv_stride-th CTA of the grid until all are placed
+  int conv_stride;
   float scale;     // 2 * inv_norm
   int KS, NS;
 };
@@ -266,8 +270,8 @@ __device__ __forceinline__ float group_sum8(const float* d, int lig) {
 // fp32 slab -> the dweight columns of one piece in the decoder's storage type; clears the slab.
 // Run by the trailing CTAs of the launch that accumulates the NEXT piece into the other slab,
 // so the conversion streams through L2 while the atomic units are busy with that piece.
-template <typename T, int G>
-__device__ __forceinline__ void convert_slab(float* __restrict__ slab, void* __restrict__ dweight, int F, int D, int piece,
+template <typename T, int G, bool L2_ONLY>
+__device__ __forceinline__ void convert_slab(float* slab, void* __restrict__ dweight, int F, int D, int piece,
                                              int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
@@ -282,8 +286,11 @@ __device__ __forceinline__ void convert_slab(float* __restrict__ slab, void* __r
       const size_t i = base + q * stride;
       if (i < total) {
         float* s = slab + (i / G) * PW + (i % G) * 4;
-        lo[q] = *reinterpret_cast<const float4*>(s);
-        if (VEC == 8) hi[q] = *reinterpret_cast<const float4*>(s + G * 4);
+        // inside the single-launch pipeline the slab was last written by L2 atomics of the same
+        // launch: read it at L2 (ld.cg), never through a possibly stale L1 line
+        lo[q] = L2_ONLY ? __ldcg(reinterpret_cast<const float4*>(s)) : *reinterpret_cast<const float4*>(s);
+        if (VEC == 8)
+          hi[q] = L2_ONLY ? __ldcg(reinterpret_cast<const float4*>(s + G * 4)) : *reinterpret_cast<const float4*>(s + G * 4);
       }
     }
 #pragma unroll
@@ -315,21 +322,14 @@ __device__ __forceinline__ void convert_slab(float* __restrict__ slab, void* __r
 // down to its first: suffix += residual; dweight[idx] += vals * suffix; dvals = <row, suffix>;
 // residual -= vals * row  (the reverse walk of hierarchical_kernels.py:147-173).
 template <typename T, int G, bool HIER, bool DET>
-__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_kernel(const BwdArgs a) {
+__device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int piece, float* slab_base, int2* staged) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
   constexpr int UPC = groups_per_cta(G);
   constexpr int U = kUnroll;
-  extern __shared__ int2 staged[];  // [UPC][KS], then (deterministic mode) int slots[UPC][KS]
-  if (!DET && (int)blockIdx.x >= a.unit_blocks) {
-    convert_slab<T, G>(a.conv_slab, a.dweight, a.F, a.D, a.conv_piece, blockIdx.x - a.unit_blocks,
-                       gridDim.x - a.unit_blocks);
-    return;
-  }
   const int K = a.K, KS = a.KS, NS = a.NS;
-  const int unit0 = blockIdx.x * UPC;
+  const int unit0 = unit_block * UPC;
   const int nunits = a.B * NS;
-  const int piece = a.piece;
   for (int i = threadIdx.x; i < UPC * KS; i += kThreads) {
     const int lu = i / KS;
     const int j = i - lu * KS;
@@ -384,7 +384,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
   const size_t row_bytes = (size_t)a.D * sizeof(T);
   const int2* mine = staged + gid * KS;
   const int* myslot = reinterpret_cast<const int*>(staged + UPC * KS) + gid * KS;
-  float* slab = a.slab + lig * 4;
+  float* slab = slab_base + lig * 4;
   float* dv = a.dv_part + ((size_t)piece * a.B + row) * K + k_first;
 
   for (int jb = KS - 1; jb >= 0; jb -= U) {  // KS is a multiple of U
@@ -432,6 +432,102 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
     const int j = jb - (lig & 7);
     if (live && lig < 8 && j < n) dv[j] = tot * coef;
   }
+}
+
+// Multi-launch form: one launch per column piece; converting CTAs for the previous piece are
+// spread evenly through the grid.
+template <typename T, int G, bool HIER, bool DET>
+__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_kernel(const BwdArgs a) {
+  extern __shared__ int2 staged[];  // [UPC][KS], then (deterministic mode) int slots[UPC][KS]
+  int unit_block = blockIdx.x;
+  if (!DET && a.conv_blocks > 0) {
+    const int q = blockIdx.x / a.conv_stride;
+    if (q < a.conv_blocks && (int)blockIdx.x - q * a.conv_stride == a.conv_stride - 1) {
+      convert_slab<T, G, false>(a.conv_slab, a.dweight, a.F, a.D, a.conv_piece, q, a.conv_blocks);
+      return;
+    }
+    unit_block = blockIdx.x - min(q, a.conv_blocks);
+  }
+  walk_units<T, G, HIER, DET>(a, unit_block, a.piece, a.slab, staged);
+}
+
+// ---- single-launch pipelined backward ------------------------------------------------------------
+// All column pieces in ONE grid, ordered piece by piece.  Piece p's blocks are its unit blocks
+// with the blocks that convert piece p-1 inserted after the first quarter.  Two counters per
+// piece carry the only dependencies:
+//   converting blocks of piece q wait until all unit blocks of piece q have finished;
+//   unit blocks of piece p wait until piece p-2 (same slab) has been converted and cleared.
+// Every wait is on blocks with LOWER block indices, which the hardware dispatches first, so the
+// lowest unfinished block never waits on anything unfinished.  Waits are bounded: after
+// kSpinLimit polls a block gives up, sets FLEXSAE_STATUS_PIPELINE_TIMEOUT and carries on (the
+// result is then invalid but the GPU is not held).
+struct PipeArgs {
+  BwdArgs b;
+  float* slabs[2];
+  int* walk_done;  // [pieces]
+  int* conv_done;  // [pieces]
+  int pieces, unit_blocks, conv_blocks, conv_offset;
+};
+
+constexpr int kSpinLimit = 1000000;  // polls of >= 0.2 us each: a fraction of a second
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void wait_count(const int* ctr, int target, int32_t* status) {
+  if (threadIdx.x == 0) {
+    int spins = 0;
+    while (ld_acquire(ctr) < target) {
+      __nanosleep(200);
+      ++spins;
+      // once any block has given up, nobody waits any more: the launch drains quickly
+      const bool abandoned = status && (spins & 1023) == 0 &&
+                             (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+      if (spins > kSpinLimit || abandoned) {
+        if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ void signal_done(int* ctr) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();  // this block's reductions / stores are visible before the count moves
+    atomicAdd(ctr, 1);
+  }
+}
+
+template <typename T, int G, bool HIER>
+__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_pipelined_kernel(const PipeArgs pa) {
+  extern __shared__ int2 staged[];
+  const int per = pa.unit_blocks + pa.conv_blocks;
+  const int p = blockIdx.x / per;
+  const int r = blockIdx.x - p * per;
+  int conv_idx = -1, unit_block = -1;
+  if (p == pa.pieces) {
+    conv_idx = r;  // the trailing blocks convert the last piece
+  } else if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) {
+    conv_idx = r - pa.conv_offset;
+  } else {
+    unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
+  }
+  if (conv_idx >= 0) {
+    const int q = p - 1;
+    if (q < 0) return;
+    wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status);
+    convert_slab<T, G, true>(pa.slabs[q & 1], pa.b.dweight, pa.b.F, pa.b.D, q, conv_idx, pa.conv_blocks);
+    signal_done(pa.conv_done + q);
+    return;
+  }
+  if (p >= 2) wait_count(pa.conv_done + (p - 2), pa.conv_blocks, pa.b.status);
+  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], staged);
+  signal_done(pa.walk_done + p);
 }
 
 // Column sums of a [B, D] fp32 matrix over row blocks: part[rb][d] = sum of rows of block rb.
@@ -552,7 +648,7 @@ constexpr int kConvertBlocks = 148 * 3;  // trailing CTAs that convert the previ
 
 struct BwdPlan {
   int G, PW, pieces, row_blocks, rows_per_block;
-  size_t slab_bytes, off_slab, off_dv, off_db, off_index, off_stage, off_part, total;
+  size_t slab_bytes, off_slab, off_dv, off_db, off_ctr, off_index, off_stage, off_part, total;
 };
 
 static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
@@ -581,6 +677,8 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   off = align_up(off + (size_t)p.pieces * s.B * s.K * 4, 256);
   p.off_db = off;
   off = align_up(off + (size_t)p.row_blocks * s.D * 4, 256);
+  p.off_ctr = off;  // per-piece completion counters of the single-launch pipeline
+  off = align_up(off + (size_t)2 * p.pieces * 4, 256);
   p.total = off;
   return p;
 }
@@ -626,6 +724,8 @@ static cudaError_t launch_bwd_det(BwdArgs a, cudaStream_t st) {
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   const long long units = (long long)a.B * a.NS;
   a.unit_blocks = (int)((units + UPC - 1) / UPC);
+  a.conv_blocks = 0;
+  a.conv_stride = 1;
   kern<<<a.unit_blocks, kThreads, smem, st>>>(a);
   t_launches++;
   return cudaGetLastError();
@@ -646,7 +746,37 @@ static cudaError_t launch_bwd(BwdArgs a, cudaStream_t st) {
     const int cap = a.piece >= 0 ? kConvertBlocks : kConvertBlocks * 4;
     if (conv_blocks > cap) conv_blocks = cap;
   }
+  a.conv_blocks = conv_blocks;
+  a.conv_stride = conv_blocks > 0 ? (a.unit_blocks + conv_blocks) / conv_blocks : 1;
   kern<<<a.unit_blocks + conv_blocks, kThreads, smem, st>>>(a);
+  t_launches++;
+  return cudaGetLastError();
+}
+
+template <typename T, int G, bool HIER>
+static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
+                                        cudaStream_t st) {
+  constexpr int UPC = groups_per_cta(G);
+  const size_t smem = (size_t)UPC * b.KS * sizeof(int2);
+  auto kern = decoder_loss_bwd_pipelined_kernel<T, G, HIER>;
+  if (cudaError_t e = allow_smem(kern, smem)) return e;
+  PipeArgs pa;
+  pa.b = b;
+  pa.slabs[0] = slab0;
+  pa.slabs[1] = slab1;
+  pa.walk_done = counters;
+  pa.conv_done = counters + pieces;
+  pa.pieces = pieces;
+  const long long units = (long long)b.B * b.NS;
+  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
+  const long long items = (long long)b.F * G;
+  int conv = (int)((items + kThreads * 4 - 1) / (kThreads * 4));
+  if (conv > kConvertBlocks) conv = kConvertBlocks;
+  pa.conv_blocks = conv;
+  pa.conv_offset = (int)((long long)pa.unit_blocks * g_opt.convert_offset_pct / 100);
+  const long long blocks = (long long)pieces * (pa.unit_blocks + conv) + conv;
+  if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  kern<<<(unsigned)blocks, kThreads, smem, st>>>(pa);
   t_launches++;
   return cudaGetLastError();
 }
@@ -682,6 +812,8 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "lanes_bwd") && lanes_ok) { g_opt.lanes_bwd = (int)value; return 0; }
   if (!strcmp(name, "l2_budget_mb") && value >= 1 && value <= 4096) { g_opt.l2_budget_mb = (int)value; return 0; }
   if (!strcmp(name, "segments") && value >= 0 && value <= 256) { g_opt.segments = (int)value; return 0; }
+  if (!strcmp(name, "pipeline") && (value == 0 || value == 1)) { g_opt.pipeline = (int)value; return 0; }
+  if (!strcmp(name, "convert_offset_pct") && value >= 0 && value <= 100) { g_opt.convert_offset_pct = (int)value; return 0; }
   return fail(FLEXSAE_EINVAL, "unknown option or value: %s=%lld", name, (long long)value);
 }
 
@@ -691,6 +823,8 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "lanes_bwd")) return g_opt.lanes_bwd;
   if (!strcmp(name, "l2_budget_mb")) return g_opt.l2_budget_mb;
   if (!strcmp(name, "segments")) return g_opt.segments;
+  if (!strcmp(name, "pipeline")) return g_opt.pipeline;
+  if (!strcmp(name, "convert_offset_pct")) return g_opt.convert_offset_pct;
   return -1;
 }
 
@@ -837,6 +971,19 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   // one more launch converts the last piece.
   e = cudaMemsetAsync(slabs[0], 0, 2 * p.slab_bytes, st);
   if (e != cudaSuccess) return fail((int)e, "slab clear failed: %s", cudaGetErrorString(e));
+  if (g_opt.pipeline) {
+    int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
+    e = cudaMemsetAsync(counters, 0, (size_t)2 * p.pieces * 4, st);
+    if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
+    a.piece = a.conv_piece = -1;
+    a.slab = a.conv_slab = nullptr;
+    a.unit_blocks = a.conv_blocks = 0;
+    a.conv_stride = 1;
+#define CALL_PIPE(T, G, H) launch_bwd_pipelined<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, st)
+    e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_PIPE);
+#undef CALL_PIPE
+    if (e != cudaSuccess) return fail((int)e, "pipelined backward launch failed: %s", cudaGetErrorString(e));
+  } else
   for (int i = 0; i <= p.pieces; i++) {
     a.piece = i < p.pieces ? i : -1;
     a.conv_piece = i - 1;

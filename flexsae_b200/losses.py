@@ -103,6 +103,9 @@ def check_status(device=None) -> None:
     bits = int(word.item())
     if bits:
         word.zero_()
+        if bits & nv.STATUS_PIPELINE_TIMEOUT:
+            raise RuntimeError("flexsae_b200: a bounded wait inside the single-launch backward gave up; "
+                               "the gradients of that call are invalid")
         if bits & nv.STATUS_BAD_INDEX:
             raise IndexError("flexsae_b200: indices outside [0, F) were passed to a fused loss")
 

@@ -48,6 +48,7 @@ extern "C" {
 
 /* bits of the optional device status word */
 #define FLEXSAE_STATUS_BAD_INDEX 1 /* an index outside [0,F) was met; it was read as row 0 */
+#define FLEXSAE_STATUS_PIPELINE_TIMEOUT 2 /* a bounded wait inside the single-launch backward gave up: gradients invalid */
 
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int flexsae_version(void);
@@ -59,7 +60,8 @@ const char* flexsae_last_error(void);
 /* Tuning knobs, process-wide: "lanes_fwd", "lanes_bwd" (8, 16, 32 lanes share one batch row;
  * 0 = choose so that one column slab of the decoder and of the fp32 gradient slab stay in L2),
  * "l2_budget_mb" (working set one column piece may occupy), "segments"
- * (what flexsae_choose_segments answers; 0 = derive from the shape).
+ * (what flexsae_choose_segments answers; 0 = derive from the shape), "pipeline" (1: the atomic
+ * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct".
  * Stands in for the literal tile constants at the reference's launch sites
  * (torch-ext/flex_sae/hierarchical_kernels.py:220-224,263-267; topk_kernels.py:64-66,181-183).
  * Returns 0, or FLEXSAE_EINVAL for an unknown name or value. */

@@ -1,0 +1,71 @@
+"""GPU, 2 ranks over NCCL (skipped with fewer than 2 GPUs): batch-sharded fused losses against
+the single-GPU fused result on the whole batch."""
+import os
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, kind, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from flexsae_b200 import distributed as fd
+        from flexsae_b200.workloads import CONFIGS, make_inputs
+        w = CONFIGS["c3_k32"].replace(B=768, F=8192)
+        rows = w.B // world
+        x = make_inputs(w, f"cuda:{rank}", row0=rank * rows, rows=rows)
+        weight = x["weight"].requires_grad_(True)
+        vals = x["vals"].requires_grad_(True)
+        bias = x["bias"].requires_grad_(True)
+        fn = fd.sharded_hierarchical_sae_loss if kind == "hier" else fd.sharded_topk_sae_loss
+        loss = fn(x["indices"], weight, vals, bias, x["target"])
+        loss.backward(x["grad_out"])
+        torch.cuda.synchronize()
+        q.put((rank, float(loss), weight.grad.float().cpu(), vals.grad.float().cpu(), bias.grad.float().cpu()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+def test_two_gpu_shards_match_one_gpu(kind):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    import flexsae_b200 as fx
+    from flexsae_b200.workloads import CONFIGS, make_inputs
+    from tests.helpers import rel_err
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, kind, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    outs = sorted([q.get(timeout=300) for _ in procs], key=lambda o: o[0])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+
+    w = CONFIGS["c3_k32"].replace(B=768, F=8192)
+    x = make_inputs(w, "cuda:0")
+    weight = x["weight"].requires_grad_(True)
+    vals = x["vals"].requires_grad_(True)
+    bias = x["bias"].requires_grad_(True)
+    fn = fx.triton_hierarchical_sae_loss if kind == "hier" else fx.triton_topk_sae_loss
+    loss = fn(x["indices"], weight, vals, bias, x["target"])
+    loss.backward(x["grad_out"])
+    rows = w.B // 2
+    for rank, l, dW, dv, db in outs:
+        assert abs(l - float(loss)) <= 1e-6 * abs(float(loss))
+        assert rel_err(dW.numpy(), weight.grad.float().cpu().numpy()) < 1e-2      # bf16 sum of two bf16 shards
+        assert rel_err(db.numpy(), bias.grad.float().cpu().numpy()) < 1e-2
+        assert torch.equal(dv, vals.grad.float().cpu()[rank * rows:(rank + 1) * rows])

@@ -44,6 +44,7 @@ def assert_close_to_oracle(got, want, tol, loss_tol=1e-5):
 def _auto_options():
     for name in ("lanes_fwd", "lanes_bwd", "segments"):
         nv.set_option(name, 0)
+    nv.set_option("pipeline", 1)
     yield
     fx.check_status()
 
@@ -86,6 +87,20 @@ def test_every_segment_count(name, kind, segments):
     path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
     w, kind, gold = load_golden(path)
     nv.set_option("segments", segments)
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("name", ["t16_64_128_1024_bfloat16", "c1", "ragged_rows_float32"])
+def test_one_launch_per_piece_form(name, kind):
+    """The multi-launch form of the atomic backward (the default is the single-launch pipeline)."""
+    path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
+    w, kind, gold = load_golden(path)
+    nv.set_option("pipeline", 0)
+    nv.set_option("lanes_bwd", 8)        # many column pieces
     x = make_inputs(w, "cpu")
     got = run_fused(kind, x)
     want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
