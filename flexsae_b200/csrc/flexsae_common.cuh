@@ -29,6 +29,10 @@ struct Pack<float> {
     return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]),
                       __float_as_uint(f[3]));
   }
+  __device__ __forceinline__ static void unpack_pairs(const uint4& u, float2* f) {
+    f[0] = make_float2(__uint_as_float(u.x), __uint_as_float(u.y));
+    f[1] = make_float2(__uint_as_float(u.z), __uint_as_float(u.w));
+  }
 };
 
 template <>
@@ -45,6 +49,12 @@ struct Pack<__nv_bfloat16> {
     f[5] = __uint_as_float(u.z & 0xffff0000u);
     f[6] = __uint_as_float(u.w << 16);
     f[7] = __uint_as_float(u.w & 0xffff0000u);
+  }
+  __device__ __forceinline__ static void unpack_pairs(const uint4& u, float2* f) {
+    f[0] = make_float2(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u));
+    f[1] = make_float2(__uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+    f[2] = make_float2(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xffff0000u));
+    f[3] = make_float2(__uint_as_float(u.w << 16), __uint_as_float(u.w & 0xffff0000u));
   }
   __device__ __forceinline__ static uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
@@ -70,6 +80,12 @@ struct Pack<__half> {
     unpack2(u.z, f + 4);
     unpack2(u.w, f + 6);
   }
+  __device__ __forceinline__ static void unpack_pairs(const uint4& u, float2* f) {
+    f[0] = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+    f[1] = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+    f[2] = __half22float2(*reinterpret_cast<const __half2*>(&u.z));
+    f[3] = __half22float2(*reinterpret_cast<const __half2*>(&u.w));
+  }
   __device__ __forceinline__ static uint32_t pack2(float a, float b) {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
@@ -80,14 +96,27 @@ struct Pack<__half> {
 };
 
 // ---- memory instructions -----------------------------------------------------------------------
-// Decoder rows are gathered once per (batch row, k) by one lane group and never reused by the
-// same SM, so they bypass L1 allocation; reuse across SMs happens in L2.
+// One 16-byte piece of a gathered decoder row.  A plain (L1-allocating) load on purpose: measured
+// on B200, `ld.global.nc.L1::no_allocate` tops out near 9.5 TB/s from L2 and its lines are not
+// retained in L2 between the ~8 batch rows that use the same decoder row (4.5x the table in HBM
+// reads per pass), while the plain load reaches ~15 TB/s and keeps the column piece L2-resident.
 __device__ __forceinline__ uint4 ld_row_piece(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
+  asm("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
+}
+
+// Asynchronous 16-byte global -> shared copy (L2 only); `bytes` = 16 copies, 0 writes zeros
+// without touching global memory.  Completion is tracked per thread in commit groups.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)),
+               "l"(gmem_src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // 16-byte fire-and-forget fp32 add, resolved by the L2 atomic units (sm_90+).
@@ -142,6 +171,12 @@ __device__ __forceinline__ void load_elems(const void* p, int dtype, size_t off,
     }
   }
 }
+
+// Packed fp32 arithmetic (two lanes of a 64-bit register pair per instruction, sm_100): the
+// kernels are bound by instruction issue as much as by memory, and this halves the FP32 issue slots.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 
 // Sum over the G lanes (G = 8, 16 or 32, lane groups aligned to G) that share one batch row.
 template <int G>

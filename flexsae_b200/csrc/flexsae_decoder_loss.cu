@@ -36,7 +36,7 @@ struct Options {
   int l2_budget_mb = 80;  // one piece of decoder columns (+ one fp32 slab) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
-  int convert_offset_pct = 25;  // where, inside a piece's unit blocks, the previous piece's converters sit
+  int convert_offset_pct = 60;  // where, inside a piece's unit blocks, the previous piece's converters sit
 };
 static Options g_opt;
 
@@ -63,6 +63,7 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 #endif
 constexpr int kThreads = 128;  // 4 warps per CTA: 16 / 8 / 4 lane groups for G = 8 / 16 / 32
 constexpr int kUnroll = 8;     // decoder-row loads in flight per lane; segment lengths are multiples of it
+constexpr int kRingSlots = 2 * kUnroll;  // backward: row pieces staged in shared memory per lane
 __host__ __device__ constexpr int groups_per_cta(int G) { return kThreads / G; }
 
 // Saved row state ("state" below), float32, written by the forward and read by the backward:
@@ -96,6 +97,7 @@ struct BwdArgs {
   float* conv_slab;       // the other slab: finished piece `conv_piece`, converted by trailing CTAs
   void* dweight;          // [F, D] in the decoder's storage type
   float* dv_part;         // [pieces, B, K]
+  float* s0;              // Hierarchical: [B, D] sum over k of the prefix residuals (dbias = coef * column sums)
   float* stage;           // deterministic mode: [B*K, PW] contribution rows in sorted-slot order
   const int* slot_of;     // deterministic mode: [B*K] sorted slot of each (b, k)
   int32_t* status;
@@ -134,8 +136,28 @@ __device__ __forceinline__ void store_f32(float* p, const float* v, int n4) {
   for (int i = 0; i < n4; i++) q[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
 }
 
+template <int H>  // H float2 pairs = 2H floats, 16-byte aligned
+__device__ __forceinline__ void load_pairs(const float* p, float2* out) {
+  const float4* q = reinterpret_cast<const float4*>(p);
+#pragma unroll
+  for (int i = 0; i < H / 2; i++) {
+    const float4 t = __ldg(q + i);
+    out[2 * i] = make_float2(t.x, t.y);
+    out[2 * i + 1] = make_float2(t.z, t.w);
+  }
+}
+
+template <int H>
+__device__ __forceinline__ void store_pairs(float* p, const float2* v) {
+  float4* q = reinterpret_cast<float4*>(p);
+#pragma unroll
+  for (int i = 0; i < H / 2; i++) q[i] = make_float4(v[2 * i].x, v[2 * i].y, v[2 * i + 1].x, v[2 * i + 1].y);
+}
+
 // ---- forward -----------------------------------------------------------------------------------
-template <typename T, int G, bool HIER>
+// SEG: the row is cut into several K-segments, so the residual and the running residual sum are
+// saved at every segment end (otherwise only the final residual is saved).
+template <typename T, int G, bool HIER, bool SEG>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_kernel(const FwdArgs a) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
@@ -158,15 +180,16 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_k
   const int col = piece * PW + lig * VEC;
   const bool active = (b < a.B) && (col < a.D);
 
-  float r[VEC], acc[VEC], csum[VEC];
+  constexpr int H = VEC / 2;
+  float2 r[H], acc[H], csum[H];
 #pragma unroll
-  for (int j = 0; j < VEC; j++) r[j] = acc[j] = csum[j] = 0.f;
+  for (int h = 0; h < H; h++) r[h] = acc[h] = csum[h] = make_float2(0.f, 0.f);
   if (active) {
     float bv[VEC], tv[VEC];
     load_elems<VEC>(a.bias, a.bias_dtype, (size_t)col, bv);
     load_elems<VEC>(a.target, a.target_dtype, (size_t)b * a.D + col, tv);
 #pragma unroll
-    for (int j = 0; j < VEC; j++) r[j] = bv[j] - tv[j];
+    for (int h = 0; h < H; h++) r[h] = make_float2(bv[2 * h] - tv[2 * h], bv[2 * h + 1] - tv[2 * h + 1]);
   }
 
   const char* wcol = reinterpret_cast<const char*>(a.weight) + (size_t)col * sizeof(T);
@@ -190,22 +213,21 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_k
     for (int u = 0; u < U; u++) {
       if (k0 + u < K) {
         const float v = __int_as_float(e[u].y);
-        float wf[VEC];
-        Pack<T>::unpack(w[u], wf);
+        const float2 vv = make_float2(v, v);
+        float2 wf[H];
+        Pack<T>::unpack_pairs(w[u], wf);
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-          r[j] = fmaf(v, wf[j], r[j]);  // residual of the k-th prefix
-          if (HIER) {
-            acc[j] = fmaf(r[j], r[j], acc[j]);  // every prefix is penalised
-            csum[j] += r[j];
-          }
+        for (int h = 0; h < H; h++) {
+          r[h] = fma2(vv, wf[h], r[h]);  // residual of the k-th prefix
+          if (HIER) acc[h] = fma2(r[h], r[h], acc[h]);  // every prefix is penalised
+          if (HIER && SEG) csum[h] = add2(csum[h], r[h]);
         }
       }
     }
-    if (HIER && (k0 + U == seg_end) && (k0 + U < K)) {  // a segment ends inside the row
+    if (HIER && SEG && (k0 + U == seg_end) && (k0 + U < K)) {  // a segment ends inside the row
       if (active) {
-        store_f32(st_r + seg * seg_stride, r, VEC / 4);
-        store_f32(st_c + seg * seg_stride, csum, VEC / 4);
+        store_pairs<H>(st_r + seg * seg_stride, r);
+        store_pairs<H>(st_c + seg * seg_stride, csum);
       }
       seg++;
       seg_end += a.KS;
@@ -213,16 +235,16 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_k
   }
   if (!HIER) {
 #pragma unroll
-    for (int j = 0; j < VEC; j++) acc[j] = r[j] * r[j];
+    for (int h = 0; h < H; h++) acc[h] = mul2(r[h], r[h]);
   }
   float s = 0.f;
 #pragma unroll
-  for (int j = 0; j < VEC; j++) s += acc[j];
+  for (int h = 0; h < H; h++) s += acc[h].x + acc[h].y;
   s = group_sum<G>(s);
   if (lig == 0 && b < a.B) a.loss_part[(size_t)piece * a.B + b] = s;
   if (active) {
-    store_f32(st_r + seg * seg_stride, r, VEC / 4);  // HIER: seg == NS - 1 here; TopK: seg == 0
-    if (HIER) store_f32(st_c + seg * seg_stride, csum, VEC / 4);
+    store_pairs<H>(st_r + seg * seg_stride, r);  // HIER: seg == NS - 1 here; TopK: seg == 0
+    if (HIER && SEG) store_pairs<H>(st_c + seg * seg_stride, csum);
   }
 }
 
@@ -322,11 +344,15 @@ __device__ __forceinline__ void convert_slab(float* slab, void* __restrict__ dwe
 // down to its first: suffix += residual; dweight[idx] += vals * suffix; dvals = <row, suffix>;
 // residual -= vals * row  (the reverse walk of hierarchical_kernels.py:147-173).
 template <typename T, int G, bool HIER, bool DET>
-__device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int piece, float* slab_base, int2* staged) {
+__device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int piece, float* slab_base, uint4* smem) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
   constexpr int UPC = groups_per_cta(G);
   constexpr int U = kUnroll;
+  // Shared memory: a per-lane ring of 2*U row pieces (each lane only ever reads back the 16 bytes
+  // it copied itself, so no warp synchronisation is involved), then the staged (index, val) pairs.
+  uint4* ring = smem + threadIdx.x;  // slot s of this lane: ring[s * kThreads]
+  int2* staged = reinterpret_cast<int2*>(smem + kRingSlots * kThreads);
   const int K = a.K, KS = a.KS, NS = a.NS;
   const int unit0 = unit_block * UPC;
   const int nunits = a.B * NS;
@@ -361,22 +387,23 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
   const bool active = live && (col < a.D);
   const float coef = __ldg(a.grad_out) * a.scale;
 
-  float r[VEC], suf[VEC];
+  constexpr int H = VEC / 2;
+  float2 r[H], suf[H];
 #pragma unroll
-  for (int j = 0; j < VEC; j++) r[j] = suf[j] = 0.f;
+  for (int h = 0; h < H; h++) r[h] = suf[h] = make_float2(0.f, 0.f);
   if (active) {
     const size_t seg_stride = (size_t)a.B * a.D;
     const float* st = a.state + (size_t)row * a.D + col;
-    load_f32(st + (HIER ? seg : 0) * seg_stride, r, VEC / 4);
+    load_pairs<H>(st + (HIER ? seg : 0) * seg_stride, r);
     if (!HIER) {
 #pragma unroll
-      for (int j = 0; j < VEC; j++) suf[j] = r[j];  // TopK: every k sees the same residual
+      for (int h = 0; h < H; h++) suf[h] = r[h];  // TopK: every k sees the same residual
     } else if (seg != NS - 1) {
-      float c_here[VEC], c_all[VEC];
-      load_f32(st + (size_t)(NS + seg) * seg_stride, c_here, VEC / 4);
-      load_f32(st + (size_t)(2 * NS - 1) * seg_stride, c_all, VEC / 4);
+      float2 c_here[H], c_all[H];
+      load_pairs<H>(st + (size_t)(NS + seg) * seg_stride, c_here);
+      load_pairs<H>(st + (size_t)(2 * NS - 1) * seg_stride, c_all);
 #pragma unroll
-      for (int j = 0; j < VEC; j++) suf[j] = c_all[j] - c_here[j];  // residuals of all later k
+      for (int h = 0; h < H; h++) suf[h] = make_float2(c_all[h].x - c_here[h].x, c_all[h].y - c_here[h].y);  // all later k
     }
   }
 
@@ -387,58 +414,86 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
   float* slab = slab_base + lig * 4;
   float* dv = a.dv_part + ((size_t)piece * a.B + row) * K + k_first;
 
-  for (int jb = KS - 1; jb >= 0; jb -= U) {  // KS is a multiple of U
-    uint4 w[U];
-    int2 e[U];
+  // Row pieces travel global -> shared asynchronously, one batch of U ahead of the batch being
+  // processed: the loads of batch b+1 are queued BEFORE the reductions of batch b, so they are not
+  // stuck behind them in the SM's memory pipeline and the L2 atomic units never run dry.
+  auto issue_batch = [&](int jb_, int half) {
 #pragma unroll
     for (int u = 0; u < U; u++) {
-      e[u] = mine[jb - u];
-      w[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (active && jb - u < n) w[u] = ld_row_piece(wcol + (size_t)e[u].x * row_bytes);
+      const int j = jb_ - u;
+      const bool ok = active && j >= 0 && j < n;
+      const int id = j >= 0 ? mine[j].x : 0;
+#ifndef FLEXSAE_EXPERIMENT_NO_LOADS
+      cp_async16(ring + (half * U + u) * kThreads, wcol + (size_t)id * row_bytes, ok ? 16 : 0);
+#else
+      cp_async16(ring + (half * U + u) * kThreads, wcol + (size_t)(id & 1) * row_bytes, ok ? 16 : 0);
+#endif
     }
+    cp_async_commit();
+  };
+  issue_batch(KS - 1, 0);
+  issue_batch(KS - 1 - U, 1);
+  int half = 0;
+  for (int jb = KS - 1; jb >= 0; jb -= U, half ^= 1) {  // KS is a multiple of U
+    cp_async_wait<1>();  // all but the newest group have landed: this batch is in the ring
+    int2 e[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) e[u] = mine[jb - u];
     float d[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const bool in_seg = jb - u < n;
       const float v = __int_as_float(e[u].y);
       const float c = v * coef;
-      float wf[VEC];
-      Pack<T>::unpack(w[u], wf);
+      const float2 cc = make_float2(c, c), nv = make_float2(-v, -v);
+      float2 wf[H];
+      Pack<T>::unpack_pairs(ring[(half * U + u) * kThreads], wf);
       if (HIER && in_seg) {
 #pragma unroll
-        for (int j = 0; j < VEC; j++) suf[j] += r[j];  // S_k = sum_{j>=k} residual_j
+        for (int h = 0; h < H; h++) suf[h] = add2(suf[h], r[h]);  // S_k = sum_{j>=k} residual_j
       }
       if (active && in_seg) {
+        float2 g[H];
+#pragma unroll
+        for (int h = 0; h < H; h++) g[h] = mul2(suf[h], cc);
         if (DET) {  // the contribution row goes to its sorted slot; it is added later, in slot order
           float4* dst = reinterpret_cast<float4*>(a.stage + (size_t)myslot[jb - u] * PW + lig * VEC);
-          __stcs(dst, make_float4(suf[0] * c, suf[1] * c, suf[2] * c, suf[3] * c));
-          if (VEC == 8) __stcs(dst + 1, make_float4(suf[VEC - 4] * c, suf[VEC - 3] * c, suf[VEC - 2] * c, suf[VEC - 1] * c));
+          __stcs(dst, make_float4(g[0].x, g[0].y, g[1].x, g[1].y));
+          if (VEC == 8) __stcs(dst + 1, make_float4(g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y));
         } else {
           float* dst = slab + (size_t)e[u].x * PW;
-          red_add_v4(dst, suf[0] * c, suf[1] * c, suf[2] * c, suf[3] * c);
-          if (VEC == 8) red_add_v4(dst + G * 4, suf[VEC - 4] * c, suf[VEC - 3] * c, suf[VEC - 2] * c, suf[VEC - 1] * c);
+#ifndef FLEXSAE_EXPERIMENT_NO_REDS
+          red_add_v4(dst, g[0].x, g[0].y, g[1].x, g[1].y);
+          if (VEC == 8) red_add_v4(dst + G * 4, g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y);
+#else
+          if (g[0].x == 1.2345e-30f) dst[0] = g[1].y + g[H - 1].x;
+#endif
         }
       }
-      float dot = 0.f;
+      float2 dot = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int j = 0; j < VEC; j++) dot = fmaf(wf[j], suf[j], dot);
-      d[u] = dot;  // rows outside the segment were loaded as zeros
+      for (int h = 0; h < H; h++) dot = fma2(wf[h], suf[h], dot);
+      d[u] = dot.x + dot.y;  // rows outside the segment were loaded as zeros
       if (HIER) {
 #pragma unroll
-        for (int j = 0; j < VEC; j++) r[j] = fmaf(-v, wf[j], r[j]);  // step back to prefix k-1
+        for (int h = 0; h < H; h++) r[h] = fma2(nv, wf[h], r[h]);  // step back to prefix k-1
       }
     }
+    issue_batch(jb - 2 * U, half);  // refill the half just consumed (an empty group past the end)
     const float tot = group_sum8<G>(d, lig);
     const int j = jb - (lig & 7);
     if (live && lig < 8 && j < n) dv[j] = tot * coef;
   }
+  // The first segment ends with S_0, the sum of all prefix residuals of the row: dbias is the
+  // column sum of these (TopK takes the column sums of the saved residual directly).
+  if (HIER && active && seg == 0) store_pairs<H>(a.s0 + (size_t)row * a.D + col, suf);
 }
 
 // Multi-launch form: one launch per column piece; converting CTAs for the previous piece are
 // spread evenly through the grid.
 template <typename T, int G, bool HIER, bool DET>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_kernel(const BwdArgs a) {
-  extern __shared__ int2 staged[];  // [UPC][KS], then (deterministic mode) int slots[UPC][KS]
+  extern __shared__ uint4 smem[];  // ring, staged pairs [UPC][KS], then (deterministic mode) int slots[UPC][KS]
   int unit_block = blockIdx.x;
   if (!DET && a.conv_blocks > 0) {
     const int q = blockIdx.x / a.conv_stride;
@@ -448,7 +503,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
     }
     unit_block = blockIdx.x - min(q, a.conv_blocks);
   }
-  walk_units<T, G, HIER, DET>(a, unit_block, a.piece, a.slab, staged);
+  walk_units<T, G, HIER, DET>(a, unit_block, a.piece, a.slab, smem);
 }
 
 // ---- single-launch pipelined backward ------------------------------------------------------------
@@ -505,7 +560,7 @@ __device__ __forceinline__ void signal_done(int* ctr) {
 
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_pipelined_kernel(const PipeArgs pa) {
-  extern __shared__ int2 staged[];
+  extern __shared__ uint4 smem[];
   const int per = pa.unit_blocks + pa.conv_blocks;
   const int p = blockIdx.x / per;
   const int r = blockIdx.x - p * per;
@@ -526,7 +581,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
     return;
   }
   if (p >= 2) wait_count(pa.conv_done + (p - 2), pa.conv_blocks, pa.b.status);
-  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], staged);
+  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
   signal_done(pa.walk_done + p);
 }
 
@@ -588,8 +643,9 @@ static int check_shape(int kind, const Shape& s, int wdt) {
     return fail(FLEXSAE_EUNSUPPORTED, "D=%lld must be a multiple of %d (16-byte row pieces)", (long long)s.D, vec);
   if (s.F > (1ll << 30) || s.D > (1ll << 20) || s.B > (1ll << 27) || s.B * s.K > (1ll << 31) - 1)
     return fail(FLEXSAE_EUNSUPPORTED, "shape too large for 32-bit row/position arithmetic");
-  // indices and vals of a CTA's rows are staged in shared memory: 16 rows * K * 8 bytes
-  if (s.K > 1600) return fail(FLEXSAE_EUNSUPPORTED, "K=%lld above the supported maximum of 1600", (long long)s.K);
+  // indices, vals (and sorted slots) of a CTA's rows are staged in shared memory next to the
+  // 32 KiB row-piece ring: 16 rows * K * 12 bytes must fit
+  if (s.K > 960) return fail(FLEXSAE_EUNSUPPORTED, "K=%lld above the supported maximum of 960", (long long)s.K);
   return 0;
 }
 
@@ -631,7 +687,7 @@ static int choose_segments(const Shape& s, int wdt) {
 }
 
 static size_t state_floats(int kind, const Shape& s, int NS) {
-  return (size_t)s.B * s.D * (kind == FLEXSAE_HIER ? 2 * (size_t)NS : 1);
+  return (size_t)s.B * s.D * ((kind == FLEXSAE_HIER && NS > 1) ? 2 * (size_t)NS : 1);
 }
 
 static int check_segments(int kind, const Shape& s, int segments, int* KS, int* NS) {
@@ -648,7 +704,7 @@ constexpr int kConvertBlocks = 148 * 3;  // trailing CTAs that convert the previ
 
 struct BwdPlan {
   int G, PW, pieces, row_blocks, rows_per_block;
-  size_t slab_bytes, off_slab, off_dv, off_db, off_ctr, off_index, off_stage, off_part, total;
+  size_t slab_bytes, off_slab, off_dv, off_db, off_s0, off_ctr, off_index, off_stage, off_part, total;
 };
 
 static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
@@ -677,6 +733,8 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   off = align_up(off + (size_t)p.pieces * s.B * s.K * 4, 256);
   p.off_db = off;
   off = align_up(off + (size_t)p.row_blocks * s.D * 4, 256);
+  p.off_s0 = off;  // summed prefix residuals of every row (Hierarchical; TopK does not use it)
+  off = align_up(off + (size_t)s.B * s.D * 4, 256);
   p.off_ctr = off;  // per-piece completion counters of the single-launch pipeline
   off = align_up(off + (size_t)2 * p.pieces * 4, 256);
   p.total = off;
@@ -698,17 +756,19 @@ static FwdPlan plan_fwd(const Shape& s, int wdt) {
   return p;
 }
 
+constexpr size_t kRingBytes = (size_t)kRingSlots * kThreads * sizeof(uint4);  // 32 KiB per CTA
+
 template <typename K>
 static cudaError_t allow_smem(K kern, size_t smem) {
   if (smem <= 48 * 1024) return cudaSuccess;
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 
-template <typename T, int G, bool HIER>
-static cudaError_t launch_fwd(const FwdArgs& a, int pieces, cudaStream_t st) {
+template <typename T, int G, bool HIER, bool SEG>
+static cudaError_t launch_fwd_seg(const FwdArgs& a, int pieces, cudaStream_t st) {
   constexpr int RPC = groups_per_cta(G);
   const size_t smem = (size_t)RPC * a.K * sizeof(int2);
-  auto kern = decoder_loss_fwd_kernel<T, G, HIER>;
+  auto kern = decoder_loss_fwd_kernel<T, G, HIER, SEG>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   dim3 grid((a.B + RPC - 1) / RPC, pieces);
   kern<<<grid, kThreads, smem, st>>>(a);
@@ -717,9 +777,15 @@ static cudaError_t launch_fwd(const FwdArgs& a, int pieces, cudaStream_t st) {
 }
 
 template <typename T, int G, bool HIER>
+static cudaError_t launch_fwd(const FwdArgs& a, int pieces, cudaStream_t st) {
+  if (HIER && a.NS > 1) return launch_fwd_seg<T, G, HIER, true>(a, pieces, st);
+  return launch_fwd_seg<T, G, HIER, false>(a, pieces, st);
+}
+
+template <typename T, int G, bool HIER>
 static cudaError_t launch_bwd_det(BwdArgs a, cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
-  const size_t smem = (size_t)UPC * a.KS * (sizeof(int2) + sizeof(int));
+  const size_t smem = kRingBytes + (size_t)UPC * a.KS * (sizeof(int2) + sizeof(int));
   auto kern = decoder_loss_bwd_kernel<T, G, HIER, true>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   const long long units = (long long)a.B * a.NS;
@@ -734,7 +800,7 @@ static cudaError_t launch_bwd_det(BwdArgs a, cudaStream_t st) {
 template <typename T, int G, bool HIER>
 static cudaError_t launch_bwd(BwdArgs a, cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
-  const size_t smem = (size_t)UPC * a.KS * sizeof(int2);
+  const size_t smem = kRingBytes + (size_t)UPC * a.KS * sizeof(int2);
   auto kern = decoder_loss_bwd_kernel<T, G, HIER, false>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   const long long units = (long long)a.B * a.NS;
@@ -757,7 +823,7 @@ template <typename T, int G, bool HIER>
 static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
                                         cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
-  const size_t smem = (size_t)UPC * b.KS * sizeof(int2);
+  const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
   auto kern = decoder_loss_bwd_pipelined_kernel<T, G, HIER>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   PipeArgs pa;
@@ -927,6 +993,7 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   a.dweight = dweight;
   a.stage = nullptr;
   a.slot_of = nullptr;
+  a.s0 = reinterpret_cast<float*>(ws + p.off_s0);
   a.dv_part = reinterpret_cast<float*>(ws + p.off_dv);
   a.status = status;
   a.B = (int)B; a.K = (int)K; a.F = (int)F; a.D = (int)D;
@@ -935,15 +1002,7 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   a.KS = KS; a.NS = NS;
   float* db_part = reinterpret_cast<float*>(ws + p.off_db);
 
-  // dbias only needs what the forward left behind: column sums of the final residual (TopK) or
-  // of the summed prefix residuals (Hierarchical: part 1 of the state, last segment).
-  const float* colsrc = state + (kind == FLEXSAE_HIER ? (size_t)(2 * NS - 1) * B * D : 0);
-  column_sums_kernel<<<dim3((unsigned)((D + 127) / 128), p.row_blocks), 128, 0, st>>>(colsrc, (int)B, (int)D,
-                                                                                      p.rows_per_block, db_part);
-  t_launches++;
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail((int)e, "column sums launch failed: %s", cudaGetErrorString(e));
-
+  cudaError_t e = cudaSuccess;
   if (dw_mode == FLEXSAE_DW_DETERMINISTIC) {
     // Sort the (decoder row, position) pairs once; then per column piece: the same reverse walk,
     // but every contribution row is stored to its sorted slot, and the rows of each decoder row
@@ -995,6 +1054,14 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
     if (e != cudaSuccess) return fail((int)e, "backward launch failed: %s", cudaGetErrorString(e));
   }
   }
+  // dbias = coef * column sums of the final residual (TopK) or of the summed prefix residuals the
+  // first-segment walkers left in s0 (Hierarchical): partial sums over row blocks, fixed order.
+  const float* colsrc = kind == FLEXSAE_HIER ? a.s0 : state;
+  column_sums_kernel<<<dim3((unsigned)((D + 127) / 128), p.row_blocks), 128, 0, st>>>(colsrc, (int)B, (int)D,
+                                                                                      p.rows_per_block, db_part);
+  t_launches++;
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail((int)e, "column sums launch failed: %s", cudaGetErrorString(e));
   const size_t BK = (size_t)B * K;
   const int dv_blocks = (int)((BK + 255) / 256);
   const int db_blocks = (int)((D + 255) / 256);

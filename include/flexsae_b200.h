@@ -73,7 +73,8 @@ int64_t flexsae_get_option(const char* name);
  * flexsae_choose_segments answers how many segments to use for a shape (0 on invalid arguments);
  * the same number must be given to the forward, the backward and flexsae_state_bytes, which
  * answers the size of the float32 state buffer the forward writes for the backward:
- * B*D floats (TopK) or 2*segments*B*D floats (Hierarchical).
+ * B*D floats (TopK, or Hierarchical with one segment) or 2*segments*B*D floats (Hierarchical
+ * with several segments).
  * Stands in for final_recon[B,D] saved by the reference forward
  * (torch-ext/flex_sae/hierarchical_kernels.py:201,285). */
 int flexsae_choose_segments(int kind, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype);

@@ -60,7 +60,7 @@ def test_options_and_workspace_sizes_without_gpu():
     nv.set_option("lanes_bwd", 32)
     n = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2304, nv.BF16, nv.DW_ATOMIC)
     nv.set_option("lanes_bwd", 0)
-    assert 2 * 65536 * 256 * 4 <= n <= 2 * 65536 * 256 * 4 + 9 * 4096 * 128 * 4 + 512 * 2304 * 4 + 4096
+    assert 2 * 65536 * 256 * 4 <= n <= 2 * 65536 * 256 * 4 + 9 * 4096 * 128 * 4 + 4096 * 2304 * 4 + 512 * 2304 * 4 + 8192
     assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2304, nv.BF16) >= 9 * 4096 * 4
     # rejected shapes give 0 and an explanation
     assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 4096, 128, 65536, 2301, nv.BF16) == 0
@@ -93,4 +93,5 @@ def test_segment_layouts():
         ns = lib.flexsae_choose_segments(nv.HIER, 64, K, 1024, 512, nv.F32)
         assert 1 <= ns <= max(1, (K + 7) // 8)
     assert lib.flexsae_state_bytes(nv.HIER, 10, 16, 256, 2) == 2 * 2 * 10 * 256 * 4
+    assert lib.flexsae_state_bytes(nv.HIER, 10, 16, 256, 1) == 10 * 256 * 4
     assert lib.flexsae_state_bytes(nv.TOPK, 10, 16, 256, 2) == 10 * 256 * 4
