@@ -63,7 +63,10 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 #endif
 constexpr int kThreads = 128;  // 4 warps per CTA: 16 / 8 / 4 lane groups for G = 8 / 16 / 32
 constexpr int kUnroll = 8;     // decoder-row loads in flight per lane; segment lengths are multiples of it
-constexpr int kRingSlots = 2 * kUnroll;  // backward: row pieces staged in shared memory per lane
+#ifndef FLEXSAE_RING
+#define FLEXSAE_RING 12
+#endif
+constexpr int kRingSlots = FLEXSAE_RING;  // backward: row pieces in flight per lane (shared-memory ring)
 __host__ __device__ constexpr int groups_per_cta(int G) { return kThreads / G; }
 
 // Saved row state ("state" below), float32, written by the forward and read by the backward:
@@ -414,28 +417,26 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
   float* slab = slab_base + lig * 4;
   float* dv = a.dv_part + ((size_t)piece * a.B + row) * K + k_first;
 
-  // Row pieces travel global -> shared asynchronously, one batch of U ahead of the batch being
-  // processed: the loads of batch b+1 are queued BEFORE the reductions of batch b, so they are not
-  // stuck behind them in the SM's memory pipeline and the L2 atomic units never run dry.
-  auto issue_batch = [&](int jb_, int half) {
-#pragma unroll
-    for (int u = 0; u < U; u++) {
-      const int j = jb_ - u;
-      const bool ok = active && j >= 0 && j < n;
-      const int id = j >= 0 ? mine[j].x : 0;
+  // Row pieces travel global -> shared asynchronously through a ring of kRingSlots slots per
+  // lane: the piece for step j - kRingSlots is requested as soon as step j has been consumed, so
+  // a load is queued long BEFORE the reductions of the steps in between and is not stuck behind
+  // them in the SM's memory pipeline.
+  constexpr int R = kRingSlots;
+  auto request = [&](int j, uint4* slot) {
+    const bool ok = active && j >= 0 && j < n;
+    const int id = j >= 0 ? mine[j].x : 0;
 #ifndef FLEXSAE_EXPERIMENT_NO_LOADS
-      cp_async16(ring + (half * U + u) * kThreads, wcol + (size_t)id * row_bytes, ok ? 16 : 0);
+    cp_async16(slot, wcol + (size_t)id * row_bytes, ok ? 16 : 0);
 #else
-      cp_async16(ring + (half * U + u) * kThreads, wcol + (size_t)(id & 1) * row_bytes, ok ? 16 : 0);
+    cp_async16(slot, wcol + (size_t)(id & 1) * row_bytes, ok ? 16 : 0);
 #endif
-    }
-    cp_async_commit();
+    cp_async_commit();  // one group per step (possibly empty) keeps the wait arithmetic uniform
   };
-  issue_batch(KS - 1, 0);
-  issue_batch(KS - 1 - U, 1);
-  int half = 0;
-  for (int jb = KS - 1; jb >= 0; jb -= U, half ^= 1) {  // KS is a multiple of U
-    cp_async_wait<1>();  // all but the newest group have landed: this batch is in the ring
+#pragma unroll
+  for (int q = 0; q < R; q++) request(KS - 1 - q, ring + q * kThreads);
+  uint4* slot = ring;
+  int slot_no = 0;
+  for (int jb = KS - 1; jb >= 0; jb -= U) {  // KS is a multiple of U
     int2 e[U];
 #pragma unroll
     for (int u = 0; u < U; u++) e[u] = mine[jb - u];
@@ -447,7 +448,14 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
       const float c = v * coef;
       const float2 cc = make_float2(c, c), nv = make_float2(-v, -v);
       float2 wf[H];
-      Pack<T>::unpack_pairs(ring[(half * U + u) * kThreads], wf);
+      cp_async_wait<R - 1>();  // at most R-1 newer requests pending: this step's piece has landed
+      Pack<T>::unpack_pairs(*slot, wf);
+      request(jb - u - R, slot);
+      slot += kThreads;
+      if (++slot_no == R) {
+        slot_no = 0;
+        slot = ring;
+      }
       if (HIER && in_seg) {
 #pragma unroll
         for (int h = 0; h < H; h++) suf[h] = add2(suf[h], r[h]);  // S_k = sum_{j>=k} residual_j
@@ -479,7 +487,6 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
         for (int h = 0; h < H; h++) r[h] = fma2(nv, wf[h], r[h]);  // step back to prefix k-1
       }
     }
-    issue_batch(jb - 2 * U, half);  // refill the half just consumed (an empty group past the end)
     const float tot = group_sum8<G>(d, lig);
     const int j = jb - (lig & 7);
     if (live && lig < 8 && j < n) dv[j] = tot * coef;
@@ -644,7 +651,7 @@ static int check_shape(int kind, const Shape& s, int wdt) {
   if (s.F > (1ll << 30) || s.D > (1ll << 20) || s.B > (1ll << 27) || s.B * s.K > (1ll << 31) - 1)
     return fail(FLEXSAE_EUNSUPPORTED, "shape too large for 32-bit row/position arithmetic");
   // indices, vals (and sorted slots) of a CTA's rows are staged in shared memory next to the
-  // 32 KiB row-piece ring: 16 rows * K * 12 bytes must fit
+  // row-piece ring: 16 rows * K * 12 bytes must fit
   if (s.K > 960) return fail(FLEXSAE_EUNSUPPORTED, "K=%lld above the supported maximum of 960", (long long)s.K);
   return 0;
 }
@@ -756,7 +763,7 @@ static FwdPlan plan_fwd(const Shape& s, int wdt) {
   return p;
 }
 
-constexpr size_t kRingBytes = (size_t)kRingSlots * kThreads * sizeof(uint4);  // 32 KiB per CTA
+constexpr size_t kRingBytes = (size_t)kRingSlots * kThreads * sizeof(uint4);  // 2 KiB per slot and CTA
 
 template <typename K>
 static cudaError_t allow_smem(K kern, size_t smem) {
