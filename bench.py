@@ -33,9 +33,9 @@ sys.path.insert(0, ROOT)
 from flexsae_b200.workloads import CONFIGS, algorithmic_bytes, make_inputs  # noqa: E402
 
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
-# dram__bytes_read + dram__bytes_write per launch of the dominant kernel, from the ncu capture
-# summarised under profiles/ (None until a capture of this build exists)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read + dram__bytes_write per launch of the dominant kernel at the headline workload,
+# from the ncu capture summarised in profiles/bench_c3_k128_hier_launch_list.md
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {("c3_k128", "hier", "atomic"): 3213.1e6}
 
 
 def hbm_peak():
@@ -328,10 +328,10 @@ def main():
                              "library's own fp32 gradient slabs are meant to stay L2-resident between launches"},
             "hbm_gbs": alg / (ms_per_step * 1e-3) / 1e9,
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
-            "roofline": {"bound": "hbm", "kernel": "decoder_loss_bwd_kernel (all launches of one backward)",
+            "roofline": {"bound": "hbm", "kernel": "decoder_loss_bwd_pipelined_kernel (one launch per backward) + its two finalising kernels",
                          "achieved": alg_bwd / (bwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": alg_bwd / (bwd_ms * 1e-3) / 1e9 / peak, "peak_source": peak_kind,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((w.name, kind, args.dweight_mode))},
             "roofline_step": {"bound": "hbm", "achieved": alg / (ms_per_step * 1e-3) / 1e9, "peak": peak,
                               "unit": "GB/s", "frac": alg / (ms_per_step * 1e-3) / 1e9 / peak,
                               "algorithmic_bytes": alg},

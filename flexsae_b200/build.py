@@ -20,7 +20,7 @@ INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo", "--use_fast_math",
+    "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-shared",
 ]
 
@@ -45,7 +45,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: the CUDA library cannot be built on this machine")
     os.makedirs(LIB_DIR, exist_ok=True)
-    extra = os.environ.get("FLEXSAE_NVCC_EXTRA", "").split()      # e.g. -DFLEXSAE_BWD_MINB=8 while tuning
+    extra = os.environ.get("FLEXSAE_NVCC_EXTRA", "--use_fast_math").split()   # e.g. "-DFLEXSAE_BWD_MINB=8" while tuning
     cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-I", INCLUDE, "-o", LIB_PATH] + _sources()
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if verbose or res.returncode != 0:
