@@ -592,6 +592,235 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
   signal_done(pa.walk_done + p);
 }
 
+// ---- batch-sharded backward: pipelined kernel + dweight reduction over peer memory ----------------
+// Every rank (one GPU each, same node) runs this kernel on its own batch shard.  The converting
+// blocks of the single-launch pipeline do the cross-GPU sum of dweight themselves, piece by piece,
+// over NVLink peer loads, overlapped with the accumulation of the following pieces:
+//   slot p converts the local slab of piece p-1 into this rank's exchange buffer X (decoder dtype),
+//   reduce-scatters piece p-2: this rank sums ITS block of decoder rows over all ranks' X (fixed
+//     rank order, fp32) into its buffer Y and into its own dweight,
+//   all-gathers piece p-3: copies the other ranks' reduced row blocks from their Y into dweight.
+// One flag per (rank, peer) carries all cross-GPU ordering: when the last converting block of
+// slot p finishes, the rank publishes seq_base + p to every peer; the converting blocks of slot p
+// first wait until every peer has published slot p-1.  X and Y are double-buffered by piece
+// parity, and "peer finished slot p-1" is exactly what makes each buffer safe to read / reuse.
+// Waits are bounded like the local ones.  Plain peer loads/stores only: no multicast of any kind.
+constexpr int kMaxRanks = 8;
+struct ShardArgs {
+  PipeArgs p;
+  int* slot_done;  // [pieces + 3] converting blocks that finished ALL stages of a slot
+  int world, rank, rows_per_rank, seq_base;
+  void* x[kMaxRanks];        // rank s's X: [2][F][PW]
+  void* y[kMaxRanks];        // rank s's Y: [2][rows_per_rank][PW]
+  int* flags_at[kMaxRanks];  // flag array living on rank s; entry [r] = last slot rank r finished
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void wait_peers(const ShardArgs& sa, int target) {
+  if (threadIdx.x == 0) {
+    int32_t* status = sa.p.b.status;
+    const int* mine = sa.flags_at[sa.rank];
+    for (int s = 0; s < sa.world; s++) {  // this rank too: its own earlier slot reads the buffers this slot rewrites
+      int spins = 0;
+      while (ld_acquire_sys(mine + s) - target < 0) {  // difference: robust to wrap-around
+        __nanosleep(200);
+        ++spins;
+        const bool abandoned = status && (spins & 1023) == 0 &&
+                               (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+        if (spins > kSpinLimit || abandoned) {
+          if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// local slab (fp32, permuted columns) -> this rank's X[parity] in natural column order; clears the slab
+template <typename T, int G>
+__device__ __forceinline__ void slab_to_exchange(float* slab, T* x, int F, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = 4;
+  const size_t total = (size_t)F * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    float4 lo[IL], hi[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        lo[q] = __ldcg(reinterpret_cast<const float4*>(sp));
+        if (VEC == 8) hi[q] = __ldcg(reinterpret_cast<const float4*>(sp + G * 4));
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        *reinterpret_cast<float4*>(sp) = zero;
+        float v[8] = {lo[q].x, lo[q].y, lo[q].z, lo[q].w, 0.f, 0.f, 0.f, 0.f};
+        if (VEC == 8) {
+          *reinterpret_cast<float4*>(sp + G * 4) = zero;
+          v[4] = hi[q].x; v[5] = hi[q].y; v[6] = hi[q].z; v[7] = hi[q].w;
+        }
+        *reinterpret_cast<uint4*>(x + i * VEC) = Pack<T>::pack(v);  // item i = (row i / G, chunk i % G)
+      }
+    }
+  }
+}
+
+// this rank's row block of one piece: sum over all ranks' X in rank order -> Y (own) and dweight.
+// IL items per thread are in flight together (IL * world 16-byte peer loads) to cover NVLink latency.
+template <typename T, int G, int IL>
+__device__ __forceinline__ void reduce_row_block(const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int W = kMaxRanks / IL;  // largest world size this instantiation serves
+  const int F = sa.p.b.F, D = sa.p.b.D;
+  const int row0 = sa.rank * sa.rows_per_rank;
+  const int rows = max(0, min(F, row0 + sa.rows_per_rank) - row0);
+  const size_t total = (size_t)rows * G;
+  const size_t par_x = (size_t)(piece & 1) * F * PW;
+  const size_t stride = (size_t)nctas * kThreads;
+  T* yown = reinterpret_cast<T*>(sa.y[sa.rank]) + (size_t)(piece & 1) * sa.rows_per_rank * PW;
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    uint4 in[IL][W];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      const size_t off = par_x + ((size_t)row0 * G + i) * VEC;
+#pragma unroll
+      for (int s = 0; s < W; s++)
+        if (i < total && s < sa.world) in[q][s] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(sa.x[s]) + off));
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float acc[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; j++) acc[j] = 0.f;
+#pragma unroll
+        for (int s = 0; s < W; s++)
+          if (s < sa.world) {
+            float f[VEC];
+            Pack<T>::unpack(in[q][s], f);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) acc[j] += f[j];
+          }
+        const uint4 out = Pack<T>::pack(acc);
+        *reinterpret_cast<uint4*>(yown + i * VEC) = out;
+        const int col = piece * PW + (int)(i % G) * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)(row0 + i / G) * D + col) = out;
+      }
+    }
+  }
+}
+
+// the other ranks' reduced row blocks of one piece: their Y -> this rank's dweight
+template <typename T, int G>
+__device__ __forceinline__ void gather_row_blocks(const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = 4;
+  const int F = sa.p.b.F, D = sa.p.b.D;
+  const size_t per_rank = (size_t)sa.rows_per_rank * G;  // items per rank block (last one may be short)
+  const size_t total = per_rank * (sa.world - 1);
+  const size_t stride = (size_t)nctas * kThreads;
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    uint4 v[IL];
+    int row[IL], chunk[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      row[q] = -1;
+      if (i < total) {
+        int s = (int)(i / per_rank);
+        const size_t w = i - (size_t)s * per_rank;
+        if (s >= sa.rank) s++;  // skip this rank's own block
+        const int r = s * sa.rows_per_rank + (int)(w / G);
+        if (r < F) {
+          row[q] = r;
+          chunk[q] = (int)(w % G);
+          const T* src = reinterpret_cast<const T*>(sa.y[s]) + (size_t)(piece & 1) * sa.rows_per_rank * PW + w * VEC;
+          v[q] = __ldcg(reinterpret_cast<const uint4*>(src));
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      if (row[q] >= 0) {
+        const int col = piece * PW + chunk[q] * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)row[q] * D + col) = v[q];
+      }
+    }
+  }
+}
+
+template <typename T, int G, bool HIER>
+__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_kernel(const ShardArgs sa) {
+  extern __shared__ uint4 smem[];
+  const PipeArgs& pa = sa.p;
+  constexpr int PW = G * Pack<T>::VEC;
+  const int per = pa.unit_blocks + pa.conv_blocks;
+  const int body = pa.pieces * per;
+  int p, conv_idx = -1, unit_block = -1;
+  if ((int)blockIdx.x >= body) {  // three draining slots of converting blocks only
+    const int t = blockIdx.x - body;
+    p = pa.pieces + t / pa.conv_blocks;
+    conv_idx = t - (p - pa.pieces) * pa.conv_blocks;
+  } else {
+    p = blockIdx.x / per;
+    const int r = blockIdx.x - p * per;
+    if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) conv_idx = r - pa.conv_offset;
+    else unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
+  }
+  if (conv_idx >= 0) {
+    const int P = pa.pieces;
+    if (p >= 1 && p - 1 < P) wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);
+    if (p >= 1) wait_peers(sa, sa.seq_base + p - 1);
+    // The slab first: the unit blocks of piece p+1 are waiting for it to be cleared.
+    if (p >= 1 && p - 1 < P)
+      slab_to_exchange<T, G>(pa.slabs[(p - 1) & 1],
+                             reinterpret_cast<T*>(sa.x[sa.rank]) + (size_t)((p - 1) & 1) * pa.b.F * PW, pa.b.F, conv_idx,
+                             pa.conv_blocks);
+    signal_done(pa.conv_done + p);
+    if (p >= 2 && p - 2 < P) {
+      if (sa.world <= 2) reduce_row_block<T, G, 4>(sa, p - 2, conv_idx, pa.conv_blocks);
+      else if (sa.world <= 4) reduce_row_block<T, G, 2>(sa, p - 2, conv_idx, pa.conv_blocks);
+      else reduce_row_block<T, G, 1>(sa, p - 2, conv_idx, pa.conv_blocks);
+    }
+    if (p >= 3 && p - 3 < P) gather_row_blocks<T, G>(sa, p - 3, conv_idx, pa.conv_blocks);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence_system();  // this block's X / Y / dweight writes before the count moves
+      const int old = atomicAdd(sa.slot_done + p, 1);
+      if (old == pa.conv_blocks - 1) {  // the whole slot is done on this rank: tell every rank
+        __threadfence_system();
+        for (int s = 0; s < sa.world; s++) st_release_sys(sa.flags_at[s] + sa.rank, sa.seq_base + p);
+      }
+    }
+    return;
+  }
+  if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status);  // slot p-1 cleared this slab
+  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
+  signal_done(pa.walk_done + p);
+}
+
 // Column sums of a [B, D] fp32 matrix over row blocks: part[rb][d] = sum of rows of block rb.
 // dbias is coef * (column sums of the final residual (TopK) / of the summed prefix residuals).
 __global__ void __launch_bounds__(128) column_sums_kernel(const float* __restrict__ x, int B, int D, int rows_per_block,
@@ -743,7 +972,7 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   p.off_s0 = off;  // summed prefix residuals of every row (Hierarchical; TopK does not use it)
   off = align_up(off + (size_t)s.B * s.D * 4, 256);
   p.off_ctr = off;  // per-piece completion counters of the single-launch pipeline
-  off = align_up(off + (size_t)2 * p.pieces * 4, 256);
+  off = align_up(off + (size_t)(3 * p.pieces + 6) * 4, 256);
   p.total = off;
   return p;
 }
@@ -850,6 +1079,35 @@ static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* s
   const long long blocks = (long long)pieces * (pa.unit_blocks + conv) + conv;
   if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
   kern<<<(unsigned)blocks, kThreads, smem, st>>>(pa);
+  t_launches++;
+  return cudaGetLastError();
+}
+
+template <typename T, int G, bool HIER>
+static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
+                                      ShardArgs sa, cudaStream_t st) {
+  constexpr int UPC = groups_per_cta(G);
+  const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
+  auto kern = decoder_loss_bwd_sharded_kernel<T, G, HIER>;
+  if (cudaError_t e = allow_smem(kern, smem)) return e;
+  PipeArgs& pa = sa.p;
+  pa.b = b;
+  pa.slabs[0] = slab0;
+  pa.slabs[1] = slab1;
+  pa.walk_done = counters;
+  pa.conv_done = counters + pieces;       // one counter per slot: pieces + 3 of them
+  sa.slot_done = counters + 2 * pieces + 3;  // and pieces + 3 more
+  pa.pieces = pieces;
+  const long long units = (long long)b.B * b.NS;
+  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
+  const long long items = (long long)b.F * G;
+  int conv = (int)((items + kThreads * 4 - 1) / (kThreads * 4));
+  if (conv > kConvertBlocks) conv = kConvertBlocks;
+  pa.conv_blocks = conv;
+  pa.conv_offset = (int)((long long)pa.unit_blocks * g_opt.convert_offset_pct / 100);
+  const long long blocks = (long long)pieces * (pa.unit_blocks + conv) + 3ll * conv;
+  if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
   t_launches++;
   return cudaGetLastError();
 }
@@ -970,10 +1228,21 @@ int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const
   return 0;
 }
 
-int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const void* vals, const float* state,
-                     int segments, const float* grad_out, void* dweight, void* dvals, void* dbias, void* workspace,
-                     size_t workspace_bytes, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
-                     int vals_dtype, int bias_dtype, double inv_norm, int dw_mode, int32_t* status, void* stream) {
+}  // extern "C"
+
+namespace flexsae {
+struct PeerInfo {  // batch-sharded call: who the other GPUs are and where their exchange buffers live
+  int world, rank, seq_base;
+  void* const* x;
+  void* const* y;
+  void* const* flags;
+};
+
+static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, const void* vals, const float* state,
+                         int segments, const float* grad_out, void* dweight, void* dvals, void* dbias, void* workspace,
+                         size_t workspace_bytes, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
+                         int vals_dtype, int bias_dtype, double inv_norm, int dw_mode, int32_t* status, void* stream,
+                         const PeerInfo* peers) {
   t_launches = 0;
   Shape s{B, K, F, D};
   if (int rc = check_shape(kind, s, weight_dtype)) return rc;
@@ -1037,9 +1306,31 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   // one more launch converts the last piece.
   e = cudaMemsetAsync(slabs[0], 0, 2 * p.slab_bytes, st);
   if (e != cudaSuccess) return fail((int)e, "slab clear failed: %s", cudaGetErrorString(e));
-  if (g_opt.pipeline) {
+  if (peers) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
-    e = cudaMemsetAsync(counters, 0, (size_t)2 * p.pieces * 4, st);
+    e = cudaMemsetAsync(counters, 0, (size_t)(3 * p.pieces + 6) * 4, st);
+    if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
+    a.piece = a.conv_piece = -1;
+    a.slab = a.conv_slab = nullptr;
+    a.unit_blocks = a.conv_blocks = 0;
+    a.conv_stride = 1;
+    ShardArgs sa;
+    sa.world = peers->world;
+    sa.rank = peers->rank;
+    sa.seq_base = peers->seq_base;
+    sa.rows_per_rank = (int)((F + peers->world - 1) / peers->world);
+    for (int r = 0; r < kMaxRanks; r++) {
+      sa.x[r] = r < peers->world ? peers->x[r] : nullptr;
+      sa.y[r] = r < peers->world ? peers->y[r] : nullptr;
+      sa.flags_at[r] = r < peers->world ? reinterpret_cast<int*>(peers->flags[r]) : nullptr;
+    }
+#define CALL_SHARD(T, G, H) launch_bwd_sharded<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, sa, st)
+    e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD);
+#undef CALL_SHARD
+    if (e != cudaSuccess) return fail((int)e, "sharded backward launch failed: %s", cudaGetErrorString(e));
+  } else if (g_opt.pipeline) {
+    int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
+    e = cudaMemsetAsync(counters, 0, (size_t)(3 * p.pieces + 6) * 4, st);
     if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
     a.piece = a.conv_piece = -1;
     a.slab = a.conv_slab = nullptr;
@@ -1079,6 +1370,57 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
   e = cudaGetLastError();
   if (e != cudaSuccess) return fail((int)e, "gradient finalize launch failed: %s", cudaGetErrorString(e));
   return 0;
+}
+}  // namespace flexsae
+
+extern "C" {
+
+int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const void* vals, const float* state,
+                     int segments, const float* grad_out, void* dweight, void* dvals, void* dbias, void* workspace,
+                     size_t workspace_bytes, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
+                     int vals_dtype, int bias_dtype, double inv_norm, int dw_mode, int32_t* status, void* stream) {
+  return loss_bwd_impl(kind, indices, weight, vals, state, segments, grad_out, dweight, dvals, dbias, workspace,
+                       workspace_bytes, B, K, F, D, weight_dtype, vals_dtype, bias_dtype, inv_norm, dw_mode, status,
+                       stream, nullptr);
+}
+
+int flexsae_shard_buffer_bytes(int64_t F, int64_t D, int weight_dtype, int world, size_t* x_bytes, size_t* y_bytes,
+                               size_t* flag_bytes) {
+  Shape s{1, 1, F, D};
+  if (int rc = check_shape(FLEXSAE_HIER, s, weight_dtype)) return rc;
+  if (world < 2 || world > kMaxRanks) return fail(FLEXSAE_EINVAL, "world size %d outside [2, %d]", world, kMaxRanks);
+  if (!x_bytes || !y_bytes || !flag_bytes) return fail(FLEXSAE_EINVAL, "null pointer argument");
+  const BwdPlan p = plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC);
+  const size_t rows_per_rank = (size_t)((F + world - 1) / world);
+  *x_bytes = align_up(2 * (size_t)F * p.PW * dtype_size(weight_dtype), 256);
+  *y_bytes = align_up(2 * rows_per_rank * p.PW * dtype_size(weight_dtype), 256);
+  *flag_bytes = 256;
+  return 0;
+}
+
+int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weight, const void* vals,
+                             const float* state, int segments, const float* grad_out, void* dweight, void* dvals,
+                             void* dbias, void* workspace, size_t workspace_bytes, int64_t B, int64_t K, int64_t F,
+                             int64_t D, int weight_dtype, int vals_dtype, int bias_dtype, double inv_norm,
+                             int32_t* status, void* stream, int world, int rank, int seq_base, void* const* x_ptrs,
+                             void* const* y_ptrs, void* const* flag_ptrs) {
+  if (world < 2 || world > kMaxRanks) return fail(FLEXSAE_EINVAL, "world size %d outside [2, %d]", world, kMaxRanks);
+  if (rank < 0 || rank >= world) return fail(FLEXSAE_EINVAL, "rank %d outside [0, %d)", rank, world);
+  if (!x_ptrs || !y_ptrs || !flag_ptrs) return fail(FLEXSAE_EINVAL, "null pointer argument");
+  for (int r = 0; r < world; r++)
+    if (!x_ptrs[r] || !y_ptrs[r] || !flag_ptrs[r] || !aligned16(x_ptrs[r]) || !aligned16(y_ptrs[r]))
+      return fail(FLEXSAE_EINVAL, "exchange buffer of rank %d is null or not 16-byte aligned", r);
+  if (seq_base < 1) return fail(FLEXSAE_EINVAL, "seq_base must be >= 1");
+  PeerInfo peers{world, rank, seq_base, x_ptrs, y_ptrs, flag_ptrs};
+  return loss_bwd_impl(kind, indices, weight, vals, state, segments, grad_out, dweight, dvals, dbias, workspace,
+                       workspace_bytes, B, K, F, D, weight_dtype, vals_dtype, bias_dtype, inv_norm, FLEXSAE_DW_ATOMIC,
+                       status, stream, &peers);
+}
+
+int flexsae_shard_slots(int64_t F, int64_t D, int weight_dtype) {
+  Shape s{1, 1, F, D};
+  if (check_shape(FLEXSAE_HIER, s, weight_dtype)) return 0;
+  return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC).pieces + 3;
 }
 
 // ---- forward for callers that cannot provide scratch memory ------------------------------------

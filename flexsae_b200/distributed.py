@@ -4,14 +4,18 @@ The reference is single-GPU.  Here every rank holds a shard of the batch rows
 (``indices``, ``vals``, ``target``) and a full replica of the decoder (``weight``, ``bias``).
 Each rank runs the ordinary fused kernels on its rows with the GLOBAL normaliser
 1/(B_global*D) resp. 1/(B_global*K*D), so its loss is its additive share of the global mean and
-its gradients are its additive share of the global gradients; one all-reduce(sum) of the scalar
-loss in the forward and of ``dweight`` and ``dbias`` in the backward (NCCL over NVLink) gives
-every rank exactly what a single GPU would have computed on the whole batch, up to summation
-order.  ``dvals`` belongs to the local rows and needs no exchange.
+its gradients are its additive share of the global gradients.  The scalar loss and ``dbias`` (D
+values) are all-reduced with NCCL.  The dense ``dweight`` table is summed over the ranks INSIDE the
+backward kernel: its converting blocks reduce-scatter and all-gather each finished column piece over
+NVLink peer loads while the next pieces are still being accumulated
+(``flexsae_loss_bwd_sharded``), so no separate all-reduce of the [F, D] gradient is exposed.
+``config.peer_reduce = False`` falls back to an NCCL all-reduce of ``dweight`` after the backward.
+``dvals`` belongs to the local rows and needs no exchange.
 """
 from __future__ import annotations
 
-from typing import Callable, Optional, Tuple
+import ctypes
+from typing import Callable, Dict, Optional, Tuple
 
 import torch
 import torch.distributed as dist
@@ -22,6 +26,60 @@ from . import losses as _losses
 # (forward, backward) of one shard; replaceable so that the exchange logic can be exercised on
 # CPU ranks (gloo) with any implementation of the local math.
 LocalImpl = Tuple[Callable, Callable]
+
+
+class config:
+    #: sum dweight over the ranks inside the backward kernel (NVLink peer memory) instead of an
+    #: NCCL all-reduce afterwards
+    peer_reduce: bool = True
+
+
+class PeerExchange:
+    """Symmetric exchange buffers of one (process group, device, decoder shape, dtype): every
+    rank's X / Y / flag buffers mapped into every process, plus the running sequence number."""
+
+    def __init__(self, group, device: torch.device, F: int, D: int, dtype: torch.dtype):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        lib = nv.load()
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        wdt = nv.DTYPE_CODES[dtype]
+        xb, yb, fb = ctypes.c_size_t(), ctypes.c_size_t(), ctypes.c_size_t()
+        nv.check(lib.flexsae_shard_buffer_bytes(F, D, wdt, self.world, ctypes.byref(xb), ctypes.byref(yb),
+                                                ctypes.byref(fb)), "flexsae_shard_buffer_bytes")
+        self.slots = lib.flexsae_shard_slots(F, D, wdt)
+        with torch.cuda.device(device):
+            self.buffer = symm_mem.empty(xb.value + yb.value + fb.value, dtype=torch.uint8, device=device)
+            self.buffer.zero_()
+            self.handle = symm_mem.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+            torch.cuda.synchronize(device)
+        dist.barrier(group)            # every rank's flags are zero before anyone can publish
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        arr = ctypes.c_void_p * self.world
+        self.x = arr(*ptrs)
+        self.y = arr(*[p + xb.value for p in ptrs])
+        self.flags = arr(*[p + xb.value + yb.value for p in ptrs])
+        self.seq = 1
+
+    def next_seq(self) -> int:
+        seq = self.seq
+        self.seq += self.slots
+        return seq
+
+
+_exchanges: Dict[tuple, PeerExchange] = {}
+
+
+def peer_exchange(group, device: torch.device, F: int, D: int, dtype: torch.dtype) -> PeerExchange:
+    """The exchange buffers for this shape, created on first use (a collective: every rank of the
+    group must get here together, which they do when they run the same training step)."""
+    key = (id(group) if group is not None else 0, device.index, F, D, dtype,
+           nv.get_option("lanes_bwd"), nv.get_option("l2_budget_mb"))
+    ex = _exchanges.get(key)
+    if ex is None:
+        ex = _exchanges[key] = PeerExchange(group, device, F, D, dtype)
+    return ex
 
 
 def _fused_local_forward(kind, indices, weight, vals, bias, target, inv_norm):
@@ -35,6 +93,14 @@ def _fused_local_backward(kind, ctx_saved, grad, bias_dtype, inv_norm):
 
 
 FUSED_IMPL: LocalImpl = (_fused_local_forward, _fused_local_backward)
+
+
+def _fused_backward_with_peer_reduce(kind, ctx_saved, grad, bias_dtype, inv_norm, group):
+    """Backward of this rank's shard; dweight comes back already summed over the group."""
+    idx_c, w_c, v_c, saved = ctx_saved
+    ex = peer_exchange(group, w_c.device, w_c.shape[0], w_c.shape[1], w_c.dtype)
+    return _losses.fused_backward(kind, idx_c, w_c, v_c, saved, grad, bias_dtype, inv_norm, dweight_mode="atomic",
+                                  peers=ex)
 
 
 class _ShardedDecoderLoss(torch.autograd.Function):
@@ -54,10 +120,16 @@ class _ShardedDecoderLoss(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         _, bwd = ctx.impl
-        dweight, dvals, dbias = bwd(ctx.kind, ctx.saved, grad, ctx.bias_dtype, ctx.inv_norm)
+        world = dist.get_world_size(ctx.group)
+        fused_peer = (ctx.impl is FUSED_IMPL and config.peer_reduce and 2 <= world <= 8
+                      and _losses.config.dweight_mode == "atomic")
+        if fused_peer:
+            dweight, dvals, dbias = _fused_backward_with_peer_reduce(ctx.kind, ctx.saved, grad, ctx.bias_dtype,
+                                                                     ctx.inv_norm, ctx.group)
+        else:
+            dweight, dvals, dbias = bwd(ctx.kind, ctx.saved, grad, ctx.bias_dtype, ctx.inv_norm)
+            dist.all_reduce(dweight, op=dist.ReduceOp.SUM, group=ctx.group)
         ctx.saved = None
-        # The dense table first: it is the long transfer; the small one rides behind it.
-        dist.all_reduce(dweight, op=dist.ReduceOp.SUM, group=ctx.group)
         dist.all_reduce(dbias, op=dist.ReduceOp.SUM, group=ctx.group)
         return None, None, None, None, None, dweight, dvals, dbias, None
 

@@ -139,8 +139,9 @@ def fused_forward(kind: int, indices, weight, vals, bias, target, inv_norm: floa
 
 
 def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype, inv_norm: float = 0.0,
-                   dweight_mode: Optional[str] = None):
-    """Runs the backward kernels; returns (dweight, dvals, dbias) in the parameters' dtypes."""
+                   dweight_mode: Optional[str] = None, peers=None):
+    """Runs the backward kernels; returns (dweight, dvals, dbias) in the parameters' dtypes.
+    With ``peers`` (a ``distributed.PeerExchange``) dweight is summed over the ranks in-kernel."""
     B, K = indices.shape
     F, D = weight.shape
     state, segments = saved
@@ -158,10 +159,17 @@ def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype
         dvals = torch.empty((B, K), dtype=vals.dtype, device=dev)
         dbias = torch.empty((D,), dtype=bias_dtype, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        rc = lib.flexsae_loss_bwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(state), segments, _ptr(go),
-                                  _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(), B, K, F, D, wdt,
-                                  nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype], float(inv_norm), mode,
-                                  _ptr(_status_word(dev)), stream)
+        if peers is not None:
+            rc = lib.flexsae_loss_bwd_sharded(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(state), segments,
+                                              _ptr(go), _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(),
+                                              B, K, F, D, wdt, nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype],
+                                              float(inv_norm), _ptr(_status_word(dev)), stream, peers.world,
+                                              peers.rank, peers.next_seq(), peers.x, peers.y, peers.flags)
+        else:
+            rc = lib.flexsae_loss_bwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(state), segments, _ptr(go),
+                                      _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(), B, K, F, D, wdt,
+                                      nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype], float(inv_norm), mode,
+                                      _ptr(_status_word(dev)), stream)
         nv.check(rc, "flexsae_loss_bwd")
         global launch_count
         launch_count += lib.flexsae_last_launch_count()

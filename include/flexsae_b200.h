@@ -128,6 +128,33 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
                      int bias_dtype, double inv_norm, int dw_mode, int32_t* status, void* stream);
 
 /*
+ * Backward of one batch shard with the cross-GPU sum of dweight done inside the same kernel, over
+ * NVLink peer memory (2..8 GPUs of one node, one process per GPU, decoder replicated).  Every rank
+ * calls it with its own rows and the GLOBAL inv_norm; on return (stream order) dweight holds the sum
+ * over all ranks, dvals the local rows' gradient, dbias the LOCAL share (sum it with any collective:
+ * it is D values).  The reference has no counterpart (it is single-GPU); in a data-parallel run it
+ * replaces flexsae_loss_bwd followed by an all-reduce of the dense [F,D] gradient.
+ *   x_ptrs / y_ptrs / flag_ptrs   host arrays of `world` DEVICE pointers, entry r = rank r's
+ *       exchange buffers, each mapped into this process (CUDA IPC / symmetric memory), of the
+ *       sizes flexsae_shard_buffer_bytes answers; the flag buffers must be zero before the first call
+ *   seq_base   first call: 1; every later call on the same buffers: previous seq_base +
+ *       flexsae_shard_slots(F, D, weight_dtype); identical on all ranks
+ * Only FLEXSAE_DW_ATOMIC accumulation.  All ranks must issue the same sequence of calls.  Waits on
+ * other GPUs are bounded; if one gives up, FLEXSAE_STATUS_PIPELINE_TIMEOUT is set in `status` and the
+ * gradients of that call are invalid.
+ */
+int flexsae_shard_buffer_bytes(int64_t F, int64_t D, int weight_dtype, int world, size_t* x_bytes,
+                               size_t* y_bytes, size_t* flag_bytes);
+int flexsae_shard_slots(int64_t F, int64_t D, int weight_dtype);
+int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weight, const void* vals,
+                             const float* state, int segments, const float* grad_out, void* dweight,
+                             void* dvals, void* dbias, void* workspace, size_t workspace_bytes,
+                             int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
+                             int vals_dtype, int bias_dtype, double inv_norm, int32_t* status,
+                             void* stream, int world, int rank, int seq_base, void* const* x_ptrs,
+                             void* const* y_ptrs, void* const* flag_ptrs);
+
+/*
  * flexsae_loss_fwd for callers that must not allocate device memory.  It has no counterpart in
  * the reference (whose launchers allocate with torch on every call).
  *

@@ -10,15 +10,17 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, kind, q):
+def _worker(rank, world, port, kind, q, peer_reduce=True):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
+        import flexsae_b200 as fx
         from flexsae_b200 import distributed as fd
         from flexsae_b200.workloads import CONFIGS, make_inputs
+        fd.config.peer_reduce = peer_reduce
         w = CONFIGS["c3_k32"].replace(B=768, F=8192)
         rows = w.B // world
         x = make_inputs(w, f"cuda:{rank}", row0=rank * rows, rows=rows)
@@ -26,16 +28,20 @@ def _worker(rank, world, port, kind, q):
         vals = x["vals"].requires_grad_(True)
         bias = x["bias"].requires_grad_(True)
         fn = fd.sharded_hierarchical_sae_loss if kind == "hier" else fd.sharded_topk_sae_loss
-        loss = fn(x["indices"], weight, vals, bias, x["target"])
-        loss.backward(x["grad_out"])
+        for _ in range(3):          # several steps in a row on the same exchange buffers
+            weight.grad = vals.grad = bias.grad = None
+            loss = fn(x["indices"], weight, vals, bias, x["target"])
+            loss.backward(x["grad_out"])
         torch.cuda.synchronize()
+        fx.check_status()
         q.put((rank, float(loss), weight.grad.float().cpu(), vals.grad.float().cpu(), bias.grad.float().cpu()))
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("peer_reduce", [True, False], ids=["peer_memory", "nccl"])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
-def test_two_gpu_shards_match_one_gpu(kind):
+def test_two_gpu_shards_match_one_gpu(kind, peer_reduce):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -47,7 +53,8 @@ def test_two_gpu_shards_match_one_gpu(kind):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, kind, q)) for r in range(2)]
+    port += 13 if peer_reduce else 0
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, kind, q, peer_reduce)) for r in range(2)]
     for p in procs:
         p.start()
     outs = sorted([q.get(timeout=300) for _ in procs], key=lambda o: o[0])
