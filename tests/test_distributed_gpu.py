@@ -1,5 +1,5 @@
-"""GPU, 2 ranks over NCCL (skipped with fewer than 2 GPUs): batch-sharded fused losses against
-the single-GPU fused result on the whole batch."""
+"""GPU, 2 ranks (and, when the box has more, as many ranks as GPUs) over NVLink: batch-sharded
+fused losses against the single-GPU fused result on the whole batch.  Skipped with one GPU."""
 import os
 import sys
 
@@ -21,7 +21,7 @@ def _worker(rank, world, port, kind, q, peer_reduce=True):
         from flexsae_b200 import distributed as fd
         from flexsae_b200.workloads import CONFIGS, make_inputs
         fd.config.peer_reduce = peer_reduce
-        w = CONFIGS["c3_k32"].replace(B=768, F=8192)
+        w = CONFIGS["c3_k32"].replace(B=768, F=8190)       # F not a multiple of the world size
         rows = w.B // world
         x = make_inputs(w, f"cuda:{rank}", row0=rank * rows, rows=rows)
         weight = x["weight"].requires_grad_(True)
@@ -39,11 +39,17 @@ def _worker(rank, world, port, kind, q, peer_reduce=True):
         dist.destroy_process_group()
 
 
+def _worlds():
+    n = torch.cuda.device_count() if torch.cuda.is_available() else 0
+    return sorted({2, min(n, 8)}) if n > 2 else [2]
+
+
+@pytest.mark.parametrize("world", _worlds())
 @pytest.mark.parametrize("peer_reduce", [True, False], ids=["peer_memory", "nccl"])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
-def test_two_gpu_shards_match_one_gpu(kind, peer_reduce):
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
 
     import flexsae_b200 as fx
@@ -54,7 +60,8 @@ def test_two_gpu_shards_match_one_gpu(kind, peer_reduce):
     q = ctx.Queue()
     port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
     port += 13 if peer_reduce else 0
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, kind, q, peer_reduce)) for r in range(2)]
+    port += 29 * world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce)) for r in range(world)]
     for p in procs:
         p.start()
     outs = sorted([q.get(timeout=300) for _ in procs], key=lambda o: o[0])
@@ -62,7 +69,7 @@ def test_two_gpu_shards_match_one_gpu(kind, peer_reduce):
         p.join(timeout=120)
         assert p.exitcode == 0
 
-    w = CONFIGS["c3_k32"].replace(B=768, F=8192)
+    w = CONFIGS["c3_k32"].replace(B=768, F=8190)
     x = make_inputs(w, "cuda:0")
     weight = x["weight"].requires_grad_(True)
     vals = x["vals"].requires_grad_(True)
@@ -70,9 +77,9 @@ def test_two_gpu_shards_match_one_gpu(kind, peer_reduce):
     fn = fx.triton_hierarchical_sae_loss if kind == "hier" else fx.triton_topk_sae_loss
     loss = fn(x["indices"], weight, vals, bias, x["target"])
     loss.backward(x["grad_out"])
-    rows = w.B // 2
+    rows = w.B // world
     for rank, l, dW, dv, db in outs:
         assert abs(l - float(loss)) <= 1e-6 * abs(float(loss))
-        assert rel_err(dW.numpy(), weight.grad.float().cpu().numpy()) < 1e-2      # bf16 sum of two bf16 shards
+        assert rel_err(dW.numpy(), weight.grad.float().cpu().numpy()) < 1e-2      # bf16 sum of bf16 shards
         assert rel_err(db.numpy(), bias.grad.float().cpu().numpy()) < 1e-2
         assert torch.equal(dv, vals.grad.float().cpu()[rank * rows:(rank + 1) * rows])
