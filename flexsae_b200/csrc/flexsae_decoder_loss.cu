@@ -55,6 +55,12 @@ static size_t dtype_size(int dt) { return dt == FLEXSAE_F32 ? 4 : 2; }
 static bool dtype_ok(int dt) { return dt == FLEXSAE_F32 || dt == FLEXSAE_BF16 || dt == FLEXSAE_F16; }
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
+#ifndef FLEXSAE_CONVERT_BLOCKS
+#define FLEXSAE_CONVERT_BLOCKS (148 * 3)
+#endif
+#ifndef FLEXSAE_CONVERT_IL
+#define FLEXSAE_CONVERT_IL 4
+#endif
 #ifndef FLEXSAE_BWD_MINB
 #define FLEXSAE_BWD_MINB 6  // resident CTAs per SM the backward is compiled for (register cap 80)
 #endif
@@ -63,10 +69,7 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 #endif
 constexpr int kThreads = 128;  // 4 warps per CTA: 16 / 8 / 4 lane groups for G = 8 / 16 / 32
 constexpr int kUnroll = 8;     // decoder-row loads in flight per lane; segment lengths are multiples of it
-#ifndef FLEXSAE_RING
-#define FLEXSAE_RING 12
-#endif
-constexpr int kRingSlots = FLEXSAE_RING;  // backward: row pieces in flight per lane (shared-memory ring)
+constexpr int kRingSlots = 2 * kUnroll;  // backward: row pieces per lane in the shared-memory ring
 __host__ __device__ constexpr int groups_per_cta(int G) { return kThreads / G; }
 
 // Saved row state ("state" below), float32, written by the forward and read by the backward:
@@ -166,14 +169,23 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_k
   constexpr int PW = G * VEC;
   constexpr int RPC = groups_per_cta(G);
   constexpr int U = kUnroll;
-  extern __shared__ int2 staged[];  // [RPC][K]
+  constexpr int H = VEC / 2;
+  extern __shared__ int2 staged[];  // [RPC][Kp]: (decoder-row offset in 16-byte units, vals bits)
   const int K = a.K;
+  const int Kp = (K + U - 1) / U * U;  // padded to whole batches: padding = row 0 with vals 0
   const int row0 = blockIdx.x * RPC;
   const int piece = blockIdx.y;
-  for (int i = threadIdx.x; i < RPC * K; i += kThreads) {
-    const int b = row0 + i / K;
-    staged[i] = (b < a.B) ? stage_pair(a.indices, a.vals, a.vals_dtype, (size_t)row0 * K + i, a.F, a.status)
-                          : make_int2(0, 0);
+  const uint32_t row16 = (uint32_t)(((size_t)a.D * sizeof(T)) >> 4);
+  for (int i = threadIdx.x; i < RPC * Kp; i += kThreads) {
+    const int lr = i / Kp;
+    const int k = i - lr * Kp;
+    const int b = row0 + lr;
+    int2 e = make_int2(0, 0);
+    if (b < a.B && k < K) {
+      e = stage_pair(a.indices, a.vals, a.vals_dtype, (size_t)b * K + k, a.F, a.status);
+      e.x = (int)((uint32_t)e.x * row16);
+    }
+    staged[i] = e;
   }
   __syncthreads();
 
@@ -183,7 +195,6 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_k
   const int col = piece * PW + lig * VEC;
   const bool active = (b < a.B) && (col < a.D);
 
-  constexpr int H = VEC / 2;
   float2 r[H], acc[H], csum[H];
 #pragma unroll
   for (int h = 0; h < H; h++) r[h] = acc[h] = csum[h] = make_float2(0.f, 0.f);
@@ -195,36 +206,36 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_k
     for (int h = 0; h < H; h++) r[h] = make_float2(bv[2 * h] - tv[2 * h], bv[2 * h + 1] - tv[2 * h + 1]);
   }
 
-  const char* wcol = reinterpret_cast<const char*>(a.weight) + (size_t)col * sizeof(T);
-  const size_t row_bytes = (size_t)a.D * sizeof(T);
-  const int2* mine = staged + gid * K;
+  // lanes past the last column / row read column 0 of row 0 (valid memory) and never store
+  const uint4* wcol = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(a.weight) +
+                                                     (size_t)(active ? col : 0) * sizeof(T));
+  const int2* mine = staged + gid * Kp;
   float* st_r = a.state + (size_t)b * a.D + col;                          // + s * B * D per segment
   float* st_c = st_r + (size_t)a.NS * a.B * a.D;
   const size_t seg_stride = (size_t)a.B * a.D;
   int seg = 0, seg_end = a.KS;
 
-  for (int k0 = 0; k0 < K; k0 += U) {
+  for (int k0 = 0; k0 < Kp; k0 += U) {
     uint4 w[U];
-    int2 e[U];
+    float v[U];
 #pragma unroll
     for (int u = 0; u < U; u++) {
-      e[u] = (k0 + u < K) ? mine[k0 + u] : make_int2(0, 0);
-      w[u] = make_uint4(0u, 0u, 0u, 0u);
-      if (active && k0 + u < K) w[u] = ld_row_piece(wcol + (size_t)e[u].x * row_bytes);
+      const int2 e = mine[k0 + u];
+      v[u] = __int_as_float(e.y);
+      w[u] = ld_row_piece(wcol + (uint32_t)e.x);
     }
+    const bool full = k0 + U <= K;
 #pragma unroll
     for (int u = 0; u < U; u++) {
-      if (k0 + u < K) {
-        const float v = __int_as_float(e[u].y);
-        const float2 vv = make_float2(v, v);
-        float2 wf[H];
-        Pack<T>::unpack_pairs(w[u], wf);
+      const float2 vv = make_float2(v[u], v[u]);
+      float2 wf[H];
+      Pack<T>::unpack_pairs(w[u], wf);
+      const bool real = full || (k0 + u < K);  // padding steps leave r unchanged (vals 0) but must not be penalised
 #pragma unroll
-        for (int h = 0; h < H; h++) {
-          r[h] = fma2(vv, wf[h], r[h]);  // residual of the k-th prefix
-          if (HIER) acc[h] = fma2(r[h], r[h], acc[h]);  // every prefix is penalised
-          if (HIER && SEG) csum[h] = add2(csum[h], r[h]);
-        }
+      for (int h = 0; h < H; h++) {
+        r[h] = fma2(vv, wf[h], r[h]);  // residual of the k-th prefix
+        if (HIER && real) acc[h] = fma2(r[h], r[h], acc[h]);  // every prefix is penalised
+        if (HIER && SEG && real) csum[h] = add2(csum[h], r[h]);
       }
     }
     if (HIER && SEG && (k0 + U == seg_end) && (k0 + U < K)) {  // a segment ends inside the row
@@ -243,6 +254,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_FWD_MINB) decoder_loss_fwd_k
   float s = 0.f;
 #pragma unroll
   for (int h = 0; h < H; h++) s += acc[h].x + acc[h].y;
+  if (!active) s = 0.f;  // lanes past the last column worked on column 0's data: not part of the loss
   s = group_sum<G>(s);
   if (lig == 0 && b < a.B) a.loss_part[(size_t)piece * a.B + b] = s;
   if (active) {
@@ -300,7 +312,7 @@ __device__ __forceinline__ void convert_slab(float* slab, void* __restrict__ dwe
                                              int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
-  constexpr int IL = 4;  // independent items in flight per thread
+  constexpr int IL = FLEXSAE_CONVERT_IL;  // independent items in flight per thread
   const size_t total = (size_t)F * G;
   const size_t stride = (size_t)nctas * kThreads;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -338,6 +350,51 @@ __device__ __forceinline__ void convert_slab(float* slab, void* __restrict__ dwe
   }
 }
 
+// One step of the reverse walk for one lane: suffix += residual (skipped on padding steps),
+// dweight contribution, dvals dot, residual stepped back to the previous prefix.
+template <typename T, int G, bool HIER, bool DET, bool FULL>
+__device__ __forceinline__ float walk_step(const int2 e, int slot, const uint4 piece16, bool in_seg, bool active, float coef,
+                                           float2* r, float2* suf, float* slab, float* stage) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int H = VEC / 2;
+  constexpr int PW = G * VEC;
+  const float v = __int_as_float(e.y);
+  const float c = v * coef;
+  const float2 cc = make_float2(c, c), nv = make_float2(-v, -v);
+  float2 wf[H];
+  Pack<T>::unpack_pairs(piece16, wf);
+  if (HIER && (FULL || in_seg)) {
+#pragma unroll
+    for (int h = 0; h < H; h++) suf[h] = add2(suf[h], r[h]);  // S_k = sum_{j>=k} residual_j
+  }
+  if (active && (FULL || in_seg)) {
+    float2 g[H];
+#pragma unroll
+    for (int h = 0; h < H; h++) g[h] = mul2(suf[h], cc);
+    if (DET) {  // the contribution row goes to its sorted slot; it is added later, in slot order
+      float4* dst = reinterpret_cast<float4*>(stage + (size_t)(uint32_t)slot * PW);
+      __stcs(dst, make_float4(g[0].x, g[0].y, g[1].x, g[1].y));
+      if (VEC == 8) __stcs(dst + 1, make_float4(g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y));
+    } else {
+      float* dst = slab + (uint32_t)e.x * (uint32_t)PW;  // PW is a power of two: a shift
+#ifndef FLEXSAE_EXPERIMENT_NO_REDS
+      red_add_v4(dst, g[0].x, g[0].y, g[1].x, g[1].y);
+      if (VEC == 8) red_add_v4(dst + G * 4, g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y);
+#else
+      if (g[0].x == 1.2345e-30f) dst[0] = g[1].y + g[H - 1].x;
+#endif
+    }
+  }
+  float2 dot = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int h = 0; h < H; h++) dot = fma2(wf[h], suf[h], dot);
+  if (HIER) {
+#pragma unroll
+    for (int h = 0; h < H; h++) r[h] = fma2(nv, wf[h], r[h]);  // step back to prefix k-1 (v = 0 on padding)
+  }
+  return dot.x + dot.y;
+}
+
 // Slab column order: a lane's elements 0..3 live at column lig*4 and, for 8-element packs,
 // elements 4..7 at column G*4 + lig*4, so that each red.v4 instruction of a lane group covers
 // whole contiguous 32-byte sectors (a lane-contiguous 32-byte layout would make every sector
@@ -346,19 +403,29 @@ __device__ __forceinline__ void convert_slab(float* slab, void* __restrict__ dwe
 // One lane group owns one (batch row, K-segment) unit and walks the segment from its last k
 // down to its first: suffix += residual; dweight[idx] += vals * suffix; dvals = <row, suffix>;
 // residual -= vals * row  (the reverse walk of hierarchical_kernels.py:147-173).
+//
+// The (decoder row, vals) pair of every (unit, step) is staged once per CTA (8 bytes; the sorted
+// slot too in deterministic mode).  Padding steps (beyond K, or of a unit past the end) are staged
+// as row 0 with vals = 0 and fetch zeros: they contribute exact zeros, and only the suffix update
+// and the dvals store look at whether a step is real -- a whole batch of 8 real steps takes a path
+// without those tests.
 template <typename T, int G, bool HIER, bool DET>
 __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int piece, float* slab_base, uint4* smem) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
   constexpr int UPC = groups_per_cta(G);
   constexpr int U = kUnroll;
+  constexpr int H = VEC / 2;
+  static_assert(kRingSlots == 2 * kUnroll, "the ring holds the batch in use and the batch in flight");
   // Shared memory: a per-lane ring of 2*U row pieces (each lane only ever reads back the 16 bytes
-  // it copied itself, so no warp synchronisation is involved), then the staged (index, val) pairs.
+  // it copied itself, so no warp synchronisation is involved), then the staged step records.
   uint4* ring = smem + threadIdx.x;  // slot s of this lane: ring[s * kThreads]
   int2* staged = reinterpret_cast<int2*>(smem + kRingSlots * kThreads);
+  int* staged_slot = reinterpret_cast<int*>(staged + UPC * a.KS);  // deterministic mode only
   const int K = a.K, KS = a.KS, NS = a.NS;
   const int unit0 = unit_block * UPC;
   const int nunits = a.B * NS;
+  const uint32_t row16 = (uint32_t)(((size_t)a.D * sizeof(T)) >> 4);  // decoder row length in 16-byte units
   for (int i = threadIdx.x; i < UPC * KS; i += kThreads) {
     const int lu = i / KS;
     const int j = i - lu * KS;
@@ -369,12 +436,13 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
       const int row = u / NS;
       const int k = (u - row * NS) * KS + j;
       if (k < K) {
-        e = stage_pair(a.indices, a.vals, a.vals_dtype, (size_t)row * K + k, a.F, a.status);
-        if (DET) slot = a.slot_of[(size_t)row * K + k];
+        const size_t g = (size_t)row * K + k;
+        e = stage_pair(a.indices, a.vals, a.vals_dtype, g, a.F, a.status);
+        if (DET) slot = a.slot_of[g];
       }
     }
     staged[i] = e;
-    if (DET) reinterpret_cast<int*>(staged + UPC * KS)[i] = slot;
+    if (DET) staged_slot[i] = slot;
   }
   __syncthreads();
 
@@ -385,12 +453,11 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
   const int row = live ? unit / NS : 0;
   const int seg = live ? unit - row * NS : 0;
   const int k_first = seg * KS;
-  const int n = live ? min(KS, K - k_first) : 0;  // k's in this segment
+  const int n = live ? min(KS, K - k_first) : 0;  // real steps of this segment
   const int col = piece * PW + lig * VEC;
   const bool active = live && (col < a.D);
   const float coef = __ldg(a.grad_out) * a.scale;
 
-  constexpr int H = VEC / 2;
   float2 r[H], suf[H];
 #pragma unroll
   for (int h = 0; h < H; h++) r[h] = suf[h] = make_float2(0.f, 0.f);
@@ -410,86 +477,62 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
     }
   }
 
-  const char* wcol = reinterpret_cast<const char*>(a.weight) + (size_t)col * sizeof(T);
-  const size_t row_bytes = (size_t)a.D * sizeof(T);
+  // lanes past the last column read column 0 instead (valid memory); they never store or reduce
+  const uint4* wcol = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(a.weight) +
+                                                     (size_t)(active ? col : 0) * sizeof(T));
   const int2* mine = staged + gid * KS;
-  const int* myslot = reinterpret_cast<const int*>(staged + UPC * KS) + gid * KS;
+  const int* myslot = staged_slot + gid * KS;
   float* slab = slab_base + lig * 4;
+  float* stage = DET ? a.stage + lig * VEC : nullptr;
   float* dv = a.dv_part + ((size_t)piece * a.B + row) * K + k_first;
 
-  // Row pieces travel global -> shared asynchronously through a ring of kRingSlots slots per
-  // lane: the piece for step j - kRingSlots is requested as soon as step j has been consumed, so
-  // a load is queued long BEFORE the reductions of the steps in between and is not stuck behind
-  // them in the SM's memory pipeline.
+  // Row pieces travel global -> shared asynchronously through the ring: the piece for step
+  // j - 16 is requested as soon as step j has been consumed, so a load is queued long BEFORE the
+  // reductions of the steps in between (it does not sit behind them in the SM's memory pipeline)
+  // and requests and reductions alternate instead of arriving in bursts.
   constexpr int R = kRingSlots;
   auto request = [&](int j, uint4* slot) {
-    const bool ok = active && j >= 0 && j < n;
-    const int id = j >= 0 ? mine[j].x : 0;
+    if (j >= 0) {  // padding steps and lanes past the last column get zeros without touching memory
 #ifndef FLEXSAE_EXPERIMENT_NO_LOADS
-    cp_async16(slot, wcol + (size_t)id * row_bytes, ok ? 16 : 0);
+      cp_async16(slot, wcol + (uint32_t)mine[j].x * row16, (active && j < n) ? 16 : 0);
 #else
-    cp_async16(slot, wcol + (size_t)(id & 1) * row_bytes, ok ? 16 : 0);
+      cp_async16(slot, wcol + ((uint32_t)mine[j].x & 1u) * row16, (active && j < n) ? 16 : 0);
 #endif
+    }
     cp_async_commit();  // one group per step (possibly empty) keeps the wait arithmetic uniform
   };
 #pragma unroll
   for (int q = 0; q < R; q++) request(KS - 1 - q, ring + q * kThreads);
-  uint4* slot = ring;
-  int slot_no = 0;
-  for (int jb = KS - 1; jb >= 0; jb -= U) {  // KS is a multiple of U
-    int2 e[U];
-#pragma unroll
-    for (int u = 0; u < U; u++) e[u] = mine[jb - u];
+  int half = 0;
+  for (int jb = KS - 1; jb >= 0; jb -= U, half ^= 1) {  // KS is a multiple of U
+    uint4* slots = ring + half * U * kThreads;
     float d[U];
+    if (jb < n) {  // all U steps are real
 #pragma unroll
-    for (int u = 0; u < U; u++) {
-      const bool in_seg = jb - u < n;
-      const float v = __int_as_float(e[u].y);
-      const float c = v * coef;
-      const float2 cc = make_float2(c, c), nv = make_float2(-v, -v);
-      float2 wf[H];
-      cp_async_wait<R - 1>();  // at most R-1 newer requests pending: this step's piece has landed
-      Pack<T>::unpack_pairs(*slot, wf);
-      request(jb - u - R, slot);
-      slot += kThreads;
-      if (++slot_no == R) {
-        slot_no = 0;
-        slot = ring;
+      for (int u = 0; u < U; u++) {
+        cp_async_wait<R - 1>();  // at most R-1 newer requests pending: this step's piece has landed
+        const uint4 w = slots[u * kThreads];
+        request(jb - u - R, slots + u * kThreads);
+        d[u] = walk_step<T, G, HIER, DET, true>(mine[jb - u], DET ? myslot[jb - u] : 0, w, true, active, coef, r, suf, slab,
+                                                stage);
       }
-      if (HIER && in_seg) {
+    } else {
 #pragma unroll
-        for (int h = 0; h < H; h++) suf[h] = add2(suf[h], r[h]);  // S_k = sum_{j>=k} residual_j
-      }
-      if (active && in_seg) {
-        float2 g[H];
-#pragma unroll
-        for (int h = 0; h < H; h++) g[h] = mul2(suf[h], cc);
-        if (DET) {  // the contribution row goes to its sorted slot; it is added later, in slot order
-          float4* dst = reinterpret_cast<float4*>(a.stage + (size_t)myslot[jb - u] * PW + lig * VEC);
-          __stcs(dst, make_float4(g[0].x, g[0].y, g[1].x, g[1].y));
-          if (VEC == 8) __stcs(dst + 1, make_float4(g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y));
-        } else {
-          float* dst = slab + (size_t)e[u].x * PW;
-#ifndef FLEXSAE_EXPERIMENT_NO_REDS
-          red_add_v4(dst, g[0].x, g[0].y, g[1].x, g[1].y);
-          if (VEC == 8) red_add_v4(dst + G * 4, g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y);
-#else
-          if (g[0].x == 1.2345e-30f) dst[0] = g[1].y + g[H - 1].x;
-#endif
-        }
-      }
-      float2 dot = make_float2(0.f, 0.f);
-#pragma unroll
-      for (int h = 0; h < H; h++) dot = fma2(wf[h], suf[h], dot);
-      d[u] = dot.x + dot.y;  // rows outside the segment were loaded as zeros
-      if (HIER) {
-#pragma unroll
-        for (int h = 0; h < H; h++) r[h] = fma2(nv, wf[h], r[h]);  // step back to prefix k-1
+      for (int u = 0; u < U; u++) {
+        cp_async_wait<R - 1>();
+        const uint4 w = slots[u * kThreads];
+        request(jb - u - R, slots + u * kThreads);
+        d[u] = walk_step<T, G, HIER, DET, false>(mine[jb - u], DET ? myslot[jb - u] : 0, w, jb - u < n, active, coef, r, suf,
+                                                 slab, stage);
       }
     }
+#ifndef FLEXSAE_EXPERIMENT_NO_DOTS
     const float tot = group_sum8<G>(d, lig);
     const int j = jb - (lig & 7);
     if (live && lig < 8 && j < n) dv[j] = tot * coef;
+#else
+    if (d[0] + d[3] + d[7] == 1.2345e-30f) dv[0] = d[1];
+#endif
   }
   // The first segment ends with S_0, the sum of all prefix residuals of the row: dbias is the
   // column sum of these (TopK takes the column sums of the saved residual directly).
@@ -583,7 +626,9 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
     const int q = p - 1;
     if (q < 0) return;
     wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status);
+#ifndef FLEXSAE_EXPERIMENT_NO_CONVERT
     convert_slab<T, G, true>(pa.slabs[q & 1], pa.b.dweight, pa.b.F, pa.b.D, q, conv_idx, pa.conv_blocks);
+#endif
     signal_done(pa.conv_done + q);
     return;
   }
@@ -879,8 +924,8 @@ static int check_shape(int kind, const Shape& s, int wdt) {
     return fail(FLEXSAE_EUNSUPPORTED, "D=%lld must be a multiple of %d (16-byte row pieces)", (long long)s.D, vec);
   if (s.F > (1ll << 30) || s.D > (1ll << 20) || s.B > (1ll << 27) || s.B * s.K > (1ll << 31) - 1)
     return fail(FLEXSAE_EUNSUPPORTED, "shape too large for 32-bit row/position arithmetic");
-  // indices, vals (and sorted slots) of a CTA's rows are staged in shared memory next to the
-  // row-piece ring: 16 rows * K * 12 bytes must fit
+  // 8 (+4 in deterministic mode) bytes per (unit, step) are staged in shared memory next to the
+  // 32 KiB row-piece ring: 16 units * K * 12 bytes must fit
   if (s.K > 960) return fail(FLEXSAE_EUNSUPPORTED, "K=%lld above the supported maximum of 960", (long long)s.K);
   return 0;
 }
@@ -919,6 +964,14 @@ static int choose_segments(const Shape& s, int wdt) {
   }
   int KS, NS;
   segment_layout((int)s.K, want, &KS, &NS);
+  if (g_opt.segments <= 0 && (long long)NS * KS != s.K) {
+    // prefer the next larger count whose segments tile K exactly: padding steps are wasted work
+    for (int w = want + 1; w <= 8; w++) {
+      int ks, ns;
+      segment_layout((int)s.K, w, &ks, &ns);
+      if ((long long)ns * ks == s.K) return ns;
+    }
+  }
   return NS;
 }
 
@@ -936,7 +989,7 @@ static int check_segments(int kind, const Shape& s, int segments, int* KS, int* 
 }
 
 constexpr int kMaxRowBlocks = 128;  // partial rows of the dbias column sums
-constexpr int kConvertBlocks = 148 * 3;  // trailing CTAs that convert the previous piece's slab
+constexpr int kConvertBlocks = FLEXSAE_CONVERT_BLOCKS;  // CTAs per piece that convert the previous piece's slab
 
 struct BwdPlan {
   int G, PW, pieces, row_blocks, rows_per_block;
@@ -1003,7 +1056,7 @@ static cudaError_t allow_smem(K kern, size_t smem) {
 template <typename T, int G, bool HIER, bool SEG>
 static cudaError_t launch_fwd_seg(const FwdArgs& a, int pieces, cudaStream_t st) {
   constexpr int RPC = groups_per_cta(G);
-  const size_t smem = (size_t)RPC * a.K * sizeof(int2);
+  const size_t smem = (size_t)RPC * ((a.K + kUnroll - 1) / kUnroll * kUnroll) * sizeof(int2);
   auto kern = decoder_loss_fwd_kernel<T, G, HIER, SEG>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   dim3 grid((a.B + RPC - 1) / RPC, pieces);
