@@ -201,6 +201,9 @@ def main():
     from flexsae_b200 import losses
 
     fx.config.dweight_mode = args.dweight_mode
+    for item in filter(None, os.environ.get("FLEXSAE_OPTIONS", "").split(",")):   # e.g. "lanes_bwd=8,segments=2"
+        name, value = item.split("=")
+        nv.set_option(name, int(value))
     rows = w.B                                     # per rank (weak scaling)
     global_rows = rows * world
     wg = w.replace(B=global_rows)

@@ -36,7 +36,8 @@ struct Options {
   int l2_budget_mb = 80;  // one piece of decoder columns (+ one fp32 slab) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
-  int convert_offset_pct = 60;  // where, inside a piece's unit blocks, the previous piece's converters sit
+  int convert_offset_pct = 60;
+  int exchange_blocks = 148;  // sharded backward: blocks per slot that move data between GPUs  // where, inside a piece's unit blocks, the previous piece's converters sit
 };
 static Options g_opt;
 
@@ -640,23 +641,27 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
 // ---- batch-sharded backward: pipelined kernel + dweight reduction over peer memory ----------------
 // Every rank (one GPU each, same node) runs this kernel on its own batch shard.  The converting
 // blocks of the single-launch pipeline do the cross-GPU sum of dweight themselves, piece by piece,
-// over NVLink peer loads, overlapped with the accumulation of the following pieces:
-//   slot p converts the local slab of piece p-1 into this rank's exchange buffer X (decoder dtype),
-//   reduce-scatters piece p-2: this rank sums ITS block of decoder rows over all ranks' X (fixed
-//     rank order, fp32) into its buffer Y and into its own dweight,
-//   all-gathers piece p-3: copies the other ranks' reduced row blocks from their Y into dweight.
+// overlapped with the accumulation of the following pieces.  All traffic between GPUs is posted
+// STORES into the peers' buffers (a remote load would stall its thread for microseconds; a store
+// does not), all loads are local:
+//   slot p converts the local slab of piece p-1 (decoder dtype) and SCATTERS it: every decoder row
+//     goes to the inbox of the rank that owns that row block (reduce-scatter by push),
+//   reduces piece p-2: this rank sums the N inbox copies of ITS row block (fixed rank order, fp32),
+//     writes its own dweight rows and BROADCASTS the reduced rows into every peer's gather buffer,
+//   copies piece p-3: the other ranks' reduced row blocks from the local gather buffer to dweight.
 // One flag per (rank, peer) carries all cross-GPU ordering: when the last converting block of
-// slot p finishes, the rank publishes seq_base + p to every peer; the converting blocks of slot p
-// first wait until every peer has published slot p-1.  X and Y are double-buffered by piece
-// parity, and "peer finished slot p-1" is exactly what makes each buffer safe to read / reuse.
-// Waits are bounded like the local ones.  Plain peer loads/stores only: no multicast of any kind.
+// slot p finishes, the rank publishes seq_base + p to every rank; the converting blocks of slot p
+// first wait until every rank (itself included) has published slot p-1.  Inbox and gather buffer
+// are double-buffered by piece parity, and "every rank finished slot p-1" is exactly what makes a
+// buffer complete to read and free to overwrite.  Waits are bounded like the local ones.  Plain
+// peer stores only: no multicast of any kind.
 constexpr int kMaxRanks = 8;
 struct ShardArgs {
   PipeArgs p;
   int* slot_done;  // [pieces + 3] converting blocks that finished ALL stages of a slot
   int world, rank, rows_per_rank, seq_base;
-  void* x[kMaxRanks];        // rank s's X: [2][F][PW]
-  void* y[kMaxRanks];        // rank s's Y: [2][rows_per_rank][PW]
+  void* inbox[kMaxRanks];    // rank o's inbox: [2][world][rows_per_rank][PW]
+  void* gathered[kMaxRanks]; // rank o's gather buffer: [2][world * rows_per_rank][PW]
   int* flags_at[kMaxRanks];  // flag array living on rank s; entry [r] = last slot rank r finished
 };
 
@@ -691,14 +696,18 @@ __device__ __forceinline__ void wait_peers(const ShardArgs& sa, int target) {
   __syncthreads();
 }
 
-// local slab (fp32, permuted columns) -> this rank's X[parity] in natural column order; clears the slab
+// local slab (fp32, permuted columns) -> decoder dtype, natural column order, each decoder row
+// stored into the inbox of the rank owning its row block; clears the slab
 template <typename T, int G>
-__device__ __forceinline__ void slab_to_exchange(float* slab, T* x, int F, int cta, int nctas) {
+__device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, int piece, int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
-  constexpr int IL = 4;
+  constexpr int IL = FLEXSAE_CONVERT_IL;
+  const int F = sa.p.b.F;
+  const int rpr = sa.rows_per_rank;
   const size_t total = (size_t)F * G;
   const size_t stride = (size_t)nctas * kThreads;
+  const size_t slot_off = ((size_t)(piece & 1) * sa.world + sa.rank) * rpr * PW;  // [parity][sender = me]
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
     float4 lo[IL], hi[IL];
@@ -715,42 +724,46 @@ __device__ __forceinline__ void slab_to_exchange(float* slab, T* x, int F, int c
     for (int q = 0; q < IL; q++) {
       const size_t i = base + q * stride;
       if (i < total) {
-        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        const int f = (int)(i / G), lig = (int)(i % G);
+        float* sp = slab + (size_t)f * PW + lig * 4;
         *reinterpret_cast<float4*>(sp) = zero;
         float v[8] = {lo[q].x, lo[q].y, lo[q].z, lo[q].w, 0.f, 0.f, 0.f, 0.f};
         if (VEC == 8) {
           *reinterpret_cast<float4*>(sp + G * 4) = zero;
           v[4] = hi[q].x; v[5] = hi[q].y; v[6] = hi[q].z; v[7] = hi[q].w;
         }
-        *reinterpret_cast<uint4*>(x + i * VEC) = Pack<T>::pack(v);  // item i = (row i / G, chunk i % G)
+        const int owner = f / rpr;
+        T* dst = reinterpret_cast<T*>(sa.inbox[owner]) + slot_off + (size_t)(f - owner * rpr) * PW + lig * VEC;
+        *reinterpret_cast<uint4*>(dst) = Pack<T>::pack(v);  // a peer store unless this rank owns the row
       }
     }
   }
 }
 
-// this rank's row block of one piece: sum over all ranks' X in rank order -> Y (own) and dweight.
-// IL items per thread are in flight together (IL * world 16-byte peer loads) to cover NVLink latency.
+// this rank's row block of one piece: sum of the N inbox copies in rank order -> own dweight rows
+// and every peer's gather buffer.  IL items per thread in flight (IL * world local 16-byte loads).
 template <typename T, int G, int IL>
-__device__ __forceinline__ void reduce_row_block(const ShardArgs& sa, int piece, int cta, int nctas) {
+__device__ __forceinline__ void reduce_broadcast(const ShardArgs& sa, int piece, int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
   constexpr int W = kMaxRanks / IL;  // largest world size this instantiation serves
   const int F = sa.p.b.F, D = sa.p.b.D;
-  const int row0 = sa.rank * sa.rows_per_rank;
-  const int rows = max(0, min(F, row0 + sa.rows_per_rank) - row0);
+  const int rpr = sa.rows_per_rank;
+  const int row0 = sa.rank * rpr;
+  const int rows = max(0, min(F, row0 + rpr) - row0);
   const size_t total = (size_t)rows * G;
-  const size_t par_x = (size_t)(piece & 1) * F * PW;
   const size_t stride = (size_t)nctas * kThreads;
-  T* yown = reinterpret_cast<T*>(sa.y[sa.rank]) + (size_t)(piece & 1) * sa.rows_per_rank * PW;
+  const T* in = reinterpret_cast<const T*>(sa.inbox[sa.rank]) + (size_t)(piece & 1) * sa.world * rpr * PW;
+  const size_t sender_stride = (size_t)rpr * PW;
+  const size_t gat_off = ((size_t)(piece & 1) * sa.world * rpr + row0) * PW;
   for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
-    uint4 in[IL][W];
+    uint4 v[IL][W];
 #pragma unroll
     for (int q = 0; q < IL; q++) {
       const size_t i = base + q * stride;
-      const size_t off = par_x + ((size_t)row0 * G + i) * VEC;
 #pragma unroll
       for (int s = 0; s < W; s++)
-        if (i < total && s < sa.world) in[q][s] = __ldcg(reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(sa.x[s]) + off));
+        if (i < total && s < sa.world) v[q][s] = __ldcg(reinterpret_cast<const uint4*>(in + s * sender_stride + i * VEC));
     }
 #pragma unroll
     for (int q = 0; q < IL; q++) {
@@ -763,12 +776,15 @@ __device__ __forceinline__ void reduce_row_block(const ShardArgs& sa, int piece,
         for (int s = 0; s < W; s++)
           if (s < sa.world) {
             float f[VEC];
-            Pack<T>::unpack(in[q][s], f);
+            Pack<T>::unpack(v[q][s], f);
 #pragma unroll
             for (int j = 0; j < VEC; j++) acc[j] += f[j];
           }
         const uint4 out = Pack<T>::pack(acc);
-        *reinterpret_cast<uint4*>(yown + i * VEC) = out;
+#pragma unroll
+        for (int o = 0; o < kMaxRanks; o++)
+          if (o < sa.world && o != sa.rank)
+            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.gathered[o]) + gat_off + i * VEC) = out;  // peer store
         const int col = piece * PW + (int)(i % G) * VEC;
         if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)(row0 + i / G) * D + col) = out;
       }
@@ -776,41 +792,34 @@ __device__ __forceinline__ void reduce_row_block(const ShardArgs& sa, int piece,
   }
 }
 
-// the other ranks' reduced row blocks of one piece: their Y -> this rank's dweight
+// the other ranks' reduced row blocks of one piece: local gather buffer -> this rank's dweight
 template <typename T, int G>
-__device__ __forceinline__ void gather_row_blocks(const ShardArgs& sa, int piece, int cta, int nctas) {
+__device__ __forceinline__ void copy_gathered(const ShardArgs& sa, int piece, int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
   constexpr int IL = 4;
   const int F = sa.p.b.F, D = sa.p.b.D;
-  const size_t per_rank = (size_t)sa.rows_per_rank * G;  // items per rank block (last one may be short)
-  const size_t total = per_rank * (sa.world - 1);
+  const int rpr = sa.rows_per_rank;
+  const size_t total = (size_t)F * G;  // items of the whole piece; this rank's own block is skipped
   const size_t stride = (size_t)nctas * kThreads;
+  const T* src = reinterpret_cast<const T*>(sa.gathered[sa.rank]) + (size_t)(piece & 1) * sa.world * rpr * PW;
+  const int own0 = sa.rank * rpr, own1 = own0 + rpr;
   for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
     uint4 v[IL];
-    int row[IL], chunk[IL];
+    bool take[IL];
 #pragma unroll
     for (int q = 0; q < IL; q++) {
       const size_t i = base + q * stride;
-      row[q] = -1;
-      if (i < total) {
-        int s = (int)(i / per_rank);
-        const size_t w = i - (size_t)s * per_rank;
-        if (s >= sa.rank) s++;  // skip this rank's own block
-        const int r = s * sa.rows_per_rank + (int)(w / G);
-        if (r < F) {
-          row[q] = r;
-          chunk[q] = (int)(w % G);
-          const T* src = reinterpret_cast<const T*>(sa.y[s]) + (size_t)(piece & 1) * sa.rows_per_rank * PW + w * VEC;
-          v[q] = __ldcg(reinterpret_cast<const uint4*>(src));
-        }
-      }
+      const int f = (int)(i / G);
+      take[q] = i < total && (f < own0 || f >= own1);
+      if (take[q]) v[q] = __ldcg(reinterpret_cast<const uint4*>(src + i * VEC));
     }
 #pragma unroll
     for (int q = 0; q < IL; q++) {
-      if (row[q] >= 0) {
-        const int col = piece * PW + chunk[q] * VEC;
-        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)row[q] * D + col) = v[q];
+      if (take[q]) {
+        const size_t i = base + q * stride;
+        const int col = piece * PW + (int)(i % G) * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (i / G) * D + col) = v[q];
       }
     }
   }
@@ -820,14 +829,14 @@ template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_kernel(const ShardArgs sa) {
   extern __shared__ uint4 smem[];
   const PipeArgs& pa = sa.p;
-  constexpr int PW = G * Pack<T>::VEC;
+  const int P = pa.pieces;
   const int per = pa.unit_blocks + pa.conv_blocks;
-  const int body = pa.pieces * per;
+  const int body = P * per;
   int p, conv_idx = -1, unit_block = -1;
   if ((int)blockIdx.x >= body) {  // three draining slots of converting blocks only
     const int t = blockIdx.x - body;
-    p = pa.pieces + t / pa.conv_blocks;
-    conv_idx = t - (p - pa.pieces) * pa.conv_blocks;
+    p = P + t / pa.conv_blocks;
+    conv_idx = t - (p - P) * pa.conv_blocks;
   } else {
     p = blockIdx.x / per;
     const int r = blockIdx.x - p * per;
@@ -835,24 +844,20 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
     else unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
   }
   if (conv_idx >= 0) {
-    const int P = pa.pieces;
-    if (p >= 1 && p - 1 < P) wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);
+    if (p >= 1 && p - 1 < P) wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);  // local slab complete
     if (p >= 1) wait_peers(sa, sa.seq_base + p - 1);
     // The slab first: the unit blocks of piece p+1 are waiting for it to be cleared.
-    if (p >= 1 && p - 1 < P)
-      slab_to_exchange<T, G>(pa.slabs[(p - 1) & 1],
-                             reinterpret_cast<T*>(sa.x[sa.rank]) + (size_t)((p - 1) & 1) * pa.b.F * PW, pa.b.F, conv_idx,
-                             pa.conv_blocks);
+    if (p >= 1 && p - 1 < P) slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
     signal_done(pa.conv_done + p);
     if (p >= 2 && p - 2 < P) {
-      if (sa.world <= 2) reduce_row_block<T, G, 4>(sa, p - 2, conv_idx, pa.conv_blocks);
-      else if (sa.world <= 4) reduce_row_block<T, G, 2>(sa, p - 2, conv_idx, pa.conv_blocks);
-      else reduce_row_block<T, G, 1>(sa, p - 2, conv_idx, pa.conv_blocks);
+      if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, conv_idx, pa.conv_blocks);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, conv_idx, pa.conv_blocks);
+      else reduce_broadcast<T, G, 1>(sa, p - 2, conv_idx, pa.conv_blocks);
     }
-    if (p >= 3 && p - 3 < P) gather_row_blocks<T, G>(sa, p - 3, conv_idx, pa.conv_blocks);
+    if (p >= 3 && p - 3 < P) copy_gathered<T, G>(sa, p - 3, conv_idx, pa.conv_blocks);
     __syncthreads();
     if (threadIdx.x == 0) {
-      __threadfence_system();  // this block's X / Y / dweight writes before the count moves
+      __threadfence_system();  // this block's peer stores and dweight writes before the count moves
       const int old = atomicAdd(sa.slot_done + p, 1);
       if (old == pa.conv_blocks - 1) {  // the whole slot is done on this rank: tell every rank
         __threadfence_system();
@@ -1373,8 +1378,8 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     sa.seq_base = peers->seq_base;
     sa.rows_per_rank = (int)((F + peers->world - 1) / peers->world);
     for (int r = 0; r < kMaxRanks; r++) {
-      sa.x[r] = r < peers->world ? peers->x[r] : nullptr;
-      sa.y[r] = r < peers->world ? peers->y[r] : nullptr;
+      sa.inbox[r] = r < peers->world ? peers->x[r] : nullptr;
+      sa.gathered[r] = r < peers->world ? peers->y[r] : nullptr;
       sa.flags_at[r] = r < peers->world ? reinterpret_cast<int*>(peers->flags[r]) : nullptr;
     }
 #define CALL_SHARD(T, G, H) launch_bwd_sharded<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, sa, st)
@@ -1445,8 +1450,8 @@ int flexsae_shard_buffer_bytes(int64_t F, int64_t D, int weight_dtype, int world
   if (!x_bytes || !y_bytes || !flag_bytes) return fail(FLEXSAE_EINVAL, "null pointer argument");
   const BwdPlan p = plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC);
   const size_t rows_per_rank = (size_t)((F + world - 1) / world);
-  *x_bytes = align_up(2 * (size_t)F * p.PW * dtype_size(weight_dtype), 256);
-  *y_bytes = align_up(2 * rows_per_rank * p.PW * dtype_size(weight_dtype), 256);
+  *x_bytes = align_up(2 * (size_t)world * rows_per_rank * p.PW * dtype_size(weight_dtype), 256);  // inbox
+  *y_bytes = *x_bytes;                                                                           // gather buffer
   *flag_bytes = 256;
   return 0;
 }

@@ -135,8 +135,9 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
  * it is D values).  The reference has no counterpart (it is single-GPU); in a data-parallel run it
  * replaces flexsae_loss_bwd followed by an all-reduce of the dense [F,D] gradient.
  *   x_ptrs / y_ptrs / flag_ptrs   host arrays of `world` DEVICE pointers, entry r = rank r's
- *       exchange buffers, each mapped into this process (CUDA IPC / symmetric memory), of the
- *       sizes flexsae_shard_buffer_bytes answers; the flag buffers must be zero before the first call
+ *       inbox, gather buffer and flag array, each mapped into this process (CUDA IPC / symmetric
+ *       memory), of the sizes flexsae_shard_buffer_bytes answers; peers only STORE into them;
+ *       the flag buffers must be zero before the first call
  *   seq_base   first call: 1; every later call on the same buffers: previous seq_base +
  *       flexsae_shard_slots(F, D, weight_dtype); identical on all ranks
  * Only FLEXSAE_DW_ATOMIC accumulation.  All ranks must issue the same sequence of calls.  Waits on
