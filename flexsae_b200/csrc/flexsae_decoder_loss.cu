@@ -37,6 +37,7 @@ struct Options {
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
   int convert_offset_pct = 60;
+  int direct_f32 = 1;     // fp32 decoder: reduce straight into dweight instead of slab + copy
   int exchange_blocks = 148;  // sharded backward: blocks per slot that move data between GPUs  // where, inside a piece's unit blocks, the previous piece's converters sit
 };
 static Options g_opt;
@@ -110,6 +111,7 @@ struct BwdArgs {
   int32_t* status;
   int B, K, F, D;
   int vals_dtype;
+  int slab_stride; // floats between consecutive decoder rows of the accumulation target: PW (slab) or D (dweight itself)
   int piece;       // column piece accumulated by this launch (-1: none, conversion only)
   int conv_piece;  // column piece converted by this launch (-1: none)
   int unit_blocks; // CTAs that walk (row, segment) units
@@ -355,7 +357,7 @@ __device__ __forceinline__ void convert_slab(float* slab, void* __restrict__ dwe
 // dweight contribution, dvals dot, residual stepped back to the previous prefix.
 template <typename T, int G, bool HIER, bool DET, bool FULL>
 __device__ __forceinline__ float walk_step(const int2 e, int slot, const uint4 piece16, bool in_seg, bool active, float coef,
-                                           float2* r, float2* suf, float* slab, float* stage) {
+                                           float2* r, float2* suf, float* slab, uint32_t slab_stride, float* stage) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int H = VEC / 2;
   constexpr int PW = G * VEC;
@@ -377,13 +379,9 @@ __device__ __forceinline__ float walk_step(const int2 e, int slot, const uint4 p
       __stcs(dst, make_float4(g[0].x, g[0].y, g[1].x, g[1].y));
       if (VEC == 8) __stcs(dst + 1, make_float4(g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y));
     } else {
-      float* dst = slab + (uint32_t)e.x * (uint32_t)PW;  // PW is a power of two: a shift
-#ifndef FLEXSAE_EXPERIMENT_NO_REDS
+      float* dst = slab + (size_t)((uint32_t)e.x) * slab_stride;
       red_add_v4(dst, g[0].x, g[0].y, g[1].x, g[1].y);
       if (VEC == 8) red_add_v4(dst + G * 4, g[H - 2].x, g[H - 2].y, g[H - 1].x, g[H - 1].y);
-#else
-      if (g[0].x == 1.2345e-30f) dst[0] = g[1].y + g[H - 1].x;
-#endif
     }
   }
   float2 dot = make_float2(0.f, 0.f);
@@ -484,6 +482,7 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
   const int2* mine = staged + gid * KS;
   const int* myslot = staged_slot + gid * KS;
   float* slab = slab_base + lig * 4;
+  const uint32_t slab_stride = (uint32_t)a.slab_stride;
   float* stage = DET ? a.stage + lig * VEC : nullptr;
   float* dv = a.dv_part + ((size_t)piece * a.B + row) * K + k_first;
 
@@ -494,11 +493,7 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
   constexpr int R = kRingSlots;
   auto request = [&](int j, uint4* slot) {
     if (j >= 0) {  // padding steps and lanes past the last column get zeros without touching memory
-#ifndef FLEXSAE_EXPERIMENT_NO_LOADS
       cp_async16(slot, wcol + (uint32_t)mine[j].x * row16, (active && j < n) ? 16 : 0);
-#else
-      cp_async16(slot, wcol + ((uint32_t)mine[j].x & 1u) * row16, (active && j < n) ? 16 : 0);
-#endif
     }
     cp_async_commit();  // one group per step (possibly empty) keeps the wait arithmetic uniform
   };
@@ -515,7 +510,7 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
         const uint4 w = slots[u * kThreads];
         request(jb - u - R, slots + u * kThreads);
         d[u] = walk_step<T, G, HIER, DET, true>(mine[jb - u], DET ? myslot[jb - u] : 0, w, true, active, coef, r, suf, slab,
-                                                stage);
+                                                slab_stride, stage);
       }
     } else {
 #pragma unroll
@@ -524,16 +519,12 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
         const uint4 w = slots[u * kThreads];
         request(jb - u - R, slots + u * kThreads);
         d[u] = walk_step<T, G, HIER, DET, false>(mine[jb - u], DET ? myslot[jb - u] : 0, w, jb - u < n, active, coef, r, suf,
-                                                 slab, stage);
+                                                 slab, slab_stride, stage);
       }
     }
-#ifndef FLEXSAE_EXPERIMENT_NO_DOTS
     const float tot = group_sum8<G>(d, lig);
     const int j = jb - (lig & 7);
     if (live && lig < 8 && j < n) dv[j] = tot * coef;
-#else
-    if (d[0] + d[3] + d[7] == 1.2345e-30f) dv[0] = d[1];
-#endif
   }
   // The first segment ends with S_0, the sum of all prefix residuals of the row: dbias is the
   // column sum of these (TopK takes the column sums of the saved residual directly).
@@ -627,10 +618,15 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
     const int q = p - 1;
     if (q < 0) return;
     wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status);
-#ifndef FLEXSAE_EXPERIMENT_NO_CONVERT
     convert_slab<T, G, true>(pa.slabs[q & 1], pa.b.dweight, pa.b.F, pa.b.D, q, conv_idx, pa.conv_blocks);
-#endif
     signal_done(pa.conv_done + q);
+    return;
+  }
+  if (pa.conv_blocks == 0) {
+    // fp32 decoder: the reductions go straight into dweight's columns of this piece (cleared by
+    // the caller); there is no slab, no conversion and nothing to wait for
+    walk_units<T, G, HIER, false>(pa.b, unit_block, p, reinterpret_cast<float*>(pa.b.dweight) + (size_t)p * (G * Pack<T>::VEC),
+                                  smem);
     return;
   }
   if (p >= 2) wait_count(pa.conv_done + (p - 2), pa.conv_blocks, pa.b.status);
@@ -1115,7 +1111,7 @@ static cudaError_t launch_bwd(BwdArgs a, cudaStream_t st) {
 
 template <typename T, int G, bool HIER>
 static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
-                                        cudaStream_t st) {
+                                        bool direct, cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
   const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
   auto kern = decoder_loss_bwd_pipelined_kernel<T, G, HIER>;
@@ -1132,6 +1128,7 @@ static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* s
   const long long items = (long long)b.F * G;
   int conv = (int)((items + kThreads * 4 - 1) / (kThreads * 4));
   if (conv > kConvertBlocks) conv = kConvertBlocks;
+  if (direct) conv = 0;
   pa.conv_blocks = conv;
   pa.conv_offset = (int)((long long)pa.unit_blocks * g_opt.convert_offset_pct / 100);
   const long long blocks = (long long)pieces * (pa.unit_blocks + conv) + conv;
@@ -1203,6 +1200,7 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "segments") && value >= 0 && value <= 256) { g_opt.segments = (int)value; return 0; }
   if (!strcmp(name, "pipeline") && (value == 0 || value == 1)) { g_opt.pipeline = (int)value; return 0; }
   if (!strcmp(name, "convert_offset_pct") && value >= 0 && value <= 100) { g_opt.convert_offset_pct = (int)value; return 0; }
+  if (!strcmp(name, "direct_f32") && (value == 0 || value == 1)) { g_opt.direct_f32 = (int)value; return 0; }
   return fail(FLEXSAE_EINVAL, "unknown option or value: %s=%lld", name, (long long)value);
 }
 
@@ -1214,6 +1212,7 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "segments")) return g_opt.segments;
   if (!strcmp(name, "pipeline")) return g_opt.pipeline;
   if (!strcmp(name, "convert_offset_pct")) return g_opt.convert_offset_pct;
+  if (!strcmp(name, "direct_f32")) return g_opt.direct_f32;
   return -1;
 }
 
@@ -1334,7 +1333,12 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
   a.vals_dtype = vals_dtype;
   a.scale = (float)(2.0 * inv_norm);
   a.KS = KS; a.NS = NS;
+  a.slab_stride = p.PW;
   float* db_part = reinterpret_cast<float*>(ws + p.off_db);
+  // An fp32 decoder needs no fp32 slab: dweight itself is the accumulation target (single GPU,
+  // single-launch form).
+  const bool direct = weight_dtype == FLEXSAE_F32 && dw_mode == FLEXSAE_DW_ATOMIC && !peers && g_opt.pipeline &&
+                      g_opt.direct_f32;
 
   cudaError_t e = cudaSuccess;
   if (dw_mode == FLEXSAE_DW_DETERMINISTIC) {
@@ -1362,8 +1366,13 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
   // Both slabs are cleared once here; afterwards every conversion leaves its slab cleared.
   // Launch i accumulates piece i into slab i%2 and converts piece i-1 out of the other slab;
   // one more launch converts the last piece.
-  e = cudaMemsetAsync(slabs[0], 0, 2 * p.slab_bytes, st);
-  if (e != cudaSuccess) return fail((int)e, "slab clear failed: %s", cudaGetErrorString(e));
+  if (direct) {
+    e = cudaMemsetAsync(dweight, 0, (size_t)F * D * sizeof(float), st);
+    a.slab_stride = (int)D;
+  } else {
+    e = cudaMemsetAsync(slabs[0], 0, 2 * p.slab_bytes, st);
+  }
+  if (e != cudaSuccess) return fail((int)e, "gradient clear failed: %s", cudaGetErrorString(e));
   if (peers) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
     e = cudaMemsetAsync(counters, 0, (size_t)(3 * p.pieces + 6) * 4, st);
@@ -1394,7 +1403,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     a.slab = a.conv_slab = nullptr;
     a.unit_blocks = a.conv_blocks = 0;
     a.conv_stride = 1;
-#define CALL_PIPE(T, G, H) launch_bwd_pipelined<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, st)
+#define CALL_PIPE(T, G, H) launch_bwd_pipelined<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, direct, st)
     e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_PIPE);
 #undef CALL_PIPE
     if (e != cudaSuccess) return fail((int)e, "pipelined backward launch failed: %s", cudaGetErrorString(e));

@@ -202,10 +202,16 @@ def triton_topk_sae_loss(indices: torch.Tensor, weight: torch.Tensor, vals: torc
                          target: torch.Tensor) -> torch.Tensor:
     """Fused TopK decoder loss; drop-in for ``flex_sae.triton_topk_sae_loss`` (the name is kept
     for callers; no Triton is involved)."""
+    if torch.compiler.is_compiling():
+        from . import compile_ops
+        return compile_ops.topk_sae_loss(indices, weight, vals, bias, target)
     return _FusedDecoderLoss.apply(nv.TOPK, 0.0, indices, weight, vals, bias, target)
 
 
 def triton_hierarchical_sae_loss(indices: torch.Tensor, weight: torch.Tensor, vals: torch.Tensor,
                                  bias: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
     """Fused Hierarchical-TopK decoder loss; drop-in for ``flex_sae.triton_hierarchical_sae_loss``."""
+    if torch.compiler.is_compiling():
+        from . import compile_ops
+        return compile_ops.hierarchical_sae_loss(indices, weight, vals, bias, target)
     return _FusedDecoderLoss.apply(nv.HIER, 0.0, indices, weight, vals, bias, target)

@@ -61,7 +61,8 @@ const char* flexsae_last_error(void);
  * 0 = choose so that one column slab of the decoder and of the fp32 gradient slab stay in L2),
  * "l2_budget_mb" (working set one column piece may occupy), "segments"
  * (what flexsae_choose_segments answers; 0 = derive from the shape), "pipeline" (1: the atomic
- * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct".
+ * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct",
+ * "direct_f32" (1: with an fp32 decoder the reductions go straight into dweight).
  * Stands in for the literal tile constants at the reference's launch sites
  * (torch-ext/flex_sae/hierarchical_kernels.py:220-224,263-267; topk_kernels.py:64-66,181-183).
  * Returns 0, or FLEXSAE_EINVAL for an unknown name or value. */

@@ -45,6 +45,7 @@ def _auto_options():
     for name in ("lanes_fwd", "lanes_bwd", "segments"):
         nv.set_option(name, 0)
     nv.set_option("pipeline", 1)
+    nv.set_option("direct_f32", 1)
     yield
     fx.check_status()
 
@@ -101,6 +102,19 @@ def test_one_launch_per_piece_form(name, kind):
     w, kind, gold = load_golden(path)
     nv.set_option("pipeline", 0)
     nv.set_option("lanes_bwd", 8)        # many column pieces
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+
+
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("name", ["c1", "ragged_rows_float32", "t32_32_160_768_float32"])
+def test_fp32_decoder_through_slab(name, kind):
+    """fp32 decoders normally reduce straight into dweight; this is the slab + copy form."""
+    path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
+    w, kind, gold = load_golden(path)
+    nv.set_option("direct_f32", 0)
     x = make_inputs(w, "cpu")
     got = run_fused(kind, x)
     want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
