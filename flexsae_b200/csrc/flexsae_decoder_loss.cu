@@ -36,9 +36,9 @@ struct Options {
   int l2_budget_mb = 80;  // one piece of decoder columns (+ one fp32 slab) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
-  int convert_offset_pct = 60;
-  int direct_f32 = 1;     // fp32 decoder: reduce straight into dweight instead of slab + copy
-  int exchange_blocks = 148;  // sharded backward: blocks per slot that move data between GPUs  // where, inside a piece's unit blocks, the previous piece's converters sit
+  int convert_offset_pct = 60;  // where, inside a piece's unit blocks, the previous piece's converters sit
+  int exchange_blocks = 148;    // sharded backward: blocks per slot for the cross-GPU reduce / broadcast / copy
+  int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
 };
 static Options g_opt;
 
@@ -656,6 +656,7 @@ struct ShardArgs {
   PipeArgs p;
   int* slot_done;  // [pieces + 3] converting blocks that finished ALL stages of a slot
   int world, rank, rows_per_rank, seq_base;
+  int exch_blocks;  // blocks per slot that reduce / broadcast / copy older pieces
   void* inbox[kMaxRanks];    // rank o's inbox: [2][world][rows_per_rank][PW]
   void* gathered[kMaxRanks]; // rank o's gather buffer: [2][world * rows_per_rank][PW]
   int* flags_at[kMaxRanks];  // flag array living on rank s; entry [r] = last slot rank r finished
@@ -793,7 +794,7 @@ template <typename T, int G>
 __device__ __forceinline__ void copy_gathered(const ShardArgs& sa, int piece, int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
-  constexpr int IL = 4;
+  constexpr int IL = 8;
   const int F = sa.p.b.F, D = sa.p.b.D;
   const int rpr = sa.rows_per_rank;
   const size_t total = (size_t)F * G;  // items of the whole piece; this rank's own block is skipped
@@ -821,50 +822,69 @@ __device__ __forceinline__ void copy_gathered(const ShardArgs& sa, int piece, in
   }
 }
 
+// Block roles inside slot p of the sharded launch (slots 0..pieces+2):
+//   exchange blocks (sa.exch_blocks, first in the slot): reduce + broadcast of piece p-2 and the
+//     copy of piece p-3 -- local loads and posted stores only, so a few blocks keep up;
+//   unit blocks: accumulate piece p;
+//   converting blocks (inserted at conv_offset): slab of piece p-1 -> scattered to the owners, cleared.
+// A slot is finished on a rank when all its exchange and converting blocks are.
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_kernel(const ShardArgs sa) {
   extern __shared__ uint4 smem[];
   const PipeArgs& pa = sa.p;
   const int P = pa.pieces;
-  const int per = pa.unit_blocks + pa.conv_blocks;
+  const int E = sa.exch_blocks;
+  const int per = E + pa.unit_blocks + pa.conv_blocks;
   const int body = P * per;
-  int p, conv_idx = -1, unit_block = -1;
-  if ((int)blockIdx.x >= body) {  // three draining slots of converting blocks only
+  int p, exch_idx = -1, conv_idx = -1, unit_block = -1;
+  if ((int)blockIdx.x >= body) {  // three draining slots: exchange and converting blocks only
     const int t = blockIdx.x - body;
-    p = P + t / pa.conv_blocks;
-    conv_idx = t - (p - P) * pa.conv_blocks;
+    const int dper = E + pa.conv_blocks;
+    p = P + t / dper;
+    const int r = t - (p - P) * dper;
+    if (r < E) exch_idx = r; else conv_idx = r - E;
   } else {
     p = blockIdx.x / per;
-    const int r = blockIdx.x - p * per;
-    if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) conv_idx = r - pa.conv_offset;
-    else unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
+    int r = blockIdx.x - p * per;
+    if (r < E) {
+      exch_idx = r;
+    } else {
+      r -= E;
+      if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) conv_idx = r - pa.conv_offset;
+      else unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
+    }
   }
-  if (conv_idx >= 0) {
-    if (p >= 1 && p - 1 < P) wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);  // local slab complete
-    if (p >= 1) wait_peers(sa, sa.seq_base + p - 1);
-    // The slab first: the unit blocks of piece p+1 are waiting for it to be cleared.
-    if (p >= 1 && p - 1 < P) slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
-    signal_done(pa.conv_done + p);
-    if (p >= 2 && p - 2 < P) {
-      if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, conv_idx, pa.conv_blocks);
-      else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, conv_idx, pa.conv_blocks);
-      else reduce_broadcast<T, G, 1>(sa, p - 2, conv_idx, pa.conv_blocks);
-    }
-    if (p >= 3 && p - 3 < P) copy_gathered<T, G>(sa, p - 3, conv_idx, pa.conv_blocks);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      __threadfence_system();  // this block's peer stores and dweight writes before the count moves
-      const int old = atomicAdd(sa.slot_done + p, 1);
-      if (old == pa.conv_blocks - 1) {  // the whole slot is done on this rank: tell every rank
-        __threadfence_system();
-        for (int s = 0; s < sa.world; s++) st_release_sys(sa.flags_at[s] + sa.rank, sa.seq_base + p);
-      }
-    }
+  if (unit_block >= 0) {
+    if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status);  // slot p-1 cleared this slab
+    walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
+    signal_done(pa.walk_done + p);
     return;
   }
-  if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status);  // slot p-1 cleared this slab
-  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
-  signal_done(pa.walk_done + p);
+  if (conv_idx >= 0) {
+    if (p >= 1 && p - 1 < P) {
+      wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);  // the local slab is complete
+      wait_peers(sa, sa.seq_base + p - 1);  // the owners have read what this parity of their inbox held
+      slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
+    }
+    signal_done(pa.conv_done + p);
+  } else {
+    if (p >= 2) wait_peers(sa, sa.seq_base + p - 1);  // inbox of piece p-2 and gather buffer of piece p-3 are complete
+    if (p >= 2 && p - 2 < P) {
+      if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, exch_idx, E);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, exch_idx, E);
+      else reduce_broadcast<T, G, 1>(sa, p - 2, exch_idx, E);
+    }
+    if (p >= 3 && p - 3 < P) copy_gathered<T, G>(sa, p - 3, exch_idx, E);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // this block's peer stores and dweight writes before the count moves
+    const int old = atomicAdd(sa.slot_done + p, 1);
+    if (old == E + pa.conv_blocks - 1) {  // the whole slot is done on this rank: tell every rank
+      __threadfence_system();
+      for (int s = 0; s < sa.world; s++) st_release_sys(sa.flags_at[s] + sa.rank, sa.seq_base + p);
+    }
+  }
 }
 
 // Column sums of a [B, D] fp32 matrix over row blocks: part[rb][d] = sum of rows of block rb.
@@ -1160,7 +1180,8 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   if (conv > kConvertBlocks) conv = kConvertBlocks;
   pa.conv_blocks = conv;
   pa.conv_offset = (int)((long long)pa.unit_blocks * g_opt.convert_offset_pct / 100);
-  const long long blocks = (long long)pieces * (pa.unit_blocks + conv) + 3ll * conv;
+  sa.exch_blocks = g_opt.exchange_blocks;
+  const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks + conv) + 3ll * (sa.exch_blocks + conv);
   if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
   kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
   t_launches++;
@@ -1201,6 +1222,7 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "pipeline") && (value == 0 || value == 1)) { g_opt.pipeline = (int)value; return 0; }
   if (!strcmp(name, "convert_offset_pct") && value >= 0 && value <= 100) { g_opt.convert_offset_pct = (int)value; return 0; }
   if (!strcmp(name, "direct_f32") && (value == 0 || value == 1)) { g_opt.direct_f32 = (int)value; return 0; }
+  if (!strcmp(name, "exchange_blocks") && value >= 1 && value <= 4096) { g_opt.exchange_blocks = (int)value; return 0; }
   return fail(FLEXSAE_EINVAL, "unknown option or value: %s=%lld", name, (long long)value);
 }
 
@@ -1213,6 +1235,7 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "pipeline")) return g_opt.pipeline;
   if (!strcmp(name, "convert_offset_pct")) return g_opt.convert_offset_pct;
   if (!strcmp(name, "direct_f32")) return g_opt.direct_f32;
+  if (!strcmp(name, "exchange_blocks")) return g_opt.exchange_blocks;
   return -1;
 }
 
