@@ -125,6 +125,37 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
                : "memory");
 }
 
+// ---- NVLink SHARP (multimem) on a multicast address: the switch sums the same 16 bytes of every
+// GPU's replica (fp32 accumulation for 16-bit types) / stores 16 bytes into every replica.
+template <typename T>
+__device__ __forceinline__ uint4 multimem_ld_reduce(const void* mc);
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce<float>(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce<__nv_bfloat16>(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+template <>
+__device__ __forceinline__ uint4 multimem_ld_reduce<__half>(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
 // ---- run-time typed loads / stores for the small operands (vals, bias, target) -------------
 __device__ __forceinline__ float load_scalar(const void* p, int dtype, size_t i) {
   if (dtype == FLEXSAE_F32) return reinterpret_cast<const float*>(p)[i];

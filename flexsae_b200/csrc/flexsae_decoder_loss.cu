@@ -657,6 +657,8 @@ struct ShardArgs {
   int* slot_done;  // [pieces + 3] converting blocks that finished ALL stages of a slot
   int world, rank, rows_per_rank, seq_base;
   int exch_blocks;  // blocks per slot that reduce / broadcast / copy older pieces
+  void* mc_inbox;     // multicast address of the inbox region of ALL ranks (NULL: plain peer stores)
+  void* mc_gathered;  // multicast address of the gather buffers of all ranks
   void* inbox[kMaxRanks];    // rank o's inbox: [2][world][rows_per_rank][PW]
   void* gathered[kMaxRanks]; // rank o's gather buffer: [2][world * rows_per_rank][PW]
   int* flags_at[kMaxRanks];  // flag array living on rank s; entry [r] = last slot rank r finished
@@ -822,6 +824,84 @@ __device__ __forceinline__ void copy_gathered(const ShardArgs& sa, int piece, in
   }
 }
 
+// ---- the same three stages through the NVSwitch (multimem), when the buffers are bound to a
+// multicast object: per GPU and step it moves F*D*sw bytes in each direction instead of
+// 2*(N-1)/N times that, and a reduction is one load instead of N.
+//   convert: slab -> this rank's OWN copy of the piece (region "inbox", used as [2][F][PW])
+//   reduce:  multimem.ld_reduce of this rank's row block (the switch adds all ranks' copies in
+//            fp32) -> own dweight rows + multimem.st into every rank's gather buffer
+//   copy:    as before
+template <typename T, int G>
+__device__ __forceinline__ void slab_to_own_copy(float* slab, const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = FLEXSAE_CONVERT_IL;
+  const int F = sa.p.b.F;
+  const size_t total = (size_t)F * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  T* x = reinterpret_cast<T*>(sa.inbox[sa.rank]) + (size_t)(piece & 1) * sa.world * sa.rows_per_rank * PW;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    float4 lo[IL], hi[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        lo[q] = __ldcg(reinterpret_cast<const float4*>(sp));
+        if (VEC == 8) hi[q] = __ldcg(reinterpret_cast<const float4*>(sp + G * 4));
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        *reinterpret_cast<float4*>(sp) = zero;
+        float v[8] = {lo[q].x, lo[q].y, lo[q].z, lo[q].w, 0.f, 0.f, 0.f, 0.f};
+        if (VEC == 8) {
+          *reinterpret_cast<float4*>(sp + G * 4) = zero;
+          v[4] = hi[q].x; v[5] = hi[q].y; v[6] = hi[q].z; v[7] = hi[q].w;
+        }
+        *reinterpret_cast<uint4*>(x + i * VEC) = Pack<T>::pack(v);
+      }
+    }
+  }
+}
+
+template <typename T, int G>
+__device__ __forceinline__ void switch_reduce_broadcast(const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = 8;  // switch reductions in flight per thread (each is a round trip through the NVSwitch)
+  const int F = sa.p.b.F, D = sa.p.b.D;
+  const int rpr = sa.rows_per_rank;
+  const int row0 = sa.rank * rpr;
+  const int rows = max(0, min(F, row0 + rpr) - row0);
+  const size_t total = (size_t)rows * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  const size_t par = (size_t)(piece & 1) * sa.world * rpr * PW;
+  const T* mc_x = reinterpret_cast<const T*>(sa.mc_inbox) + par + (size_t)row0 * PW;
+  T* mc_y = reinterpret_cast<T*>(sa.mc_gathered) + par + (size_t)row0 * PW;
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    uint4 v[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) v[q] = multimem_ld_reduce<T>(mc_x + i * VEC);
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        multimem_st(mc_y + i * VEC, v[q]);
+        const int col = piece * PW + (int)(i % G) * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)(row0 + i / G) * D + col) = v[q];
+      }
+    }
+  }
+}
+
 // Block roles inside slot p of the sharded launch (slots 0..pieces+2):
 //   exchange blocks (sa.exch_blocks, first in the slot): reduce + broadcast of piece p-2 and the
 //     copy of piece p-3 -- local loads and posted stores only, so a few blocks keep up;
@@ -864,12 +944,15 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
     if (p >= 1 && p - 1 < P) {
       wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);  // the local slab is complete
       wait_peers(sa, sa.seq_base + p - 1);  // the owners have read what this parity of their inbox held
-      slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
+      if (sa.mc_inbox) slab_to_own_copy<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
+      else slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
     }
     signal_done(pa.conv_done + p);
   } else {
     if (p >= 2) wait_peers(sa, sa.seq_base + p - 1);  // inbox of piece p-2 and gather buffer of piece p-3 are complete
-    if (p >= 2 && p - 2 < P) {
+    if (p >= 2 && p - 2 < P && sa.mc_inbox) {
+      switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, E);
+    } else if (p >= 2 && p - 2 < P) {
       if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, exch_idx, E);
       else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, exch_idx, E);
       else reduce_broadcast<T, G, 1>(sa, p - 2, exch_idx, E);
@@ -1316,6 +1399,8 @@ struct PeerInfo {  // batch-sharded call: who the other GPUs are and where their
   void* const* x;
   void* const* y;
   void* const* flags;
+  void* mc_x;
+  void* mc_y;
 };
 
 static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, const void* vals, const float* state,
@@ -1409,6 +1494,8 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     sa.rank = peers->rank;
     sa.seq_base = peers->seq_base;
     sa.rows_per_rank = (int)((F + peers->world - 1) / peers->world);
+    sa.mc_inbox = peers->mc_x;
+    sa.mc_gathered = peers->mc_y;
     for (int r = 0; r < kMaxRanks; r++) {
       sa.inbox[r] = r < peers->world ? peers->x[r] : nullptr;
       sa.gathered[r] = r < peers->world ? peers->y[r] : nullptr;
@@ -1493,7 +1580,7 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
                              void* dbias, void* workspace, size_t workspace_bytes, int64_t B, int64_t K, int64_t F,
                              int64_t D, int weight_dtype, int vals_dtype, int bias_dtype, double inv_norm,
                              int32_t* status, void* stream, int world, int rank, int seq_base, void* const* x_ptrs,
-                             void* const* y_ptrs, void* const* flag_ptrs) {
+                             void* const* y_ptrs, void* const* flag_ptrs, void* multicast_x, void* multicast_y) {
   if (world < 2 || world > kMaxRanks) return fail(FLEXSAE_EINVAL, "world size %d outside [2, %d]", world, kMaxRanks);
   if (rank < 0 || rank >= world) return fail(FLEXSAE_EINVAL, "rank %d outside [0, %d)", rank, world);
   if (!x_ptrs || !y_ptrs || !flag_ptrs) return fail(FLEXSAE_EINVAL, "null pointer argument");
@@ -1501,7 +1588,9 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
     if (!x_ptrs[r] || !y_ptrs[r] || !flag_ptrs[r] || !aligned16(x_ptrs[r]) || !aligned16(y_ptrs[r]))
       return fail(FLEXSAE_EINVAL, "exchange buffer of rank %d is null or not 16-byte aligned", r);
   if (seq_base < 1) return fail(FLEXSAE_EINVAL, "seq_base must be >= 1");
-  PeerInfo peers{world, rank, seq_base, x_ptrs, y_ptrs, flag_ptrs};
+  if ((multicast_x == nullptr) != (multicast_y == nullptr) || !aligned16(multicast_x) || !aligned16(multicast_y))
+    return fail(FLEXSAE_EINVAL, "multicast addresses must both be given (16-byte aligned) or both be NULL");
+  PeerInfo peers{world, rank, seq_base, x_ptrs, y_ptrs, flag_ptrs, multicast_x, multicast_y};
   return loss_bwd_impl(kind, indices, weight, vals, state, segments, grad_out, dweight, dvals, dbias, workspace,
                        workspace_bytes, B, K, F, D, weight_dtype, vals_dtype, bias_dtype, inv_norm, FLEXSAE_DW_ATOMIC,
                        status, stream, &peers);

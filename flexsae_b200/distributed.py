@@ -32,6 +32,9 @@ class config:
     #: sum dweight over the ranks inside the backward kernel (NVLink peer memory) instead of an
     #: NCCL all-reduce afterwards
     peer_reduce: bool = True
+    #: let the NVSwitch do the sum and the broadcast (multimem) when the exchange buffers could be
+    #: bound to a multicast object; otherwise, or when False, plain peer stores
+    use_multicast: bool = True
 
 
 class PeerExchange:
@@ -60,6 +63,15 @@ class PeerExchange:
         self.x = arr(*ptrs)
         self.y = arr(*[p + xb.value for p in ptrs])
         self.flags = arr(*[p + xb.value + yb.value for p in ptrs])
+        mc = 0
+        if config.use_multicast:
+            try:
+                mc = int(self.handle.multicast_ptr or 0)
+            except Exception:
+                mc = 0
+        self.multicast = mc != 0
+        self.mc_x = ctypes.c_void_p(mc) if mc else None
+        self.mc_y = ctypes.c_void_p(mc + xb.value) if mc else None
         self.seq = 1
 
     def next_seq(self) -> int:
@@ -75,7 +87,7 @@ def peer_exchange(group, device: torch.device, F: int, D: int, dtype: torch.dtyp
     """The exchange buffers for this shape, created on first use (a collective: every rank of the
     group must get here together, which they do when they run the same training step)."""
     key = (id(group) if group is not None else 0, device.index, F, D, dtype,
-           nv.get_option("lanes_bwd"), nv.get_option("l2_budget_mb"))
+           nv.get_option("lanes_bwd"), nv.get_option("l2_budget_mb"), config.use_multicast)
     ex = _exchanges.get(key)
     if ex is None:
         ex = _exchanges[key] = PeerExchange(group, device, F, D, dtype)

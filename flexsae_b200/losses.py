@@ -164,7 +164,8 @@ def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype
                                               _ptr(go), _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(),
                                               B, K, F, D, wdt, nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype],
                                               float(inv_norm), _ptr(_status_word(dev)), stream, peers.world,
-                                              peers.rank, peers.next_seq(), peers.x, peers.y, peers.flags)
+                                              peers.rank, peers.next_seq(), peers.x, peers.y, peers.flags,
+                                              peers.mc_x, peers.mc_y)
         else:
             rc = lib.flexsae_loss_bwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(state), segments, _ptr(go),
                                       _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(), B, K, F, D, wdt,

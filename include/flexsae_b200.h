@@ -139,6 +139,10 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
  *       inbox, gather buffer and flag array, each mapped into this process (CUDA IPC / symmetric
  *       memory), of the sizes flexsae_shard_buffer_bytes answers; peers only STORE into them;
  *       the flag buffers must be zero before the first call
+ *   multicast_x / multicast_y   optional: the multicast (NVLink SHARP) addresses that map onto
+ *       all ranks' x / y buffers; when given, the reduction is done by the switch
+ *       (multimem.ld_reduce) and the reduced rows are broadcast with multimem.st; NULL, NULL =
+ *       plain peer stores
  *   seq_base   first call: 1; every later call on the same buffers: previous seq_base +
  *       flexsae_shard_slots(F, D, weight_dtype); identical on all ranks
  * Only FLEXSAE_DW_ATOMIC accumulation.  All ranks must issue the same sequence of calls.  Waits on
@@ -154,7 +158,8 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
                              int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype,
                              int vals_dtype, int bias_dtype, double inv_norm, int32_t* status,
                              void* stream, int world, int rank, int seq_base, void* const* x_ptrs,
-                             void* const* y_ptrs, void* const* flag_ptrs);
+                             void* const* y_ptrs, void* const* flag_ptrs, void* multicast_x,
+                             void* multicast_y);
 
 /*
  * flexsae_loss_fwd for callers that must not allocate device memory.  It has no counterpart in

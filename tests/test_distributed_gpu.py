@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, kind, q, peer_reduce=True):
+def _worker(rank, world, port, kind, q, peer_reduce=True, multicast=True):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -21,6 +21,7 @@ def _worker(rank, world, port, kind, q, peer_reduce=True):
         from flexsae_b200 import distributed as fd
         from flexsae_b200.workloads import CONFIGS, make_inputs
         fd.config.peer_reduce = peer_reduce
+        fd.config.use_multicast = multicast
         w = CONFIGS["c3_k32"].replace(B=768, F=8190)       # F not a multiple of the world size
         rows = w.B // world
         x = make_inputs(w, f"cuda:{rank}", row0=rank * rows, rows=rows)
@@ -45,7 +46,7 @@ def _worlds():
 
 
 @pytest.mark.parametrize("world", _worlds())
-@pytest.mark.parametrize("peer_reduce", [True, False], ids=["peer_memory", "nccl"])
+@pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "nccl"])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
 def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     if torch.cuda.device_count() < world:
@@ -59,9 +60,9 @@ def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
-    port += 13 if peer_reduce else 0
-    port += 29 * world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce)) for r in range(world)]
+    port += {"multicast": 13, "stores": 5, "nccl": 0}[peer_reduce] + 29 * world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce != "nccl", peer_reduce == "multicast"))
+             for r in range(world)]
     for p in procs:
         p.start()
     outs = sorted([q.get(timeout=300) for _ in procs], key=lambda o: o[0])
