@@ -33,7 +33,7 @@ from tests.golden.cases import FULL_DWEIGHT_MAX_ELEMS, GOLDEN_CASES, KINDS  # no
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference repository")
     args = ap.parse_args()
     sys.path.insert(0, os.path.join(args.reference, "torch-ext"))
     import flex_sae  # the reference package
