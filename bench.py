@@ -201,7 +201,7 @@ def main():
     from flexsae_b200 import losses
 
     fx.config.dweight_mode = args.dweight_mode
-    fd.config.use_multicast = os.environ.get("FLEXSAE_MULTICAST", "1") != "0"
+    fd.config.use_multicast = os.environ.get("FLEXSAE_MULTICAST", "0") != "0"
     fd.config.peer_reduce = os.environ.get("FLEXSAE_PEER_REDUCE", "1") != "0"
     for item in filter(None, os.environ.get("FLEXSAE_OPTIONS", "").split(",")):   # e.g. "lanes_bwd=8,segments=2"
         name, value = item.split("=")
