@@ -917,12 +917,18 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   const int per = E + pa.unit_blocks + pa.conv_blocks;
   const int body = P * per;
   int p, exch_idx = -1, conv_idx = -1, unit_block = -1;
-  if ((int)blockIdx.x >= body) {  // three draining slots: exchange and converting blocks only
+  int exch_n = E;  // blocks that share the exchange work of this slot
+  if ((int)blockIdx.x >= body) {  // three draining slots: no unit blocks, so every block helps with the exchange
     const int t = blockIdx.x - body;
     const int dper = E + pa.conv_blocks;
     p = P + t / dper;
     const int r = t - (p - P) * dper;
-    if (r < E) exch_idx = r; else conv_idx = r - E;
+    if (p == P && r >= E) {
+      conv_idx = r - E;  // slot P still has the last slab to convert
+    } else {
+      exch_idx = r;
+      exch_n = (p == P) ? E : dper;
+    }
   } else {
     p = blockIdx.x / per;
     int r = blockIdx.x - p * per;
@@ -951,13 +957,13 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   } else {
     if (p >= 2) wait_peers(sa, sa.seq_base + p - 1);  // inbox of piece p-2 and gather buffer of piece p-3 are complete
     if (p >= 2 && p - 2 < P && sa.mc_inbox) {
-      switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, E);
+      switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, exch_n);
     } else if (p >= 2 && p - 2 < P) {
-      if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, exch_idx, E);
-      else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, exch_idx, E);
-      else reduce_broadcast<T, G, 1>(sa, p - 2, exch_idx, E);
+      if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, exch_idx, exch_n);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, exch_idx, exch_n);
+      else reduce_broadcast<T, G, 1>(sa, p - 2, exch_idx, exch_n);
     }
-    if (p >= 3 && p - 3 < P) copy_gathered<T, G>(sa, p - 3, exch_idx, E);
+    if (p >= 3 && p - 3 < P) copy_gathered<T, G>(sa, p - 3, exch_idx, exch_n);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
