@@ -62,7 +62,10 @@ def load() -> ctypes.CDLL:
     if _lib is not None:
         return _lib
     path = _build.LIB_PATH
-    if os.environ.get("FLEXSAE_NO_BUILD", "0") != "1":
+    override = os.environ.get("FLEXSAE_LIB")        # a library built elsewhere (tuning variants)
+    if override:
+        path = override
+    elif os.environ.get("FLEXSAE_NO_BUILD", "0") != "1":
         try:
             path = _build.build()
         except RuntimeError:

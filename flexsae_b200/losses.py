@@ -75,11 +75,12 @@ def _validate(indices, weight, vals, bias, target) -> Tuple[int, int, int, int]:
 
 
 def _workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
-    """A per-device scratch buffer that is kept between calls (so that the fp32 gradient slab
-    keeps its L2 lines warm) and only ever grows.  All work of one device is assumed to be
-    enqueued on one stream at a time, like the rest of a training step."""
-    cache: Dict[int, torch.Tensor] = _tls.__dict__.setdefault("ws", {})
-    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    """A scratch buffer per (device, stream) that is kept between calls (so that the fp32 gradient
+    slabs keep their L2 lines warm) and only ever grows.  Calls enqueued on different streams get
+    different buffers, so they may overlap on the GPU; calls on one stream are ordered by it."""
+    cache: Dict[tuple, torch.Tensor] = _tls.__dict__.setdefault("ws", {})
+    index = dev.index if dev.index is not None else torch.cuda.current_device()
+    key = (index, torch.cuda.current_stream(dev).cuda_stream)
     buf = cache.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 1), dtype=torch.uint8, device=dev)

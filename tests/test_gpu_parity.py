@@ -323,3 +323,28 @@ def test_atomic_and_deterministic_modes_agree():
     assert out["atomic"]["loss"] == out["deterministic"]["loss"]
     assert np.array_equal(out["atomic"]["dvals"], out["deterministic"]["dvals"])
     assert rel_err(out["atomic"]["dweight"], out["deterministic"]["dweight"]) < 6e-3   # one bf16 rounding apart at most
+
+
+def test_calls_on_two_streams_do_not_share_scratch():
+    """Two backward passes enqueued on different streams may overlap on the GPU: each stream has
+    its own workspace, so both must give what they give alone."""
+    ws = [CONFIGS["c3_k32"].replace(B=1024, F=8192, seed=71), CONFIGS["c3_k32"].replace(B=1024, F=8192, seed=72)]
+    xs = [make_inputs(w, "cuda") for w in ws]
+    alone = [run_fused("hier", x) for x in xs]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    params = []
+    torch.cuda.synchronize()
+    for x, st in zip(xs, streams):
+        with torch.cuda.stream(st):
+            wt = x["weight"].detach().clone().requires_grad_(True)
+            v = x["vals"].detach().clone().requires_grad_(True)
+            b = x["bias"].detach().clone().requires_grad_(True)
+            loss = fx.triton_hierarchical_sae_loss(x["indices"], wt, v, b, x["target"])
+            loss.backward(x["grad_out"])
+            params.append((loss, wt, v, b))
+    torch.cuda.synchronize()
+    for (loss, wt, v, b), ref in zip(params, alone):
+        assert float(loss) == ref["loss"]
+        assert np.array_equal(v.grad.float().cpu().numpy(), ref["dvals"])
+        assert rel_err(wt.grad.float().cpu().numpy(), ref["dweight"]) < 6e-3
+        assert np.array_equal(b.grad.float().cpu().numpy(), ref["dbias"])
