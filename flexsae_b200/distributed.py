@@ -84,15 +84,27 @@ class PeerExchange:
 _exchanges: Dict[tuple, PeerExchange] = {}
 
 
-def peer_exchange(group, device: torch.device, F: int, D: int, dtype: torch.dtype) -> PeerExchange:
+def peer_exchange(group, device: torch.device, F: int, D: int, dtype: torch.dtype) -> Optional[PeerExchange]:
     """The exchange buffers for this shape, created on first use (a collective: every rank of the
-    group must get here together, which they do when they run the same training step)."""
+    group must get here together, which they do when they run the same training step).  ``None``
+    when symmetric memory cannot be set up on this machine (agreed on by all ranks)."""
     key = (id(group) if group is not None else 0, device.index, F, D, dtype,
            nv.get_option("lanes_bwd"), nv.get_option("l2_budget_mb"), config.use_multicast)
-    ex = _exchanges.get(key)
-    if ex is None:
-        ex = _exchanges[key] = PeerExchange(group, device, F, D, dtype)
-    return ex
+    if key not in _exchanges:
+        ex, problem = None, None
+        try:
+            ex = PeerExchange(group, device, F, D, dtype)
+        except Exception as e:  # no symmetric memory / no peer access on this machine
+            problem = e
+        ok = torch.tensor([0 if ex is None else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)      # all ranks take the same path
+        if int(ok.item()) == 0:
+            import warnings
+            warnings.warn(f"flexsae_b200: peer-memory exchange unavailable ({problem}); "
+                          "dweight will be all-reduced with NCCL after the backward")
+            ex = None
+        _exchanges[key] = ex
+    return _exchanges[key]
 
 
 def _fused_local_forward(kind, indices, weight, vals, bias, target, inv_norm):
@@ -112,8 +124,11 @@ def _fused_backward_with_peer_reduce(kind, ctx_saved, grad, bias_dtype, inv_norm
     """Backward of this rank's shard; dweight comes back already summed over the group."""
     idx_c, w_c, v_c, saved = ctx_saved
     ex = peer_exchange(group, w_c.device, w_c.shape[0], w_c.shape[1], w_c.dtype)
-    return _losses.fused_backward(kind, idx_c, w_c, v_c, saved, grad, bias_dtype, inv_norm, dweight_mode="atomic",
-                                  peers=ex)
+    out = _losses.fused_backward(kind, idx_c, w_c, v_c, saved, grad, bias_dtype, inv_norm, dweight_mode="atomic",
+                                 peers=ex)
+    if ex is None:  # no peer memory here: the plain collective instead
+        dist.all_reduce(out[0], op=dist.ReduceOp.SUM, group=group)
+    return out
 
 
 class _ShardedDecoderLoss(torch.autograd.Function):
