@@ -1,0 +1,351 @@
+// Batch-sharded backward: the single-launch pipeline with the cross-GPU sum of dweight done by its
+// own blocks over NVLink peer memory.
+#pragma once
+
+#include "flexsae_backward.cuh"
+
+namespace flexsae {
+
+// ---- batch-sharded backward: pipelined kernel + dweight reduction over peer memory ----------------
+// Every rank (one GPU each, same node) runs this kernel on its own batch shard.  The converting
+// blocks of the single-launch pipeline do the cross-GPU sum of dweight themselves, piece by piece,
+// overlapped with the accumulation of the following pieces.  All traffic between GPUs is posted
+// STORES into the peers' buffers (a remote load would stall its thread for microseconds; a store
+// does not), all loads are local:
+//   slot p converts the local slab of piece p-1 (decoder dtype) and SCATTERS it: every decoder row
+//     goes to the inbox of the rank that owns that row block (reduce-scatter by push),
+//   reduces piece p-2: this rank sums the N inbox copies of ITS row block (fixed rank order, fp32),
+//     writes its own dweight rows and BROADCASTS the reduced rows into every peer's gather buffer,
+//   copies piece p-3: the other ranks' reduced row blocks from the local gather buffer to dweight.
+// One flag per (rank, peer) carries all cross-GPU ordering: when the last converting block of
+// slot p finishes, the rank publishes seq_base + p to every rank; the converting blocks of slot p
+// first wait until every rank (itself included) has published slot p-1.  Inbox and gather buffer
+// are double-buffered by piece parity, and "every rank finished slot p-1" is exactly what makes a
+// buffer complete to read and free to overwrite.  Waits are bounded like the local ones.  Plain
+// peer stores only: no multicast of any kind.
+constexpr int kMaxRanks = 8;
+struct ShardArgs {
+  PipeArgs p;
+  int* slot_done;  // [pieces + 3] converting blocks that finished ALL stages of a slot
+  int world, rank, rows_per_rank, seq_base;
+  int exch_blocks;  // blocks per slot that reduce / broadcast / copy older pieces
+  void* mc_inbox;     // multicast address of the inbox region of ALL ranks (NULL: plain peer stores)
+  void* mc_gathered;  // multicast address of the gather buffers of all ranks
+  void* inbox[kMaxRanks];    // rank o's inbox: [2][world][rows_per_rank][PW]
+  void* gathered[kMaxRanks]; // rank o's gather buffer: [2][world * rows_per_rank][PW]
+  int* flags_at[kMaxRanks];  // flag array living on rank s; entry [r] = last slot rank r finished
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void wait_peers(const ShardArgs& sa, int target) {
+  if (threadIdx.x == 0) {
+    int32_t* status = sa.p.b.status;
+    const int* mine = sa.flags_at[sa.rank];
+    for (int s = 0; s < sa.world; s++) {  // this rank too: its own earlier slot reads the buffers this slot rewrites
+      int spins = 0;
+      while (ld_acquire_sys(mine + s) - target < 0) {  // difference: robust to wrap-around
+        __nanosleep(200);
+        ++spins;
+        const bool abandoned = status && (spins & 1023) == 0 &&
+                               (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+        if (spins > kSpinLimit || abandoned) {
+          if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// local slab (fp32, permuted columns) -> decoder dtype, natural column order, each decoder row
+// stored into the inbox of the rank owning its row block; clears the slab
+template <typename T, int G>
+__device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = FLEXSAE_CONVERT_IL;
+  const int F = sa.p.b.F;
+  const int rpr = sa.rows_per_rank;
+  const size_t total = (size_t)F * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  const size_t slot_off = ((size_t)(piece & 1) * sa.world + sa.rank) * rpr * PW;  // [parity][sender = me]
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    float4 lo[IL], hi[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        lo[q] = __ldcg(reinterpret_cast<const float4*>(sp));
+        if (VEC == 8) hi[q] = __ldcg(reinterpret_cast<const float4*>(sp + G * 4));
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        const int f = (int)(i / G), lig = (int)(i % G);
+        float* sp = slab + (size_t)f * PW + lig * 4;
+        *reinterpret_cast<float4*>(sp) = zero;
+        float v[8] = {lo[q].x, lo[q].y, lo[q].z, lo[q].w, 0.f, 0.f, 0.f, 0.f};
+        if (VEC == 8) {
+          *reinterpret_cast<float4*>(sp + G * 4) = zero;
+          v[4] = hi[q].x; v[5] = hi[q].y; v[6] = hi[q].z; v[7] = hi[q].w;
+        }
+        const int owner = f / rpr;
+        T* dst = reinterpret_cast<T*>(sa.inbox[owner]) + slot_off + (size_t)(f - owner * rpr) * PW + lig * VEC;
+        *reinterpret_cast<uint4*>(dst) = Pack<T>::pack(v);  // a peer store unless this rank owns the row
+      }
+    }
+  }
+}
+
+// this rank's row block of one piece: sum of the N inbox copies in rank order -> own dweight rows
+// and every peer's gather buffer.  IL items per thread in flight (IL * world local 16-byte loads).
+template <typename T, int G, int IL>
+__device__ __forceinline__ void reduce_broadcast(const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int W = kMaxRanks / IL;  // largest world size this instantiation serves
+  const int F = sa.p.b.F, D = sa.p.b.D;
+  const int rpr = sa.rows_per_rank;
+  const int row0 = sa.rank * rpr;
+  const int rows = max(0, min(F, row0 + rpr) - row0);
+  const size_t total = (size_t)rows * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  const T* in = reinterpret_cast<const T*>(sa.inbox[sa.rank]) + (size_t)(piece & 1) * sa.world * rpr * PW;
+  const size_t sender_stride = (size_t)rpr * PW;
+  const size_t gat_off = ((size_t)(piece & 1) * sa.world * rpr + row0) * PW;
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    uint4 v[IL][W];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+#pragma unroll
+      for (int s = 0; s < W; s++)
+        if (i < total && s < sa.world) v[q][s] = __ldcg(reinterpret_cast<const uint4*>(in + s * sender_stride + i * VEC));
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float acc[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; j++) acc[j] = 0.f;
+#pragma unroll
+        for (int s = 0; s < W; s++)
+          if (s < sa.world) {
+            float f[VEC];
+            Pack<T>::unpack(v[q][s], f);
+#pragma unroll
+            for (int j = 0; j < VEC; j++) acc[j] += f[j];
+          }
+        const uint4 out = Pack<T>::pack(acc);
+#pragma unroll
+        for (int o = 0; o < kMaxRanks; o++)
+          if (o < sa.world && o != sa.rank)
+            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.gathered[o]) + gat_off + i * VEC) = out;  // peer store
+        const int col = piece * PW + (int)(i % G) * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)(row0 + i / G) * D + col) = out;
+      }
+    }
+  }
+}
+
+// the other ranks' reduced row blocks of one piece: local gather buffer -> this rank's dweight
+template <typename T, int G>
+__device__ __forceinline__ void copy_gathered(const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = 8;
+  const int F = sa.p.b.F, D = sa.p.b.D;
+  const int rpr = sa.rows_per_rank;
+  const size_t total = (size_t)F * G;  // items of the whole piece; this rank's own block is skipped
+  const size_t stride = (size_t)nctas * kThreads;
+  const T* src = reinterpret_cast<const T*>(sa.gathered[sa.rank]) + (size_t)(piece & 1) * sa.world * rpr * PW;
+  const int own0 = sa.rank * rpr, own1 = own0 + rpr;
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    uint4 v[IL];
+    bool take[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      const int f = (int)(i / G);
+      take[q] = i < total && (f < own0 || f >= own1);
+      if (take[q]) v[q] = __ldcg(reinterpret_cast<const uint4*>(src + i * VEC));
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      if (take[q]) {
+        const size_t i = base + q * stride;
+        const int col = piece * PW + (int)(i % G) * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (i / G) * D + col) = v[q];
+      }
+    }
+  }
+}
+
+// ---- the same three stages through the NVSwitch (multimem), when the buffers are bound to a
+// multicast object: per GPU and step it moves F*D*sw bytes in each direction instead of
+// 2*(N-1)/N times that, and a reduction is one load instead of N.
+//   convert: slab -> this rank's OWN copy of the piece (region "inbox", used as [2][F][PW])
+//   reduce:  multimem.ld_reduce of this rank's row block (the switch adds all ranks' copies in
+//            fp32) -> own dweight rows + multimem.st into every rank's gather buffer
+//   copy:    as before
+template <typename T, int G>
+__device__ __forceinline__ void slab_to_own_copy(float* slab, const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = FLEXSAE_CONVERT_IL;
+  const int F = sa.p.b.F;
+  const size_t total = (size_t)F * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  T* x = reinterpret_cast<T*>(sa.inbox[sa.rank]) + (size_t)(piece & 1) * sa.world * sa.rows_per_rank * PW;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    float4 lo[IL], hi[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        lo[q] = __ldcg(reinterpret_cast<const float4*>(sp));
+        if (VEC == 8) hi[q] = __ldcg(reinterpret_cast<const float4*>(sp + G * 4));
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
+        *reinterpret_cast<float4*>(sp) = zero;
+        float v[8] = {lo[q].x, lo[q].y, lo[q].z, lo[q].w, 0.f, 0.f, 0.f, 0.f};
+        if (VEC == 8) {
+          *reinterpret_cast<float4*>(sp + G * 4) = zero;
+          v[4] = hi[q].x; v[5] = hi[q].y; v[6] = hi[q].z; v[7] = hi[q].w;
+        }
+        *reinterpret_cast<uint4*>(x + i * VEC) = Pack<T>::pack(v);
+      }
+    }
+  }
+}
+
+template <typename T, int G>
+__device__ __forceinline__ void switch_reduce_broadcast(const ShardArgs& sa, int piece, int cta, int nctas) {
+  constexpr int VEC = Pack<T>::VEC;
+  constexpr int PW = G * VEC;
+  constexpr int IL = 8;  // switch reductions in flight per thread (each is a round trip through the NVSwitch)
+  const int F = sa.p.b.F, D = sa.p.b.D;
+  const int rpr = sa.rows_per_rank;
+  const int row0 = sa.rank * rpr;
+  const int rows = max(0, min(F, row0 + rpr) - row0);
+  const size_t total = (size_t)rows * G;
+  const size_t stride = (size_t)nctas * kThreads;
+  const size_t par = (size_t)(piece & 1) * sa.world * rpr * PW;
+  const T* mc_x = reinterpret_cast<const T*>(sa.mc_inbox) + par + (size_t)row0 * PW;
+  T* mc_y = reinterpret_cast<T*>(sa.mc_gathered) + par + (size_t)row0 * PW;
+  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+    uint4 v[IL];
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) v[q] = multimem_ld_reduce<T>(mc_x + i * VEC);
+    }
+#pragma unroll
+    for (int q = 0; q < IL; q++) {
+      const size_t i = base + q * stride;
+      if (i < total) {
+        multimem_st(mc_y + i * VEC, v[q]);
+        const int col = piece * PW + (int)(i % G) * VEC;
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)(row0 + i / G) * D + col) = v[q];
+      }
+    }
+  }
+}
+
+// Block roles inside slot p of the sharded launch (slots 0..pieces+2):
+//   exchange blocks (sa.exch_blocks, first in the slot): reduce + broadcast of piece p-2 and the
+//     copy of piece p-3 -- local loads and posted stores only, so a few blocks keep up;
+//   unit blocks: accumulate piece p;
+//   converting blocks (inserted at conv_offset): slab of piece p-1 -> scattered to the owners, cleared.
+// A slot is finished on a rank when all its exchange and converting blocks are.
+template <typename T, int G, bool HIER>
+__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_kernel(const ShardArgs sa) {
+  extern __shared__ uint4 smem[];
+  const PipeArgs& pa = sa.p;
+  const int P = pa.pieces;
+  const int E = sa.exch_blocks;
+  const int per = E + pa.unit_blocks + pa.conv_blocks;
+  const int body = P * per;
+  int p, exch_idx = -1, conv_idx = -1, unit_block = -1;
+  int exch_n = E;  // blocks that share the exchange work of this slot
+  if ((int)blockIdx.x >= body) {  // three draining slots: no unit blocks, so every block helps with the exchange
+    const int t = blockIdx.x - body;
+    const int dper = E + pa.conv_blocks;
+    p = P + t / dper;
+    const int r = t - (p - P) * dper;
+    if (p == P && r >= E) {
+      conv_idx = r - E;  // slot P still has the last slab to convert
+    } else {
+      exch_idx = r;
+      exch_n = (p == P) ? E : dper;
+    }
+  } else {
+    p = blockIdx.x / per;
+    int r = blockIdx.x - p * per;
+    if (r < E) {
+      exch_idx = r;
+    } else {
+      r -= E;
+      if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) conv_idx = r - pa.conv_offset;
+      else unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
+    }
+  }
+  if (unit_block >= 0) {
+    if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status);  // slot p-1 cleared this slab
+    walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
+    signal_done(pa.walk_done + p);
+    return;
+  }
+  if (conv_idx >= 0) {
+    if (p >= 1 && p - 1 < P) {
+      wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);  // the local slab is complete
+      wait_peers(sa, sa.seq_base + p - 1);  // the owners have read what this parity of their inbox held
+      if (sa.mc_inbox) slab_to_own_copy<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
+      else slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
+    }
+    signal_done(pa.conv_done + p);
+  } else {
+    if (p >= 2) wait_peers(sa, sa.seq_base + p - 1);  // inbox of piece p-2 and gather buffer of piece p-3 are complete
+    if (p >= 2 && p - 2 < P && sa.mc_inbox) {
+      switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, exch_n);
+    } else if (p >= 2 && p - 2 < P) {
+      if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, exch_idx, exch_n);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, exch_idx, exch_n);
+      else reduce_broadcast<T, G, 1>(sa, p - 2, exch_idx, exch_n);
+    }
+    if (p >= 3 && p - 3 < P) copy_gathered<T, G>(sa, p - 3, exch_idx, exch_n);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // this block's peer stores and dweight writes before the count moves
+    const int old = atomicAdd(sa.slot_done + p, 1);
+    if (old == E + pa.conv_blocks - 1) {  // the whole slot is done on this rank: tell every rank
+      __threadfence_system();
+      for (int s = 0; s < sa.world; s++) st_release_sys(sa.flags_at[s] + sa.rank, sa.seq_base + p);
+    }
+  }
+}
+
+}  // namespace flexsae
