@@ -203,6 +203,7 @@ def main():
     fx.config.dweight_mode = args.dweight_mode
     fd.config.use_multicast = os.environ.get("FLEXSAE_MULTICAST", "0") != "0"
     fd.config.peer_reduce = os.environ.get("FLEXSAE_PEER_REDUCE", "1") != "0"
+    fd.config.symmetric_dweight = os.environ.get("FLEXSAE_SYMMETRIC_DWEIGHT", "0") != "0"
     for item in filter(None, os.environ.get("FLEXSAE_OPTIONS", "").split(",")):   # e.g. "lanes_bwd=8,segments=2"
         name, value = item.split("=")
         nv.set_option(name, int(value))

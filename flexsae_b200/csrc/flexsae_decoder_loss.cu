@@ -39,6 +39,9 @@ struct Options {
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
   int convert_offset_pct = 60;  // where, inside a piece's unit blocks, the previous piece's converters sit
   int exchange_blocks = 148;    // sharded backward: blocks per slot for the cross-GPU reduce / broadcast / copy
+  int exchange_offset_pct = 0;  // ... and where inside a piece's unit blocks they sit (capped at convert_offset_pct)
+  int scatter_rotate = 0;       // sharded backward: ranks start their scatter sweeps at different row blocks
+  int flag_fan_out = 0;         // sharded backward: a finished slot is announced by one thread per rank
   int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
 };
 static Options g_opt;
@@ -183,7 +186,7 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   p.off_s0 = off;  // summed prefix residuals of every row (Hierarchical; TopK does not use it)
   off = align_up(off + (size_t)s.B * s.D * 4, 256);
   p.off_ctr = off;  // per-piece completion counters of the single-launch pipeline
-  off = align_up(off + (size_t)(3 * p.pieces + 6) * 4, 256);
+  off = align_up(off + (size_t)(4 * p.pieces + 9) * 4, 256);
   p.total = off;
   return p;
 }
@@ -309,6 +312,7 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   pa.walk_done = counters;
   pa.conv_done = counters + pieces;       // one counter per slot: pieces + 3 of them
   sa.slot_done = counters + 2 * pieces + 3;  // and pieces + 3 more
+  sa.scatter_done = counters + 3 * pieces + 6;  // and again
   pa.pieces = pieces;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
@@ -318,6 +322,10 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   pa.conv_blocks = conv;
   pa.conv_offset = (int)((long long)pa.unit_blocks * g_opt.convert_offset_pct / 100);
   sa.exch_blocks = g_opt.exchange_blocks;
+  sa.exch_offset = (int)((long long)pa.unit_blocks * g_opt.exchange_offset_pct / 100);
+  if (sa.exch_offset > pa.conv_offset) sa.exch_offset = pa.conv_offset;
+  sa.rotate = g_opt.scatter_rotate;
+  sa.fan_out = g_opt.flag_fan_out;
   const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks + conv) + 3ll * (sa.exch_blocks + conv);
   if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
   kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
@@ -360,6 +368,9 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "convert_offset_pct") && value >= 0 && value <= 100) { g_opt.convert_offset_pct = (int)value; return 0; }
   if (!strcmp(name, "direct_f32") && (value == 0 || value == 1)) { g_opt.direct_f32 = (int)value; return 0; }
   if (!strcmp(name, "exchange_blocks") && value >= 1 && value <= 4096) { g_opt.exchange_blocks = (int)value; return 0; }
+  if (!strcmp(name, "exchange_offset_pct") && value >= 0 && value <= 100) { g_opt.exchange_offset_pct = (int)value; return 0; }
+  if (!strcmp(name, "scatter_rotate") && (value == 0 || value == 1)) { g_opt.scatter_rotate = (int)value; return 0; }
+  if (!strcmp(name, "flag_fan_out") && (value == 0 || value == 1)) { g_opt.flag_fan_out = (int)value; return 0; }
   return fail(FLEXSAE_EINVAL, "unknown option or value: %s=%lld", name, (long long)value);
 }
 
@@ -373,6 +384,9 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "convert_offset_pct")) return g_opt.convert_offset_pct;
   if (!strcmp(name, "direct_f32")) return g_opt.direct_f32;
   if (!strcmp(name, "exchange_blocks")) return g_opt.exchange_blocks;
+  if (!strcmp(name, "exchange_offset_pct")) return g_opt.exchange_offset_pct;
+  if (!strcmp(name, "scatter_rotate")) return g_opt.scatter_rotate;
+  if (!strcmp(name, "flag_fan_out")) return g_opt.flag_fan_out;
   return -1;
 }
 
@@ -455,6 +469,7 @@ struct PeerInfo {  // batch-sharded call: who the other GPUs are and where their
   void* const* flags;
   void* mc_x;
   void* mc_y;
+  void* const* dweight;  // every rank's dweight (peer-mapped), or NULL
 };
 
 static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, const void* vals, const float* state,
@@ -537,7 +552,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
   if (e != cudaSuccess) return fail((int)e, "gradient clear failed: %s", cudaGetErrorString(e));
   if (peers) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
-    e = cudaMemsetAsync(counters, 0, (size_t)(3 * p.pieces + 6) * 4, st);
+    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 9) * 4, st);
     if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
     a.piece = a.conv_piece = -1;
     a.slab = a.conv_slab = nullptr;
@@ -554,6 +569,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
       sa.inbox[r] = r < peers->world ? peers->x[r] : nullptr;
       sa.gathered[r] = r < peers->world ? peers->y[r] : nullptr;
       sa.flags_at[r] = r < peers->world ? reinterpret_cast<int*>(peers->flags[r]) : nullptr;
+      sa.dweight_at[r] = (peers->dweight && r < peers->world) ? peers->dweight[r] : nullptr;
     }
 #define CALL_SHARD(T, G, H) launch_bwd_sharded<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, sa, st)
     e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD);
@@ -561,7 +577,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     if (e != cudaSuccess) return fail((int)e, "sharded backward launch failed: %s", cudaGetErrorString(e));
   } else if (g_opt.pipeline) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
-    e = cudaMemsetAsync(counters, 0, (size_t)(3 * p.pieces + 6) * 4, st);
+    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 9) * 4, st);
     if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
     a.piece = a.conv_piece = -1;
     a.slab = a.conv_slab = nullptr;
@@ -634,7 +650,8 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
                              void* dbias, void* workspace, size_t workspace_bytes, int64_t B, int64_t K, int64_t F,
                              int64_t D, int weight_dtype, int vals_dtype, int bias_dtype, double inv_norm,
                              int32_t* status, void* stream, int world, int rank, int seq_base, void* const* x_ptrs,
-                             void* const* y_ptrs, void* const* flag_ptrs, void* multicast_x, void* multicast_y) {
+                             void* const* y_ptrs, void* const* flag_ptrs, void* multicast_x, void* multicast_y,
+                             void* const* dweight_ptrs) {
   if (world < 2 || world > kMaxRanks) return fail(FLEXSAE_EINVAL, "world size %d outside [2, %d]", world, kMaxRanks);
   if (rank < 0 || rank >= world) return fail(FLEXSAE_EINVAL, "rank %d outside [0, %d)", rank, world);
   if (!x_ptrs || !y_ptrs || !flag_ptrs) return fail(FLEXSAE_EINVAL, "null pointer argument");
@@ -644,11 +661,35 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
   if (seq_base < 1) return fail(FLEXSAE_EINVAL, "seq_base must be >= 1");
   if ((multicast_x == nullptr) != (multicast_y == nullptr) || !aligned16(multicast_x) || !aligned16(multicast_y))
     return fail(FLEXSAE_EINVAL, "multicast addresses must both be given (16-byte aligned) or both be NULL");
-  PeerInfo peers{world, rank, seq_base, x_ptrs, y_ptrs, flag_ptrs, multicast_x, multicast_y};
+  if (dweight_ptrs) {
+    if (multicast_x) return fail(FLEXSAE_EINVAL, "dweight_ptrs cannot be combined with the multicast path");
+    for (int r = 0; r < world; r++)
+      if (!dweight_ptrs[r] || !aligned16(dweight_ptrs[r]))
+        return fail(FLEXSAE_EINVAL, "dweight of rank %d is null or not 16-byte aligned", r);
+    if (dweight_ptrs[rank] != dweight)
+      return fail(FLEXSAE_EINVAL, "dweight_ptrs[rank] must be this rank's dweight");
+  }
+  PeerInfo peers{world, rank, seq_base, x_ptrs, y_ptrs, flag_ptrs, multicast_x, multicast_y, dweight_ptrs};
   return loss_bwd_impl(kind, indices, weight, vals, state, segments, grad_out, dweight, dvals, dbias, workspace,
                        workspace_bytes, B, K, F, D, weight_dtype, vals_dtype, bias_dtype, inv_norm, FLEXSAE_DW_ATOMIC,
                        status, stream, &peers);
 }
+
+#ifdef FLEXSAE_TRACE
+// Tuning builds only: copy the current device's slot timeline of the sharded backward to the host
+// (and clear it).  Synchronises the device.
+int flexsae_debug_trace_read(unsigned long long* out, size_t bytes, int clear) {
+  if (!out || bytes != sizeof(unsigned long long) * 64 * kTrFields) return fail(FLEXSAE_EINVAL, "trace table is %zu bytes", sizeof(unsigned long long) * 64 * kTrFields);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out, g_trace, bytes);
+  if (e == cudaSuccess && clear) {
+    static unsigned long long zeros[64 * kTrFields];
+    e = cudaMemcpyToSymbol(g_trace, zeros, bytes);
+  }
+  if (e != cudaSuccess) return fail((int)e, "trace read failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+#endif
 
 int flexsae_shard_slots(int64_t F, int64_t D, int weight_dtype) {
   Shape s{1, 1, F, D};

@@ -17,24 +17,58 @@ namespace flexsae {
 //   reduces piece p-2: this rank sums the N inbox copies of ITS row block (fixed rank order, fp32),
 //     writes its own dweight rows and BROADCASTS the reduced rows into every peer's gather buffer,
 //   copies piece p-3: the other ranks' reduced row blocks from the local gather buffer to dweight.
-// One flag per (rank, peer) carries all cross-GPU ordering: when the last converting block of
-// slot p finishes, the rank publishes seq_base + p to every rank; the converting blocks of slot p
-// first wait until every rank (itself included) has published slot p-1.  Inbox and gather buffer
-// are double-buffered by piece parity, and "every rank finished slot p-1" is exactly what makes a
-// buffer complete to read and free to overwrite.  Waits are bounded like the local ones.  Plain
-// peer stores only: no multicast of any kind.
+// Two flags per (rank, peer) carry all cross-GPU ordering.  When the last converting block of slot p
+// finishes, the rank publishes seq_base + p in its SCATTER flag on every rank; when the last exchange
+// block of slot p finishes, the same in its EXCHANGE flag.  Who waits for what:
+//   converting blocks of slot p (they overwrite the inbox half that held piece p-3): every rank's
+//     exchange flag >= slot p-1, i.e. the owners have reduced piece p-3;
+//   exchange blocks of slot p: every rank's scatter flag >= slot p-1 (the inbox copies of piece p-2
+//     are complete) and, because the gather buffer is double-buffered as well, every rank's exchange
+//     flag >= slot p-1 (piece p-3 has been broadcast, piece p-4 copied out).
+// With peer-mapped dweight tables there is no gather buffer and the exchange blocks wait for the
+// scatter flags only (plus, in the very last slot, for every rank's last broadcast): an exchange may
+// then take longer than one slot without holding anything up.  Waits are bounded like the local
+// ones.  Plain peer stores only: no multicast of any kind.
 constexpr int kMaxRanks = 8;
+constexpr int kScatterFlags = 32;  // offset (ints) of the scatter flags inside a rank's flag array
 struct ShardArgs {
   PipeArgs p;
-  int* slot_done;  // [pieces + 3] converting blocks that finished ALL stages of a slot
+  int* slot_done;  // [pieces + 3] exchange blocks of a slot that have finished
+  int* scatter_done;  // [pieces + 3] converting blocks of a slot whose peer stores are out
   int world, rank, rows_per_rank, seq_base;
   int exch_blocks;  // blocks per slot that reduce / broadcast / copy older pieces
+  int exch_offset;  // unit blocks of a slot dispatched before its exchange blocks (<= conv_offset)
+  int rotate;       // 1: each rank starts its scatter sweep at its right-hand neighbour's row block
+  int fan_out;      // 1: the flags of a finished slot are stored by one thread per destination rank
   void* mc_inbox;     // multicast address of the inbox region of ALL ranks (NULL: plain peer stores)
   void* mc_gathered;  // multicast address of the gather buffers of all ranks
   void* inbox[kMaxRanks];    // rank o's inbox: [2][world][rows_per_rank][PW]
   void* gathered[kMaxRanks]; // rank o's gather buffer: [2][world * rows_per_rank][PW]
-  int* flags_at[kMaxRanks];  // flag array living on rank s; entry [r] = last slot rank r finished
+  int* flags_at[kMaxRanks];  // flag array living on rank s: [r] = last slot whose exchange rank r finished,
+                             // [kScatterFlags + r] = last slot whose scatter rank r finished
+  void* dweight_at[kMaxRanks];  // every rank's dweight when those are peer-mapped: the broadcast then
+                                // lands in place and the gather buffer and its copy are not used (else NULL)
 };
+
+// Tuning builds (-DFLEXSAE_TRACE) record, per slot, when each block role started and ended on
+// this GPU's nanosecond timer; flexsae_debug_trace_read returns the table.  Minima are kept as
+// the maximum of the complement so that a cleared table is all zeros.
+enum { kTrUnitStart, kTrUnitEnd, kTrConvEntry, kTrConvStart, kTrConvEnd, kTrExchEntry, kTrExchStart, kTrExchEnd, kTrFields };
+#ifdef FLEXSAE_TRACE
+__device__ unsigned long long g_trace[64][kTrFields];
+__device__ __forceinline__ void trace_mark(int slot, int field, bool is_min) {
+  if (threadIdx.x == 0 && slot < 64) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    atomicMax(&g_trace[slot][field], is_min ? ~t : t);
+  }
+}
+#define FLEXSAE_TRACE_MIN(slot, field) trace_mark(slot, field, true)
+#define FLEXSAE_TRACE_MAX(slot, field) trace_mark(slot, field, false)
+#else
+#define FLEXSAE_TRACE_MIN(slot, field)
+#define FLEXSAE_TRACE_MAX(slot, field)
+#endif
 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
@@ -46,21 +80,24 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__device__ __forceinline__ void wait_peers(const ShardArgs& sa, int target) {
-  if (threadIdx.x == 0) {
+// One thread per (rank, flag kind) polls: lanes 0..world-1 of warp 0 the exchange flags, of warp 1
+// the scatter flags (this rank's own flags too: its own earlier slots use the same buffers).
+__device__ __forceinline__ void wait_peers(const ShardArgs& sa, bool need_exchange, int exchange_target,
+                                           bool need_scatter, int scatter_target) {
+  const int kind = threadIdx.x >> 5, s = threadIdx.x & 31;
+  if (kind < 2 && s < sa.world && (kind == 0 ? need_exchange : need_scatter)) {
     int32_t* status = sa.p.b.status;
-    const int* mine = sa.flags_at[sa.rank];
-    for (int s = 0; s < sa.world; s++) {  // this rank too: its own earlier slot reads the buffers this slot rewrites
-      int spins = 0;
-      while (ld_acquire_sys(mine + s) - target < 0) {  // difference: robust to wrap-around
-        __nanosleep(200);
-        ++spins;
-        const bool abandoned = status && (spins & 1023) == 0 &&
-                               (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-        if (spins > kSpinLimit || abandoned) {
-          if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-          break;
-        }
+    const int* flag = sa.flags_at[sa.rank] + kind * kScatterFlags + s;
+    const int target = kind == 0 ? exchange_target : scatter_target;
+    int spins = 0;
+    while (ld_acquire_sys(flag) - target < 0) {  // difference: robust to wrap-around
+      __nanosleep(100);
+      ++spins;
+      const bool abandoned = status && (spins & 1023) == 0 &&
+                             (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+      if (spins > kSpinLimit || abandoned) {
+        if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+        break;
       }
     }
   }
@@ -79,22 +116,27 @@ __device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, i
   const size_t total = (size_t)F * G;
   const size_t stride = (size_t)nctas * kThreads;
   const size_t slot_off = ((size_t)(piece & 1) * sa.world + sa.rank) * rpr * PW;  // [parity][sender = me]
+  // Rotated sweep: every rank starts at the row block of its right-hand neighbour; the ranks move
+  // in step, so at any moment they store to different owners instead of all to one.
+  const size_t rot = sa.rotate ? ((size_t)((sa.rank + 1) % sa.world) * rpr % F) * G : 0;
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
     float4 lo[IL], hi[IL];
+    size_t item[IL];
 #pragma unroll
     for (int q = 0; q < IL; q++) {
-      const size_t i = base + q * stride;
-      if (i < total) {
-        float* sp = slab + (i / G) * PW + (i % G) * 4;
+      const size_t j = base + q * stride;
+      item[q] = j + rot < total ? j + rot : j + rot - total;  // only used when j < total
+      if (j < total) {
+        float* sp = slab + (item[q] / G) * PW + (item[q] % G) * 4;
         lo[q] = __ldcg(reinterpret_cast<const float4*>(sp));
         if (VEC == 8) hi[q] = __ldcg(reinterpret_cast<const float4*>(sp + G * 4));
       }
     }
 #pragma unroll
     for (int q = 0; q < IL; q++) {
-      const size_t i = base + q * stride;
-      if (i < total) {
+      const size_t i = item[q];
+      if (base + q * stride < total) {
         const int f = (int)(i / G), lig = (int)(i % G);
         float* sp = slab + (size_t)f * PW + lig * 4;
         *reinterpret_cast<float4*>(sp) = zero;
@@ -112,8 +154,9 @@ __device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, i
 }
 
 // this rank's row block of one piece: sum of the N inbox copies in rank order -> own dweight rows
-// and every peer's gather buffer.  IL items per thread in flight (IL * world local 16-byte loads).
-template <typename T, int G, int IL>
+// and every peer's gather buffer (IN_PLACE: straight into every peer's dweight rows instead).
+// IL items per thread in flight (IL * world local 16-byte loads).
+template <typename T, int G, int IL, bool IN_PLACE>
 __device__ __forceinline__ void reduce_broadcast(const ShardArgs& sa, int piece, int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
@@ -152,12 +195,20 @@ __device__ __forceinline__ void reduce_broadcast(const ShardArgs& sa, int piece,
             for (int j = 0; j < VEC; j++) acc[j] += f[j];
           }
         const uint4 out = Pack<T>::pack(acc);
-#pragma unroll
-        for (int o = 0; o < kMaxRanks; o++)
-          if (o < sa.world && o != sa.rank)
-            *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.gathered[o]) + gat_off + i * VEC) = out;  // peer store
         const int col = piece * PW + (int)(i % G) * VEC;
-        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + (size_t)(row0 + i / G) * D + col) = out;
+        const size_t dw_off = (size_t)(row0 + i / G) * D + col;
+        if (IN_PLACE) {
+#pragma unroll
+          for (int o = 0; o < kMaxRanks; o++)
+            if (o < sa.world && o != sa.rank && col < D)
+              *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.dweight_at[o]) + dw_off) = out;  // peer store
+        } else {
+#pragma unroll
+          for (int o = 0; o < kMaxRanks; o++)
+            if (o < sa.world && o != sa.rank)
+              *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.gathered[o]) + gat_off + i * VEC) = out;  // peer store
+        }
+        if (col < D) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(sa.p.b.dweight) + dw_off) = out;
       }
     }
   }
@@ -275,11 +326,11 @@ __device__ __forceinline__ void switch_reduce_broadcast(const ShardArgs& sa, int
 }
 
 // Block roles inside slot p of the sharded launch (slots 0..pieces+2):
-//   exchange blocks (sa.exch_blocks, first in the slot): reduce + broadcast of piece p-2 and the
-//     copy of piece p-3 -- local loads and posted stores only, so a few blocks keep up;
+//   exchange blocks (sa.exch_blocks, after the first sa.exch_offset unit blocks): reduce + broadcast
+//     of piece p-2 and the copy of piece p-3 -- local loads and posted stores only, so a few blocks
+//     keep up; placed a little into the slot so that what they wait for has usually arrived;
 //   unit blocks: accumulate piece p;
 //   converting blocks (inserted at conv_offset): slab of piece p-1 -> scattered to the owners, cleared.
-// A slot is finished on a rank when all its exchange and converting blocks are.
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_kernel(const ShardArgs sa) {
   extern __shared__ uint4 smem[];
@@ -290,6 +341,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   const int body = P * per;
   int p, exch_idx = -1, conv_idx = -1, unit_block = -1;
   int exch_n = E;  // blocks that share the exchange work of this slot
+  const bool in_place = sa.dweight_at[0] != nullptr && sa.mc_inbox == nullptr;
   if ((int)blockIdx.x >= body) {  // three draining slots: no unit blocks, so every block helps with the exchange
     const int t = blockIdx.x - body;
     const int dper = E + pa.conv_blocks;
@@ -304,8 +356,10 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   } else {
     p = blockIdx.x / per;
     int r = blockIdx.x - p * per;
-    if (r < E) {
-      exch_idx = r;
+    if (r < sa.exch_offset) {
+      unit_block = r;
+    } else if (r < sa.exch_offset + E) {
+      exch_idx = r - sa.exch_offset;
     } else {
       r -= E;
       if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) conv_idx = r - pa.conv_offset;
@@ -314,38 +368,67 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   }
   if (unit_block >= 0) {
     if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status);  // slot p-1 cleared this slab
+    FLEXSAE_TRACE_MIN(p, kTrUnitStart);
     walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
     signal_done(pa.walk_done + p);
+    FLEXSAE_TRACE_MAX(p, kTrUnitEnd);
     return;
   }
   if (conv_idx >= 0) {
+    FLEXSAE_TRACE_MIN(p, kTrConvEntry);
     if (p >= 1 && p - 1 < P) {
       wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);  // the local slab is complete
-      wait_peers(sa, sa.seq_base + p - 1);  // the owners have read what this parity of their inbox held
+      wait_peers(sa, true, sa.seq_base + p - 1, false, 0);  // the owners have reduced what this half of their inbox held
+      FLEXSAE_TRACE_MIN(p, kTrConvStart);
       if (sa.mc_inbox) slab_to_own_copy<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
       else slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
     }
     signal_done(pa.conv_done + p);
+    FLEXSAE_TRACE_MAX(p, kTrConvEnd);
   } else {
-    if (p >= 2) wait_peers(sa, sa.seq_base + p - 1);  // inbox of piece p-2 and gather buffer of piece p-3 are complete
+    FLEXSAE_TRACE_MIN(p, kTrExchEntry);
+    // the inbox copies of piece p-2 are complete (the last scatter happens in slot P); through the
+    // gather buffer also: piece p-3 has arrived in it and piece p-4 has been copied out everywhere;
+    // in place: the very last slot returns only when every rank's last broadcast has landed here
+    if (p >= 2) wait_peers(sa, !in_place || p == P + 2, sa.seq_base + p - 1, true, sa.seq_base + min(p - 1, P));
+    FLEXSAE_TRACE_MIN(p, kTrExchStart);
     if (p >= 2 && p - 2 < P && sa.mc_inbox) {
       switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, exch_n);
     } else if (p >= 2 && p - 2 < P) {
-      if (sa.world <= 2) reduce_broadcast<T, G, 4>(sa, p - 2, exch_idx, exch_n);
-      else if (sa.world <= 4) reduce_broadcast<T, G, 2>(sa, p - 2, exch_idx, exch_n);
-      else reduce_broadcast<T, G, 1>(sa, p - 2, exch_idx, exch_n);
+      if (in_place) {
+        if (sa.world <= 2) reduce_broadcast<T, G, 4, true>(sa, p - 2, exch_idx, exch_n);
+        else if (sa.world <= 4) reduce_broadcast<T, G, 2, true>(sa, p - 2, exch_idx, exch_n);
+        else reduce_broadcast<T, G, 1, true>(sa, p - 2, exch_idx, exch_n);
+      } else {
+        if (sa.world <= 2) reduce_broadcast<T, G, 4, false>(sa, p - 2, exch_idx, exch_n);
+        else if (sa.world <= 4) reduce_broadcast<T, G, 2, false>(sa, p - 2, exch_idx, exch_n);
+        else reduce_broadcast<T, G, 1, false>(sa, p - 2, exch_idx, exch_n);
+      }
     }
-    if (p >= 3 && p - 3 < P) copy_gathered<T, G>(sa, p - 3, exch_idx, exch_n);
+    // in-place broadcast: nothing to copy, but slot pieces+2 still waits (above) until every rank's
+    // last broadcast has landed in this rank's dweight
+    if (p >= 3 && p - 3 < P && !in_place) copy_gathered<T, G>(sa, p - 3, exch_idx, exch_n);
   }
   __syncthreads();
+  if (exch_idx >= 0) { FLEXSAE_TRACE_MAX(p, kTrExchEnd); }
+  // The last block of its kind in the slot tells every rank: thread 0 alone, one release store after
+  // the other, or (fan_out) one thread per destination so that the stores travel side by side.
+  __shared__ int s_publish;
+  const bool scatter = conv_idx >= 0;
   if (threadIdx.x == 0) {
     __threadfence_system();  // this block's peer stores and dweight writes before the count moves
-    const int old = atomicAdd(sa.slot_done + p, 1);
-    if (old == E + pa.conv_blocks - 1) {  // the whole slot is done on this rank: tell every rank
+    const int old = atomicAdd((scatter ? sa.scatter_done : sa.slot_done) + p, 1);
+    const bool last = old == (scatter ? pa.conv_blocks : exch_n) - 1;
+    s_publish = last && sa.fan_out;
+    if (last && !sa.fan_out) {
       __threadfence_system();
-      for (int s = 0; s < sa.world; s++) st_release_sys(sa.flags_at[s] + sa.rank, sa.seq_base + p);
+      for (int s = 0; s < sa.world; s++)
+        st_release_sys(sa.flags_at[s] + (scatter ? kScatterFlags : 0) + sa.rank, sa.seq_base + p);
     }
   }
+  __syncthreads();
+  if (s_publish && (int)threadIdx.x < sa.world)  // each release orders what the block has seen before its own store
+    st_release_sys(sa.flags_at[threadIdx.x] + (scatter ? kScatterFlags : 0) + sa.rank, sa.seq_base + p);
 }
 
 }  // namespace flexsae

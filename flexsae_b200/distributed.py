@@ -36,6 +36,13 @@ class config:
     #: bound to a multicast object; otherwise, or when False, plain peer stores.  Off by default:
     #: measured on 2 GPUs it is 7 % slower than peer stores (it saves bytes only from 4 ranks up)
     use_multicast: bool = False
+    #: keep ``weight.grad`` of the sharded losses in one persistent peer-mapped table per decoder
+    #: shape, so that the reduced rows are stored straight into every rank's gradient (no gather
+    #: buffer, no copy pass).  The gradient a backward returns is then a view of that table and the
+    #: NEXT sharded backward of the same shape overwrites it: consume it (optimizer step) and drop
+    #: it (``grad = None`` / ``zero_grad(set_to_none=True)``) before then, on the same stream.  A
+    #: backward that finds the previous gradient still referenced raises instead of overwriting it.
+    symmetric_dweight: bool = False
 
 
 class PeerExchange:
@@ -74,11 +81,33 @@ class PeerExchange:
         self.mc_x = ctypes.c_void_p(mc) if mc else None
         self.mc_y = ctypes.c_void_p(mc + xb.value) if mc else None
         self.seq = 1
+        self.dweight = None
+        if config.symmetric_dweight and not self.multicast:
+            with torch.cuda.device(device):
+                flat = symm_mem.empty(F * D, dtype=dtype, device=device)
+                self.dweight_handle = symm_mem.rendezvous(flat, group if group is not None else dist.group.WORLD)
+                self.dweight = flat.view(F, D)
+                del flat
+            self.dweight_ptrs = arr(*[int(p) for p in self.dweight_handle.buffer_ptrs])
+            self._dweight_refs = _storage_refs(self.dweight)
+
+    def take_dweight(self):
+        """A fresh view of the persistent gradient table plus every rank's address of it."""
+        if _storage_refs(self.dweight) > self._dweight_refs:
+            raise RuntimeError("flexsae_b200: the weight gradient of the previous sharded backward is still referenced and "
+                               "this backward would overwrite it; drop it first (grad = None) or set "
+                               "flexsae_b200.distributed.config.symmetric_dweight = False")
+        return self.dweight.view(self.dweight.shape), self.dweight_ptrs
 
     def next_seq(self) -> int:
         seq = self.seq
         self.seq += self.slots
         return seq
+
+
+def _storage_refs(t: torch.Tensor) -> int:
+    """How many tensors (and storage handles) share ``t``'s memory."""
+    return torch._C._storage_Use_Count(t.untyped_storage()._cdata)
 
 
 _exchanges: Dict[tuple, PeerExchange] = {}
@@ -89,7 +118,8 @@ def peer_exchange(group, device: torch.device, F: int, D: int, dtype: torch.dtyp
     group must get here together, which they do when they run the same training step).  ``None``
     when symmetric memory cannot be set up on this machine (agreed on by all ranks)."""
     key = (id(group) if group is not None else 0, device.index, F, D, dtype,
-           nv.get_option("lanes_bwd"), nv.get_option("l2_budget_mb"), config.use_multicast)
+           nv.get_option("lanes_bwd"), nv.get_option("l2_budget_mb"), config.use_multicast,
+           config.symmetric_dweight)
     if key not in _exchanges:
         ex, problem = None, None
         try:

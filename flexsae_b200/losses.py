@@ -156,7 +156,11 @@ def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype
         if need == 0:
             raise nv.FlexSaeNativeError("flexsae_loss_bwd: " + lib.flexsae_last_error().decode())
         ws = _workspace(dev, need)
-        dweight = torch.empty((F, D), dtype=weight.dtype, device=dev)
+        dw_ptrs = None
+        if peers is not None and getattr(peers, "dweight", None) is not None:
+            dweight, dw_ptrs = peers.take_dweight()      # every rank's table is peer-mapped: reduced rows land in place
+        else:
+            dweight = torch.empty((F, D), dtype=weight.dtype, device=dev)
         dvals = torch.empty((B, K), dtype=vals.dtype, device=dev)
         dbias = torch.empty((D,), dtype=bias_dtype, device=dev)
         stream = torch.cuda.current_stream(dev).cuda_stream
@@ -166,7 +170,7 @@ def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype
                                               B, K, F, D, wdt, nv.DTYPE_CODES[vals.dtype], nv.DTYPE_CODES[bias_dtype],
                                               float(inv_norm), _ptr(_status_word(dev)), stream, peers.world,
                                               peers.rank, peers.next_seq(), peers.x, peers.y, peers.flags,
-                                              peers.mc_x, peers.mc_y)
+                                              peers.mc_x, peers.mc_y, dw_ptrs)
         else:
             rc = lib.flexsae_loss_bwd(kind, _ptr(indices), _ptr(weight), _ptr(vals), _ptr(state), segments, _ptr(go),
                                       _ptr(dweight), _ptr(dvals), _ptr(dbias), _ptr(ws), ws.numel(), B, K, F, D, wdt,

@@ -62,7 +62,11 @@ const char* flexsae_last_error(void);
  * "l2_budget_mb" (working set one column piece may occupy), "segments"
  * (what flexsae_choose_segments answers; 0 = derive from the shape), "pipeline" (1: the atomic
  * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct",
- * "direct_f32" (1: with an fp32 decoder the reductions go straight into dweight).
+ * "direct_f32" (1: with an fp32 decoder the reductions go straight into dweight),
+ * "exchange_blocks" and "exchange_offset_pct" (sharded backward: how many blocks per column piece
+ * do the cross-GPU exchange and how far into the piece's blocks they are placed), "scatter_rotate"
+ * (1: each rank starts its scatter at a different owner's rows), "flag_fan_out" (1: a finished
+ * slot is announced to all ranks by parallel stores).
  * Stands in for the literal tile constants at the reference's launch sites
  * (torch-ext/flex_sae/hierarchical_kernels.py:220-224,263-267; topk_kernels.py:64-66,181-183).
  * Returns 0, or FLEXSAE_EINVAL for an unknown name or value. */
@@ -138,11 +142,19 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
  *   x_ptrs / y_ptrs / flag_ptrs   host arrays of `world` DEVICE pointers, entry r = rank r's
  *       inbox, gather buffer and flag array, each mapped into this process (CUDA IPC / symmetric
  *       memory), of the sizes flexsae_shard_buffer_bytes answers; peers only STORE into them;
- *       the flag buffers must be zero before the first call
+ *       the flag buffers (two words per rank: one for its scatters, one for its exchanges) must be
+ *       zero before the first call
  *   multicast_x / multicast_y   optional: the multicast (NVLink SHARP) addresses that map onto
  *       all ranks' x / y buffers; when given, the reduction is done by the switch
  *       (multimem.ld_reduce) and the reduced rows are broadcast with multimem.st; NULL, NULL =
  *       plain peer stores
+ *   dweight_ptrs   optional: host array of `world` device pointers, entry r = rank r's `dweight`
+ *       argument of this same call, mapped into this process (so dweight itself lives in symmetric
+ *       / IPC memory; dweight_ptrs[rank] == dweight).  The reduced rows are then stored straight
+ *       into every rank's dweight and the gather buffer and its copy pass are skipped.  A peer may
+ *       start writing into this rank's dweight as soon as this rank has started the call, so
+ *       whatever read the previous contents must precede the call in stream order.  Not with the
+ *       multicast path.  NULL = through the gather buffer
  *   seq_base   first call: 1; every later call on the same buffers: previous seq_base +
  *       flexsae_shard_slots(F, D, weight_dtype); identical on all ranks
  * Only FLEXSAE_DW_ATOMIC accumulation.  All ranks must issue the same sequence of calls.  Waits on
@@ -159,7 +171,7 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
                              int vals_dtype, int bias_dtype, double inv_norm, int32_t* status,
                              void* stream, int world, int rank, int seq_base, void* const* x_ptrs,
                              void* const* y_ptrs, void* const* flag_ptrs, void* multicast_x,
-                             void* multicast_y);
+                             void* multicast_y, void* const* dweight_ptrs);
 
 /*
  * flexsae_loss_fwd for callers that must not allocate device memory.  It has no counterpart in

@@ -101,13 +101,16 @@ def test_sharded_entry_rejects_bad_arguments_without_a_gpu():
     lib = nv.load()
     three = (ctypes.c_void_p * 3)(16, 32, 48)
     base = [nv.HIER] + [None] * 4 + [1] + [None] * 5 + [0, 4, 4, 16, 256, nv.F32, nv.F32, nv.F32, 0.0, None, None]
-    assert lib.flexsae_loss_bwd_sharded(*base, 1, 0, 1, three, three, three, None, None) == -1      # world < 2
+    assert lib.flexsae_loss_bwd_sharded(*base, 1, 0, 1, three, three, three, None, None, None) == -1      # world < 2
     assert b"world size" in lib.flexsae_last_error()
-    assert lib.flexsae_loss_bwd_sharded(*base, 9, 0, 1, three, three, three, None, None) == -1      # world > 8
-    assert lib.flexsae_loss_bwd_sharded(*base, 3, 3, 1, three, three, three, None, None) == -1      # rank out of range
-    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 0, three, three, three, None, None) == -1      # seq_base < 1
-    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 1, None, three, three, None, None) == -1       # missing buffers
-    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 1, three, three, three, 64, None) == -1        # one multicast address only
+    assert lib.flexsae_loss_bwd_sharded(*base, 9, 0, 1, three, three, three, None, None, None) == -1      # world > 8
+    assert lib.flexsae_loss_bwd_sharded(*base, 3, 3, 1, three, three, three, None, None, None) == -1      # rank out of range
+    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 0, three, three, three, None, None, None) == -1      # seq_base < 1
+    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 1, None, three, three, None, None, None) == -1       # missing buffers
+    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 1, three, three, three, 64, None, None) == -1        # one multicast address only
+    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 1, three, three, three, 64, 64, three) == -1    # in place + multicast
+    assert lib.flexsae_loss_bwd_sharded(*base, 3, 0, 1, three, three, three, None, None, three) == -1  # [rank] is not dweight
+    assert b"dweight_ptrs[rank]" in lib.flexsae_last_error()
     x, y, f = ctypes.c_size_t(), ctypes.c_size_t(), ctypes.c_size_t()
     nv.set_option("lanes_bwd", 16)
     assert lib.flexsae_shard_buffer_bytes(65536, 2304, nv.BF16, 8, ctypes.byref(x), ctypes.byref(y), ctypes.byref(f)) == 0

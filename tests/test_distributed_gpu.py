@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, kind, q, peer_reduce=True, multicast=True):
+def _worker(rank, world, port, kind, q, mode):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -20,8 +20,12 @@ def _worker(rank, world, port, kind, q, peer_reduce=True, multicast=True):
         import flexsae_b200 as fx
         from flexsae_b200 import distributed as fd
         from flexsae_b200.workloads import CONFIGS, make_inputs
-        fd.config.peer_reduce = peer_reduce
-        fd.config.use_multicast = multicast
+        fd.config.peer_reduce = mode != "nccl"
+        fd.config.use_multicast = mode == "multicast"
+        fd.config.symmetric_dweight = mode == "inplace"
+        if mode == "inplace":       # together with the other non-default exchange settings
+            for name, value in (("exchange_offset_pct", 25), ("scatter_rotate", 1), ("flag_fan_out", 1)):
+                fx._native.set_option(name, value)
         w = CONFIGS["c3_k32"].replace(B=768, F=8190)       # F not a multiple of the world size
         rows = w.B // world
         x = make_inputs(w, f"cuda:{rank}", row0=rank * rows, rows=rows)
@@ -35,7 +39,13 @@ def _worker(rank, world, port, kind, q, peer_reduce=True, multicast=True):
             loss.backward(x["grad_out"])
         torch.cuda.synchronize()
         fx.check_status()
-        q.put((rank, float(loss), weight.grad.float().cpu(), vals.grad.float().cpu(), bias.grad.float().cpu()))
+        out = (rank, float(loss), weight.grad.float().cpu(), vals.grad.float().cpu(), bias.grad.float().cpu())
+        if mode == "inplace":       # the gradient is a view of the persistent table: a backward that would
+            loss = fn(x["indices"], weight, vals, bias, x["target"])   # overwrite it while it is held must refuse
+            with pytest.raises(RuntimeError, match="still referenced"):
+                loss.backward(x["grad_out"])
+            torch.cuda.synchronize()
+        q.put(out)
     finally:
         dist.destroy_process_group()
 
@@ -46,7 +56,7 @@ def _worlds():
 
 
 @pytest.mark.parametrize("world", _worlds())
-@pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "nccl"])
+@pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "inplace", "nccl"])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
 def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     if torch.cuda.device_count() < world:
@@ -60,9 +70,8 @@ def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
-    port += {"multicast": 13, "stores": 5, "nccl": 0}[peer_reduce] + 29 * world
-    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce != "nccl", peer_reduce == "multicast"))
-             for r in range(world)]
+    port += {"multicast": 13, "stores": 5, "inplace": 17, "nccl": 0}[peer_reduce] + 29 * world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce)) for r in range(world)]
     for p in procs:
         p.start()
     outs = sorted([q.get(timeout=300) for _ in procs], key=lambda o: o[0])
