@@ -2,7 +2,9 @@
 
 nvcc cross-compiles without a GPU, so this runs on a CPU-only machine; the shared object then
 travels with the source tree.  ``python -m flexsae_b200.build`` rebuilds when a source is newer
-than the library; ``--force`` always rebuilds; ``--verbose`` prints ptxas resource usage.
+than the library; ``--force`` always rebuilds; ``--verbose`` prints ptxas resource usage;
+``--trace`` builds the tuning variant ``libflexsae_b200_trace.so`` (compiled with
+``-DFLEXSAE_TRACE``: the sharded backward records a per-slot timeline, see ``slot_timeline.py``).
 """
 from __future__ import annotations
 
@@ -16,6 +18,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "_lib")
 LIB_PATH = os.path.join(LIB_DIR, "libflexsae_b200.so")
+TRACE_LIB_PATH = os.path.join(LIB_DIR, "libflexsae_b200_trace.so")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 
 NVCC_FLAGS = [
@@ -29,31 +32,34 @@ def _sources():
     return sorted(glob.glob(os.path.join(CSRC, "*.cu")))
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
+def _stale(lib_path: str = LIB_PATH) -> bool:
+    if not os.path.exists(lib_path):
         return True
-    t = os.path.getmtime(LIB_PATH)
+    t = os.path.getmtime(lib_path)
     deps = _sources() + glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(INCLUDE, "*.h"))
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, trace: bool = False) -> str:
     """Compiles every ``csrc/*.cu`` into one shared library and returns its path."""
-    if not force and not _stale():
-        return LIB_PATH
+    out = TRACE_LIB_PATH if trace else LIB_PATH
+    if not force and not _stale(out):
+        return out
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
         raise RuntimeError("nvcc not found: the CUDA library cannot be built on this machine")
     os.makedirs(LIB_DIR, exist_ok=True)
     extra = os.environ.get("FLEXSAE_NVCC_EXTRA", "--use_fast_math").split()   # e.g. "-DFLEXSAE_BWD_MINB=8" while tuning
-    cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-I", INCLUDE, "-o", LIB_PATH] + _sources()
+    if trace:
+        extra = extra + ["-DFLEXSAE_TRACE"]
+    cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-I", INCLUDE, "-o", out] + _sources()
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout[-4000:])
-    return LIB_PATH
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, trace="--trace" in sys.argv))
