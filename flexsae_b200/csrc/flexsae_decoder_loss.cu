@@ -66,6 +66,7 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 #include "flexsae_forward.cuh"
 #include "flexsae_backward.cuh"
 #include "flexsae_sharded.cuh"
+#include "flexsae_small_allreduce.cuh"
 
 namespace flexsae {
 
@@ -673,6 +674,45 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
   return loss_bwd_impl(kind, indices, weight, vals, state, segments, grad_out, dweight, dvals, dbias, workspace,
                        workspace_bytes, B, K, F, D, weight_dtype, vals_dtype, bias_dtype, inv_norm, FLEXSAE_DW_ATOMIC,
                        status, stream, &peers);
+}
+
+int flexsae_small_allreduce_bytes(int world, int64_t capacity, size_t* bytes) {
+  if (world < 2 || world > kMaxRanks) return fail(FLEXSAE_EINVAL, "world size %d outside [2, %d]", world, kMaxRanks);
+  if (capacity < 1 || capacity > (1 << 24) || !bytes) return fail(FLEXSAE_EINVAL, "capacity %lld outside [1, 2^24] or null pointer", (long long)capacity);
+  *bytes = align_up(kSmallFlagBytes + 2 * (size_t)world * (size_t)capacity * sizeof(float), 256);
+  return 0;
+}
+
+int flexsae_small_allreduce(const void* in, void* out, int64_t n, int dtype, int world, int rank, int seq,
+                            void* const* buf_ptrs, int64_t capacity, int32_t* status, void* stream) {
+  t_launches = 0;
+  if (world < 2 || world > kMaxRanks) return fail(FLEXSAE_EINVAL, "world size %d outside [2, %d]", world, kMaxRanks);
+  if (rank < 0 || rank >= world) return fail(FLEXSAE_EINVAL, "rank %d outside [0, %d)", rank, world);
+  if (!in || !out || !buf_ptrs) return fail(FLEXSAE_EINVAL, "null pointer argument");
+  if (!dtype_ok(dtype)) return fail(FLEXSAE_EINVAL, "unknown dtype code %d", dtype);
+  if (capacity < 1 || capacity > (1 << 24)) return fail(FLEXSAE_EINVAL, "capacity %lld outside [1, 2^24]", (long long)capacity);
+  if (n < 1 || n > capacity) return fail(FLEXSAE_EINVAL, "n = %lld outside [1, capacity = %lld]", (long long)n, (long long)capacity);
+  if (seq < 1) return fail(FLEXSAE_EINVAL, "seq must be >= 1");
+  SmallReduceArgs a;
+  a.in = in;
+  a.out = out;
+  a.n = (int)n;
+  a.dtype = dtype;
+  a.world = world;
+  a.rank = rank;
+  a.seq = seq;
+  a.capacity = capacity;
+  a.status = status;
+  for (int r = 0; r < kMaxRanks; r++) {
+    a.buf[r] = r < world ? buf_ptrs[r] : nullptr;
+    if (r < world && (!a.buf[r] || !aligned16(a.buf[r])))
+      return fail(FLEXSAE_EINVAL, "exchange buffer of rank %d is null or not 16-byte aligned", r);
+  }
+  small_allreduce_kernel<<<1, kSmallThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  t_launches++;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail((int)e, "small all-reduce launch failed: %s", cudaGetErrorString(e));
+  return 0;
 }
 
 #ifdef FLEXSAE_TRACE

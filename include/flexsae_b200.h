@@ -174,6 +174,24 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
                              void* multicast_y, void* const* dweight_ptrs);
 
 /*
+ * Sum of `n` values (n <= capacity) over the 2..8 GPUs of one node through peer memory, in ONE
+ * single-block launch: what the batch-sharded losses use for the scalar loss and for dbias instead
+ * of a library all-reduce, whose latency dominates at these sizes.  The reference has no
+ * counterpart (it is single-GPU).  Values travel and are added as fp32, in rank order, so every
+ * rank receives identical bits; `in` and `out` hold `dtype` elements and may be the same memory.
+ *   buf_ptrs   host array of `world` device pointers, entry r = rank r's exchange buffer of
+ *       flexsae_small_allreduce_bytes(world, capacity) bytes, mapped into this process, zero before
+ *       the first call; peers only store into it
+ *   seq        1 on the first call on these buffers, then +1 per call; identical on all ranks, which
+ *       must issue the same sequence of calls (each rank: in stream order)
+ * The wait for the other ranks is bounded; if it gives up, FLEXSAE_STATUS_PIPELINE_TIMEOUT is set in
+ * `status` and `out` is invalid.
+ */
+int flexsae_small_allreduce_bytes(int world, int64_t capacity, size_t* bytes);
+int flexsae_small_allreduce(const void* in, void* out, int64_t n, int dtype, int world, int rank, int seq,
+                            void* const* buf_ptrs, int64_t capacity, int32_t* status, void* stream);
+
+/*
  * flexsae_loss_fwd for callers that must not allocate device memory.  It has no counterpart in
  * the reference (whose launchers allocate with torch on every call).
  *

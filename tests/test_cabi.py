@@ -117,3 +117,28 @@ def test_sharded_entry_rejects_bad_arguments_without_a_gpu():
     nv.set_option("lanes_bwd", 0)
     assert x.value == 2 * 65536 * 128 * 2 and y.value == x.value and f.value >= 8 * 4
     assert lib.flexsae_shard_slots(65536, 2304, nv.BF16) == 18 + 3
+
+
+def test_small_allreduce_rejects_bad_arguments_without_a_gpu():
+    lib = nv.load()
+    two = (ctypes.c_void_p * 2)(256, 512)
+    n = ctypes.c_size_t()
+    assert lib.flexsae_small_allreduce_bytes(8, 16384, ctypes.byref(n)) == 0
+    assert n.value == 256 + 2 * 8 * 16384 * 4
+    assert lib.flexsae_small_allreduce_bytes(1, 16, ctypes.byref(n)) == -1
+    assert lib.flexsae_small_allreduce_bytes(2, 0, ctypes.byref(n)) == -1
+    ok = dict(n=4, dtype=nv.F32, world=2, rank=0, seq=1, cap=16)
+
+    def call(**kw):
+        a = {**ok, **kw}
+        return lib.flexsae_small_allreduce(kw.get("src", 64), 64, a["n"], a["dtype"], a["world"], a["rank"], a["seq"],
+                                           kw.get("bufs", two), a["cap"], None, None)
+
+    assert call(world=1) == -1 and b"world size" in lib.flexsae_last_error()
+    assert call(world=9) == -1
+    assert call(rank=2) == -1
+    assert call(n=0) == -1 and call(n=17) == -1 and b"capacity" in lib.flexsae_last_error()
+    assert call(dtype=7) == -1
+    assert call(seq=0) == -1
+    assert call(src=None) == -1 and call(bufs=None) == -1
+    assert call(bufs=(ctypes.c_void_p * 2)(256, 0)) == -1 and b"rank 1" in lib.flexsae_last_error()

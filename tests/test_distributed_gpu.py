@@ -23,6 +23,7 @@ def _worker(rank, world, port, kind, q, mode):
         fd.config.peer_reduce = mode != "nccl"
         fd.config.use_multicast = mode == "multicast"
         fd.config.symmetric_dweight = mode == "inplace"
+        fd.config.fused_small_reduce = mode == "inplace"
         if mode == "inplace":       # together with the other non-default exchange settings
             for name, value in (("exchange_offset_pct", 25), ("scatter_rotate", 1), ("flag_fan_out", 1)):
                 fx._native.set_option(name, value)
@@ -93,3 +94,56 @@ def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
         assert rel_err(dW.numpy(), weight.grad.float().cpu().numpy()) < 1e-2      # bf16 sum of bf16 shards
         assert rel_err(db.numpy(), bias.grad.float().cpu().numpy()) < 1e-2
         assert torch.equal(dv, vals.grad.float().cpu()[rank * rows:(rank + 1) * rows])
+
+
+def _small_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import flexsae_b200 as fx
+        from flexsae_b200 import distributed as fd
+        ex = fd.small_exchange(None, torch.device("cuda", rank))
+        assert ex is not None
+        worst = 0.0
+        same = True
+        for step, (n, dtype) in enumerate([(1, torch.float32), (7, torch.float32), (2304, torch.bfloat16), (16384, torch.float32),
+                                           (1, torch.float32), (2305, torch.float16), (33, torch.float32)] * 3):
+            g = torch.Generator(device="cpu").manual_seed(1000 * step + rank)
+            t = torch.randn(n, generator=g).to(device=f"cuda:{rank}", dtype=dtype)
+            want = t.float().clone()
+            dist.all_reduce(want)
+            got = ex.all_reduce_(t.clone()).float()
+            tol = 1e-6 if dtype == torch.float32 else 1e-2
+            worst = max(worst, float(((got - want).abs() / (want.abs() + 1.0)).max()) / tol)
+            every = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(every, got)
+            same = same and all(torch.equal(every[0], e) for e in every)      # identical bits on every rank
+        torch.cuda.synchronize()
+        fx.check_status()
+        q.put((rank, worst, same))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", _worlds())
+def test_small_allreduce_matches_nccl(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 100 + 3 * world
+    procs = [ctx.Process(target=_small_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, worst, same in outs:
+        assert worst <= 1.0, (rank, worst)
+        assert same
