@@ -41,6 +41,8 @@ struct Options {
   int exchange_blocks = 148;    // sharded backward: blocks per slot for the cross-GPU reduce / broadcast / copy
   int exchange_offset_pct = 0;  // ... and where inside a piece's unit blocks they sit (capped at convert_offset_pct)
   int scatter_rotate = 0;       // sharded backward: ranks start their scatter sweeps at different row blocks
+  int sharded_convert_blocks = 0;       // sharded backward: converting blocks per piece (0 = as on one GPU)
+  int sharded_convert_offset_pct = -1;  // sharded backward: their place in the piece (-1 = convert_offset_pct)
   int flag_fan_out = 0;         // sharded backward: a finished slot is announced by one thread per rank
   int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
 };
@@ -319,9 +321,11 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
   const long long items = (long long)b.F * G;
   int conv = (int)((items + kThreads * 4 - 1) / (kThreads * 4));
-  if (conv > kConvertBlocks) conv = kConvertBlocks;
+  const int conv_cap = g_opt.sharded_convert_blocks > 0 ? g_opt.sharded_convert_blocks : kConvertBlocks;
+  if (conv > conv_cap) conv = conv_cap;
   pa.conv_blocks = conv;
-  pa.conv_offset = (int)((long long)pa.unit_blocks * g_opt.convert_offset_pct / 100);
+  const int conv_pct = g_opt.sharded_convert_offset_pct >= 0 ? g_opt.sharded_convert_offset_pct : g_opt.convert_offset_pct;
+  pa.conv_offset = (int)((long long)pa.unit_blocks * conv_pct / 100);
   sa.exch_blocks = g_opt.exchange_blocks;
   sa.exch_offset = (int)((long long)pa.unit_blocks * g_opt.exchange_offset_pct / 100);
   if (sa.exch_offset > pa.conv_offset) sa.exch_offset = pa.conv_offset;
@@ -372,6 +376,8 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "exchange_offset_pct") && value >= 0 && value <= 100) { g_opt.exchange_offset_pct = (int)value; return 0; }
   if (!strcmp(name, "scatter_rotate") && (value == 0 || value == 1)) { g_opt.scatter_rotate = (int)value; return 0; }
   if (!strcmp(name, "flag_fan_out") && (value == 0 || value == 1)) { g_opt.flag_fan_out = (int)value; return 0; }
+  if (!strcmp(name, "sharded_convert_blocks") && value >= 0 && value <= 8192) { g_opt.sharded_convert_blocks = (int)value; return 0; }
+  if (!strcmp(name, "sharded_convert_offset_pct") && value >= -1 && value <= 100) { g_opt.sharded_convert_offset_pct = (int)value; return 0; }
   return fail(FLEXSAE_EINVAL, "unknown option or value: %s=%lld", name, (long long)value);
 }
 
@@ -388,6 +394,8 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "exchange_offset_pct")) return g_opt.exchange_offset_pct;
   if (!strcmp(name, "scatter_rotate")) return g_opt.scatter_rotate;
   if (!strcmp(name, "flag_fan_out")) return g_opt.flag_fan_out;
+  if (!strcmp(name, "sharded_convert_blocks")) return g_opt.sharded_convert_blocks;
+  if (!strcmp(name, "sharded_convert_offset_pct")) return g_opt.sharded_convert_offset_pct;
   return -1;
 }
 

@@ -66,7 +66,9 @@ const char* flexsae_last_error(void);
  * "exchange_blocks" and "exchange_offset_pct" (sharded backward: how many blocks per column piece
  * do the cross-GPU exchange and how far into the piece's blocks they are placed), "scatter_rotate"
  * (1: each rank starts its scatter at a different owner's rows), "flag_fan_out" (1: a finished
- * slot is announced to all ranks by parallel stores).
+ * slot is announced to all ranks by parallel stores), "sharded_convert_blocks" and
+ * "sharded_convert_offset_pct" (sharded backward: number and placement of the converting blocks
+ * when they differ from the single-GPU kernel's; 0 / -1 = the same).
  * Stands in for the literal tile constants at the reference's launch sites
  * (torch-ext/flex_sae/hierarchical_kernels.py:220-224,263-267; topk_kernels.py:64-66,181-183).
  * Returns 0, or FLEXSAE_EINVAL for an unknown name or value. */
