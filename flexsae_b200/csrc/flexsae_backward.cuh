@@ -359,6 +359,76 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
   signal_done(pa.walk_done + p);
 }
 
+// ---- single-launch backward with a shared conversion queue --------------------------------------
+// Same pipeline, but no block is a converter by position.  The slab of a finished piece is cut into
+// `chunks` chunks behind a claim counter, and whoever is running takes them:
+//   a unit block that has finished its walk of piece p takes up to `exit_chunks` chunks of piece
+//     p-1 if that piece's walk is complete (it never waits for it);
+//   a unit block of piece p that finds piece p-2 (same slab) not fully converted yet takes chunks of
+//     it until none is left, then waits for the ones still in other blocks' hands;
+//   `tail` blocks after the last piece take whatever is left of the last two pieces.
+// So a conversion starts the moment its piece's last unit block finishes, at the rate at which
+// blocks retire, instead of when converter blocks placed at a fixed position become resident.
+// Every chunk that is waited for has been claimed by a running block that finishes it without
+// waiting, and a piece's walk depends only on lower block indices: no wait can be circular.
+struct StealArgs {
+  PipeArgs p;       // conv_blocks / conv_offset unused; conv_done counts finished chunks
+  int* claim;       // [pieces] next chunk of each piece's slab to hand out
+  int chunks;       // chunks per slab
+  int exit_chunks;  // chunks a unit block takes after its walk
+};
+
+template <typename T, int G>
+__device__ __forceinline__ void take_chunks(const StealArgs& sa, int q, int limit, int* s_chunk) {
+  const PipeArgs& pa = sa.p;
+  for (int n = 0; n < limit; n++) {
+    if (threadIdx.x == 0) *s_chunk = atomicAdd(sa.claim + q, 1);
+    __syncthreads();
+    const int c = *s_chunk;
+    __syncthreads();  // everyone has read the chunk number before thread 0 may overwrite it
+    if (c >= sa.chunks) break;
+    convert_slab<T, G, true>(pa.slabs[q & 1], pa.b.dweight, pa.b.F, pa.b.D, q, c, sa.chunks);
+    signal_done(pa.conv_done + q);
+  }
+}
+
+template <typename T, int G, bool HIER>
+__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_stealing_kernel(const StealArgs sa) {
+  extern __shared__ uint4 smem[];
+  __shared__ int s_chunk, s_state;
+  const PipeArgs& pa = sa.p;
+  const int p = blockIdx.x / pa.unit_blocks;
+  if (p >= pa.pieces) {  // tail: the last two pieces have no later unit blocks to convert them
+    for (int q = max(0, pa.pieces - 2); q < pa.pieces; q++) {
+      wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status);
+      take_chunks<T, G>(sa, q, 0x7fffffff, &s_chunk);
+    }
+    return;
+  }
+  const int unit_block = blockIdx.x - p * pa.unit_blocks;
+  if (p >= 2) {
+    if (threadIdx.x == 0) s_state = ld_acquire(pa.conv_done + (p - 2)) >= sa.chunks;
+    __syncthreads();
+    const bool converted = s_state != 0;
+    __syncthreads();
+    if (!converted) {  // this block's slab still holds piece p-2: help, then wait for the chunks in other hands
+      wait_count(pa.walk_done + (p - 2), pa.unit_blocks, pa.b.status);
+      take_chunks<T, G>(sa, p - 2, 0x7fffffff, &s_chunk);
+      wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status);
+    }
+  }
+  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
+  signal_done(pa.walk_done + p);
+  if (p >= 1 && sa.exit_chunks > 0) {
+    if (threadIdx.x == 0)
+      s_state = ld_acquire(pa.walk_done + (p - 1)) >= pa.unit_blocks && ld_acquire(sa.claim + (p - 1)) < sa.chunks;
+    __syncthreads();
+    const bool open = s_state != 0;
+    __syncthreads();
+    if (open) take_chunks<T, G>(sa, p - 1, sa.exit_chunks, &s_chunk);
+  }
+}
+
 // Column sums of a [B, D] fp32 matrix over row blocks: part[rb][d] = sum of rows of block rb.
 // dbias is coef * (column sums of the final residual (TopK) / of the summed prefix residuals).
 __global__ void __launch_bounds__(128) column_sums_kernel(const float* __restrict__ x, int B, int D, int rows_per_block,

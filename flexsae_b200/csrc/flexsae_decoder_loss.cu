@@ -45,6 +45,9 @@ struct Options {
   int sharded_convert_offset_pct = -1;  // sharded backward: their place in the piece (-1 = convert_offset_pct)
   int flag_fan_out = 0;         // sharded backward: a finished slot is announced by one thread per rank
   int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
+  int convert_steal = 0;        // single-launch backward: slab conversion taken in chunks by whichever blocks run
+  int steal_chunks = 1024;      // ... chunks per slab
+  int steal_exit_chunks = 1;    // ... chunks a unit block takes after its walk
 };
 static Options g_opt;
 
@@ -302,6 +305,38 @@ static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* s
 }
 
 template <typename T, int G, bool HIER>
+static cudaError_t launch_bwd_stealing(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
+                                       cudaStream_t st) {
+  constexpr int UPC = groups_per_cta(G);
+  const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
+  auto kern = decoder_loss_bwd_stealing_kernel<T, G, HIER>;
+  if (cudaError_t e = allow_smem(kern, smem)) return e;
+  StealArgs sa;
+  PipeArgs& pa = sa.p;
+  pa.b = b;
+  pa.slabs[0] = slab0;
+  pa.slabs[1] = slab1;
+  pa.walk_done = counters;
+  pa.conv_done = counters + pieces;
+  sa.claim = counters + 2 * pieces + 3;
+  pa.pieces = pieces;
+  const long long units = (long long)b.B * b.NS;
+  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
+  pa.conv_blocks = pa.conv_offset = 0;
+  const long long items = (long long)b.F * G;
+  long long chunks = (items + kThreads * 4 - 1) / (kThreads * 4);
+  if (chunks > g_opt.steal_chunks) chunks = g_opt.steal_chunks;
+  sa.chunks = (int)chunks;
+  sa.exit_chunks = g_opt.steal_exit_chunks;
+  const int tail = sa.chunks < kConvertBlocks ? sa.chunks : kConvertBlocks;
+  const long long blocks = (long long)pieces * pa.unit_blocks + tail;
+  if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
+  t_launches++;
+  return cudaGetLastError();
+}
+
+template <typename T, int G, bool HIER>
 static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
                                       ShardArgs sa, cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
@@ -370,6 +405,9 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "l2_budget_mb") && value >= 1 && value <= 4096) { g_opt.l2_budget_mb = (int)value; return 0; }
   if (!strcmp(name, "segments") && value >= 0 && value <= 256) { g_opt.segments = (int)value; return 0; }
   if (!strcmp(name, "pipeline") && (value == 0 || value == 1)) { g_opt.pipeline = (int)value; return 0; }
+  if (!strcmp(name, "convert_steal") && (value == 0 || value == 1)) { g_opt.convert_steal = (int)value; return 0; }
+  if (!strcmp(name, "steal_chunks") && value >= 1 && value <= 65536) { g_opt.steal_chunks = (int)value; return 0; }
+  if (!strcmp(name, "steal_exit_chunks") && value >= 0 && value <= 64) { g_opt.steal_exit_chunks = (int)value; return 0; }
   if (!strcmp(name, "convert_offset_pct") && value >= 0 && value <= 100) { g_opt.convert_offset_pct = (int)value; return 0; }
   if (!strcmp(name, "direct_f32") && (value == 0 || value == 1)) { g_opt.direct_f32 = (int)value; return 0; }
   if (!strcmp(name, "exchange_blocks") && value >= 1 && value <= 4096) { g_opt.exchange_blocks = (int)value; return 0; }
@@ -388,6 +426,9 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "l2_budget_mb")) return g_opt.l2_budget_mb;
   if (!strcmp(name, "segments")) return g_opt.segments;
   if (!strcmp(name, "pipeline")) return g_opt.pipeline;
+  if (!strcmp(name, "convert_steal")) return g_opt.convert_steal;
+  if (!strcmp(name, "steal_chunks")) return g_opt.steal_chunks;
+  if (!strcmp(name, "steal_exit_chunks")) return g_opt.steal_exit_chunks;
   if (!strcmp(name, "convert_offset_pct")) return g_opt.convert_offset_pct;
   if (!strcmp(name, "direct_f32")) return g_opt.direct_f32;
   if (!strcmp(name, "exchange_blocks")) return g_opt.exchange_blocks;
@@ -593,7 +634,10 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     a.unit_blocks = a.conv_blocks = 0;
     a.conv_stride = 1;
 #define CALL_PIPE(T, G, H) launch_bwd_pipelined<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, direct, st)
-    e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_PIPE);
+#define CALL_STEAL(T, G, H) launch_bwd_stealing<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, st)
+    if (g_opt.convert_steal && !direct) e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_STEAL);
+    else e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_PIPE);
+#undef CALL_STEAL
 #undef CALL_PIPE
     if (e != cudaSuccess) return fail((int)e, "pipelined backward launch failed: %s", cudaGetErrorString(e));
   } else

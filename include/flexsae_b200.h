@@ -63,6 +63,9 @@ const char* flexsae_last_error(void);
  * (what flexsae_choose_segments answers; 0 = derive from the shape), "pipeline" (1: the atomic
  * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct",
  * "direct_f32" (1: with an fp32 decoder the reductions go straight into dweight),
+ * "convert_steal" (1: in the single-launch backward the slab conversion is not done by blocks at a
+ * fixed position but taken in "steal_chunks" chunks by whichever blocks are running, each unit
+ * block taking "steal_exit_chunks" after its walk),
  * "exchange_blocks" and "exchange_offset_pct" (sharded backward: how many blocks per column piece
  * do the cross-GPU exchange and how far into the piece's blocks they are placed), "scatter_rotate"
  * (1: each rank starts its scatter at a different owner's rows), "flag_fan_out" (1: a finished

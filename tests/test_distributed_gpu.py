@@ -6,6 +6,8 @@ import sys
 import pytest
 import torch
 
+from tests.helpers import unverified_on_gpu
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
@@ -22,9 +24,9 @@ def _worker(rank, world, port, kind, q, mode):
         from flexsae_b200.workloads import CONFIGS, make_inputs
         fd.config.peer_reduce = mode != "nccl"
         fd.config.use_multicast = mode == "multicast"
-        fd.config.symmetric_dweight = mode == "inplace"
-        fd.config.fused_small_reduce = mode == "inplace"
-        if mode == "inplace":       # together with the other non-default exchange settings
+        fd.config.symmetric_dweight = mode in ("inplace", "inplace_small")
+        fd.config.fused_small_reduce = mode == "inplace_small"
+        if mode in ("inplace", "inplace_small"):       # together with the other non-default exchange settings
             for name, value in (("exchange_offset_pct", 25), ("scatter_rotate", 1), ("flag_fan_out", 1)):
                 fx._native.set_option(name, value)
         w = CONFIGS["c3_k32"].replace(B=768, F=8190)       # F not a multiple of the world size
@@ -41,7 +43,7 @@ def _worker(rank, world, port, kind, q, mode):
         torch.cuda.synchronize()
         fx.check_status()
         out = (rank, float(loss), weight.grad.float().cpu(), vals.grad.float().cpu(), bias.grad.float().cpu())
-        if mode == "inplace":       # the gradient is a view of the persistent table: a backward that would
+        if mode in ("inplace", "inplace_small"):       # the gradient is a view of the persistent table: a backward that would
             loss = fn(x["indices"], weight, vals, bias, x["target"])   # overwrite it while it is held must refuse
             with pytest.raises(RuntimeError, match="still referenced"):
                 loss.backward(x["grad_out"])
@@ -57,7 +59,8 @@ def _worlds():
 
 
 @pytest.mark.parametrize("world", _worlds())
-@pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "inplace", "nccl"])
+@pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "inplace", "nccl",
+                                         pytest.param("inplace_small", marks=unverified_on_gpu)])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
 def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     if torch.cuda.device_count() < world:
@@ -71,7 +74,7 @@ def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
-    port += {"multicast": 13, "stores": 5, "inplace": 17, "nccl": 0}[peer_reduce] + 29 * world
+    port += {"multicast": 13, "stores": 5, "inplace": 17, "inplace_small": 19, "nccl": 0}[peer_reduce] + 29 * world
     procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce)) for r in range(world)]
     for p in procs:
         p.start()
@@ -128,6 +131,7 @@ def _small_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+@unverified_on_gpu
 @pytest.mark.parametrize("world", _worlds())
 def test_small_allreduce_matches_nccl(world):
     if torch.cuda.device_count() < world:
