@@ -39,6 +39,7 @@ SIGNATURES = {
     "flexsae_shard_slots": (_c_int, [_c_i64, _c_i64, _c_int]),
     "flexsae_loss_bwd_sharded": (_c_int, [_c_int] + [_c_vp] * 4 + [_c_int] + [_c_vp] * 5 + [_c_sz] + [_c_i64] * 4
                                  + [_c_int] * 3 + [_c_dbl, _c_vp, _c_vp] + [_c_int] * 3 + [_c_vp] * 6),
+    "flexsae_topk_select": (_c_int, [_c_vp, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_vp, _c_int, _c_vp, _c_vp]),
     "flexsae_small_allreduce_bytes": (_c_int, [_c_int, _c_i64, _c_vp]),
     "flexsae_small_allreduce": (_c_int, [_c_vp, _c_vp, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_i64, _c_vp, _c_vp]),
     "flexsae_loss_fwd_static_scratch": (_c_int, [_c_int] + [_c_vp] * 7 + [_c_int] + [_c_i64] * 4 + [_c_int] * 4

@@ -72,6 +72,7 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 #include "flexsae_backward.cuh"
 #include "flexsae_sharded.cuh"
 #include "flexsae_small_allreduce.cuh"
+#include "flexsae_topk_select.cuh"
 
 namespace flexsae {
 
@@ -726,6 +727,62 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
   return loss_bwd_impl(kind, indices, weight, vals, state, segments, grad_out, dweight, dvals, dbias, workspace,
                        workspace_bytes, B, K, F, D, weight_dtype, vals_dtype, bias_dtype, inv_norm, FLEXSAE_DW_ATOMIC,
                        status, stream, &peers);
+}
+
+}  // extern "C"
+
+namespace flexsae {
+template <typename T>
+static cudaError_t launch_topk_select(const SelectArgs& a, int64_t B, cudaStream_t st) {
+  const size_t row_bytes = (size_t)a.F * sizeof(T);
+  const bool cached = row_bytes + kSelFixedSmem <= 200 * 1024;  // leaves room below the 227 KB a CTA may have
+  const size_t smem = kSelFixedSmem + (cached ? row_bytes : 0);
+  cudaError_t e;
+  if (cached) {
+    auto kern = topk_select_kernel<T, true>;
+    if ((e = allow_smem(kern, smem)) != cudaSuccess) return e;
+    kern<<<(unsigned)B, kSelThreads, smem, st>>>(a);
+  } else {
+    auto kern = topk_select_kernel<T, false>;
+    if ((e = allow_smem(kern, smem)) != cudaSuccess) return e;
+    kern<<<(unsigned)B, kSelThreads, smem, st>>>(a);
+  }
+  t_launches++;
+  return cudaGetLastError();
+}
+}  // namespace flexsae
+
+extern "C" {
+
+int flexsae_topk_select(const void* acts, int acts_dtype, int64_t B, int64_t F, int64_t K, int relu, void* vals,
+                        int vals_dtype, int64_t* indices, void* stream) {
+  t_launches = 0;
+  if (!dtype_ok(acts_dtype) || !dtype_ok(vals_dtype))
+    return fail(FLEXSAE_EINVAL, "unknown dtype code (activations %d, vals %d)", acts_dtype, vals_dtype);
+  if (B < 1 || F < 1 || K < 1) return fail(FLEXSAE_EINVAL, "B, F, K must be positive (got %lld %lld %lld)", (long long)B, (long long)F, (long long)K);
+  if (!acts || !vals || !indices) return fail(FLEXSAE_EINVAL, "null pointer argument");
+  if (!aligned16(acts)) return fail(FLEXSAE_EINVAL, "activations must be 16-byte aligned");
+  const int vec = 16 / (int)dtype_size(acts_dtype);
+  if (F % vec != 0) return fail(FLEXSAE_EUNSUPPORTED, "F=%lld must be a multiple of %d (16-byte loads)", (long long)F, vec);
+  if (K > F) return fail(FLEXSAE_EINVAL, "K=%lld exceeds F=%lld", (long long)K, (long long)F);
+  if (K > kSelMaxK) return fail(FLEXSAE_EUNSUPPORTED, "K=%lld above the supported maximum of %d", (long long)K, kSelMaxK);
+  if (F > (1ll << 30) || B > 0x7fffffffll) return fail(FLEXSAE_EUNSUPPORTED, "shape too large for 32-bit index arithmetic");
+  SelectArgs a;
+  a.acts = acts;
+  a.vals = vals;
+  a.indices = indices;
+  a.F = (int)F;
+  a.K = (int)K;
+  a.Kp = 1;
+  while (a.Kp < a.K) a.Kp <<= 1;
+  a.vals_dtype = vals_dtype;
+  a.relu = relu != 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = acts_dtype == FLEXSAE_F32    ? launch_topk_select<float>(a, B, st)
+                  : acts_dtype == FLEXSAE_BF16 ? launch_topk_select<__nv_bfloat16>(a, B, st)
+                                               : launch_topk_select<__half>(a, B, st);
+  if (e != cudaSuccess) return fail((int)e, "top-K selection launch failed: %s", cudaGetErrorString(e));
+  return 0;
 }
 
 int flexsae_small_allreduce_bytes(int world, int64_t capacity, size_t* bytes) {

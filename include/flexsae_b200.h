@@ -179,6 +179,20 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
                              void* multicast_y, void* const* dweight_ptrs);
 
 /*
+ * The step in front of the losses: for each of B rows of encoder activations acts[B,F], the K
+ * largest entries as indices[B,K] (int64 decoder rows) and vals[B,K] in descending order of value
+ * (equal values: lower index first) -- the layout and order the loss entry points take.  The
+ * reference has no counterpart: its losses start from indices and vals (its tests and example draw
+ * them at random, tests/test_all_kernels.py:20-33, example.py:45-51) and a caller is left to run
+ * torch.topk on the encoder output.  One launch,
+ * no scratch memory; the selection is exact and deterministic (radix select + index-ordered
+ * compaction + in-CTA sort).  relu != 0 clamps the reported values at zero.
+ * Needs F a multiple of 8 (16-bit activations) or 4 (fp32), acts 16-byte aligned, K <= min(F, 1024).
+ */
+int flexsae_topk_select(const void* acts, int acts_dtype, int64_t B, int64_t F, int64_t K, int relu,
+                        void* vals, int vals_dtype, int64_t* indices, void* stream);
+
+/*
  * Sum of `n` values (n <= capacity) over the 2..8 GPUs of one node through peer memory, in ONE
  * single-block launch: what the batch-sharded losses use for the scalar loss and for dbias instead
  * of a library all-reduce, whose latency dominates at these sizes.  The reference has no

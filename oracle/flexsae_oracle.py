@@ -110,3 +110,18 @@ def digest(dweight: np.ndarray, n_rows: int = 4) -> Dict[str, np.ndarray]:
         "dweight_rows_idx": touched.astype(np.int64),
         "dweight_rows": dweight[touched].astype(np.float64),
     }
+
+
+def topk_select(acts, k: int, relu: bool = True):
+    """The producer step in front of the losses: per row the ``k`` largest activations, values in
+    descending order, equal values by ascending index (what ``torch.topk(acts, k, sorted=True)``
+    returns up to the order of ties, which torch leaves open).  The reference has no such function
+    (its tests draw indices and vals at random, tests/test_all_kernels.py:20-33), so this one is
+    pinned to torch.topk itself in ``tests/test_producer.py`` rather than to a golden file.
+    Returns ``(indices int64 [B,k], vals float64 [B,k])``."""
+    a = _as64(acts)
+    order = np.argsort(-a, axis=1, kind="stable")[:, :k]
+    vals = np.take_along_axis(a, order, axis=1)
+    if relu:
+        vals = np.maximum(vals, 0.0)
+    return order.astype(np.int64), vals
