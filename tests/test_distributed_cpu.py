@@ -82,3 +82,28 @@ def test_two_rank_shards_match_single_process(kind, rows):
         np.testing.assert_allclose(db, want["dbias"], rtol=1e-5, atol=1e-9)
         np.testing.assert_allclose(dv, want["dvals"][row0:row0 + rows[rank]], rtol=1e-5, atol=1e-9)  # local rows only
         row0 += rows[rank]
+
+
+def test_persistent_gradient_table_is_not_overwritten_while_referenced():
+    """symmetric_dweight hands out views of one persistent table; a backward must refuse to overwrite
+    it while an earlier gradient is still alive (here without any GPU: only the bookkeeping)."""
+    import torch
+
+    from flexsae_b200 import distributed as fd
+
+    ex = object.__new__(fd.PeerExchange)
+    ex.dweight = torch.zeros(4, 8)
+    ex.dweight_ptrs = None
+    ex._dweight_refs = fd._storage_refs(ex.dweight)
+    grad, _ = ex.take_dweight()
+    assert grad.data_ptr() == ex.dweight.data_ptr() and grad.shape == (4, 8)
+    with pytest.raises(RuntimeError, match="still referenced"):
+        ex.take_dweight()
+    holder = torch.nn.Parameter(torch.zeros(4, 8))
+    holder.grad = grad
+    del grad
+    with pytest.raises(RuntimeError, match="still referenced"):      # held as somebody's .grad
+        ex.take_dweight()
+    holder.grad = None
+    again, _ = ex.take_dweight()
+    assert again.data_ptr() == ex.dweight.data_ptr()
