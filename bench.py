@@ -7,8 +7,10 @@
 A step is one forward + backward of the loss over one batch of seeded synthetic inputs
 (flexsae_b200.workloads).  At N = 1 the workload is the headline set-up
 F=65536, D=2304, K=128, B=4096, bf16 decoder / fp32 vals, Hierarchical loss; at N > 1 every
-rank keeps B=4096 rows (weak scaling), the decoder is replicated and the scalar loss, dweight
-and dbias are all-reduced over NCCL each step.  Under torchrun one process drives one GPU.
+rank keeps B=4096 rows (weak scaling), the decoder is replicated, dweight is summed over the ranks
+inside the backward kernel and the scalar loss and dbias are all-reduced each step.  `--workload
+c5` (global batch 65536) splits its rows over the ranks instead (strong scaling).  Under torchrun
+one process drives one GPU.
 
 `value` is batch rows per second over all ranks with inputs resident in HBM; `e2e` is the same
 through the public autograd API with the step's indices / vals / target copied from pinned host
@@ -176,6 +178,9 @@ def main():
     ap.add_argument("--dweight-mode", default="atomic", choices=["atomic", "deterministic"])
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU-baseline sample budget (0 = skip)")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = same as --steps")
+    ap.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
+                    help="weak: every rank keeps the workload's B rows; strong: the workload's B rows are split over "
+                         "the ranks; auto: strong for c5 (its B is the global batch), weak otherwise")
     args = ap.parse_args()
     w = CONFIGS[args.workload]
     kind = args.kind
@@ -207,9 +212,16 @@ def main():
     for item in filter(None, os.environ.get("FLEXSAE_OPTIONS", "").split(",")):   # e.g. "lanes_bwd=8,segments=2"
         name, value = item.split("=")
         nv.set_option(name, int(value))
-    rows = w.B                                     # per rank (weak scaling)
+    scaling = args.scaling if args.scaling != "auto" else ("strong" if w.name == "c5" else "weak")
+    if scaling == "strong":
+        if w.B % world:
+            raise SystemExit(f"--scaling strong: B={w.B} does not split evenly over {world} ranks")
+        rows = w.B // world                        # the workload's batch is the global one
+    else:
+        rows = w.B                                 # per rank
     global_rows = rows * world
     wg = w.replace(B=global_rows)
+    w = w.replace(B=rows)                          # what one GPU processes per step
     x = make_inputs(wg, dev, row0=rank * rows, rows=rows)
     weight = x["weight"].requires_grad_(True)
     bias = x["bias"].requires_grad_(True)
@@ -324,7 +336,7 @@ def main():
         line = {
             "metric": "hier_topk_fwd_bwd_throughput" if kind == "hier" else "topk_fwd_bwd_throughput",
             "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": w.name, "kind": kind, "B_per_gpu": rows, "global_B": global_rows, "K": w.K,
                        "F": w.F, "D": w.D, "storage": f"{w.weight_dtype} weight/bias/target, {w.vals_dtype} vals",
