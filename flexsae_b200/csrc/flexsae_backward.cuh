@@ -279,7 +279,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
 // piece carry the only dependencies:
 //   converting blocks of piece q wait until all unit blocks of piece q have finished;
 //   unit blocks of piece p wait until piece p-2 (same slab) has been converted and cleared.
-// Every wait is on blocks with LOWER block indices, which the hardware dispatches first, so the
+// Every wait is on blocks with LOWER role indices, which start first (see role_index), so the
 // lowest unfinished block never waits on anything unfinished.  Waits are bounded: after
 // kSpinLimit polls a block gives up, sets FLEXSAE_STATUS_PIPELINE_TIMEOUT and carries on (the
 // result is then invalid but the GPU is not held).
@@ -289,6 +289,7 @@ struct PipeArgs {
   int* walk_done;  // [pieces]
   int* conv_done;  // [pieces]
   int pieces, unit_blocks, conv_blocks, conv_offset;
+  int* ticket;  // NULL: blocks take their roles by blockIdx.x; else by the order in which they start
 };
 
 constexpr int kSpinLimit = 1000000;  // polls of >= 0.2 us each: a fraction of a second
@@ -325,12 +326,24 @@ __device__ __forceinline__ void signal_done(int* ctr) {
   }
 }
 
+// The waits of the single-launch kernels are safe as long as a block never starts before the blocks
+// it waits for.  Hardware hands out blockIdx.x in increasing order in practice, but nothing
+// documents that; with a ticket counter the role index IS the starting order, by construction.
+__device__ __forceinline__ int role_index(int* ticket) {
+  if (!ticket) return (int)blockIdx.x;
+  __shared__ int s_ticket;
+  if (threadIdx.x == 0) s_ticket = atomicAdd(ticket, 1);
+  __syncthreads();
+  return s_ticket;
+}
+
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_pipelined_kernel(const PipeArgs pa) {
   extern __shared__ uint4 smem[];
+  const int bid = role_index(pa.ticket);
   const int per = pa.unit_blocks + pa.conv_blocks;
-  const int p = blockIdx.x / per;
-  const int r = blockIdx.x - p * per;
+  const int p = bid / per;
+  const int r = bid - p * per;
   int conv_idx = -1, unit_block = -1;
   if (p == pa.pieces) {
     conv_idx = r;  // the trailing blocks convert the last piece
@@ -397,7 +410,8 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   extern __shared__ uint4 smem[];
   __shared__ int s_chunk, s_state;
   const PipeArgs& pa = sa.p;
-  const int p = blockIdx.x / pa.unit_blocks;
+  const int bid = role_index(pa.ticket);
+  const int p = bid / pa.unit_blocks;
   if (p >= pa.pieces) {  // tail: the last two pieces have no later unit blocks to convert them
     for (int q = max(0, pa.pieces - 2); q < pa.pieces; q++) {
       wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status);
@@ -405,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
     }
     return;
   }
-  const int unit_block = blockIdx.x - p * pa.unit_blocks;
+  const int unit_block = bid - p * pa.unit_blocks;
   if (p >= 2) {
     if (threadIdx.x == 0) s_state = ld_acquire(pa.conv_done + (p - 2)) >= sa.chunks;
     __syncthreads();

@@ -45,6 +45,7 @@ struct Options {
   int sharded_convert_offset_pct = -1;  // sharded backward: their place in the piece (-1 = convert_offset_pct)
   int flag_fan_out = 0;         // sharded backward: a finished slot is announced by one thread per rank
   int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
+  int ticket_order = 0;         // single-launch kernels: blocks take their roles in the order they start (atomic ticket)
   int convert_steal = 0;        // single-launch backward: slab conversion taken in chunks by whichever blocks run
   int steal_chunks = 1024;      // ... chunks per slab
   int steal_exit_chunks = 1;    // ... chunks a unit block takes after its walk
@@ -193,7 +194,7 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   p.off_s0 = off;  // summed prefix residuals of every row (Hierarchical; TopK does not use it)
   off = align_up(off + (size_t)s.B * s.D * 4, 256);
   p.off_ctr = off;  // per-piece completion counters of the single-launch pipeline
-  off = align_up(off + (size_t)(4 * p.pieces + 9) * 4, 256);
+  off = align_up(off + (size_t)(4 * p.pieces + 10) * 4, 256);
   p.total = off;
   return p;
 }
@@ -289,6 +290,7 @@ static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* s
   pa.slabs[1] = slab1;
   pa.walk_done = counters;
   pa.conv_done = counters + pieces;
+  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
@@ -320,6 +322,7 @@ static cudaError_t launch_bwd_stealing(const BwdArgs& b, float* slab0, float* sl
   pa.walk_done = counters;
   pa.conv_done = counters + pieces;
   sa.claim = counters + 2 * pieces + 3;
+  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
@@ -352,6 +355,7 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   pa.conv_done = counters + pieces;       // one counter per slot: pieces + 3 of them
   sa.slot_done = counters + 2 * pieces + 3;  // and pieces + 3 more
   sa.scatter_done = counters + 3 * pieces + 6;  // and again
+  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
@@ -407,6 +411,7 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "segments") && value >= 0 && value <= 256) { g_opt.segments = (int)value; return 0; }
   if (!strcmp(name, "pipeline") && (value == 0 || value == 1)) { g_opt.pipeline = (int)value; return 0; }
   if (!strcmp(name, "convert_steal") && (value == 0 || value == 1)) { g_opt.convert_steal = (int)value; return 0; }
+  if (!strcmp(name, "ticket_order") && (value == 0 || value == 1)) { g_opt.ticket_order = (int)value; return 0; }
   if (!strcmp(name, "steal_chunks") && value >= 1 && value <= 65536) { g_opt.steal_chunks = (int)value; return 0; }
   if (!strcmp(name, "steal_exit_chunks") && value >= 0 && value <= 64) { g_opt.steal_exit_chunks = (int)value; return 0; }
   if (!strcmp(name, "convert_offset_pct") && value >= 0 && value <= 100) { g_opt.convert_offset_pct = (int)value; return 0; }
@@ -428,6 +433,7 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "segments")) return g_opt.segments;
   if (!strcmp(name, "pipeline")) return g_opt.pipeline;
   if (!strcmp(name, "convert_steal")) return g_opt.convert_steal;
+  if (!strcmp(name, "ticket_order")) return g_opt.ticket_order;
   if (!strcmp(name, "steal_chunks")) return g_opt.steal_chunks;
   if (!strcmp(name, "steal_exit_chunks")) return g_opt.steal_exit_chunks;
   if (!strcmp(name, "convert_offset_pct")) return g_opt.convert_offset_pct;
@@ -603,7 +609,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
   if (e != cudaSuccess) return fail((int)e, "gradient clear failed: %s", cudaGetErrorString(e));
   if (peers) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
-    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 9) * 4, st);
+    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 10) * 4, st);
     if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
     a.piece = a.conv_piece = -1;
     a.slab = a.conv_slab = nullptr;
@@ -628,7 +634,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     if (e != cudaSuccess) return fail((int)e, "sharded backward launch failed: %s", cudaGetErrorString(e));
   } else if (g_opt.pipeline) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
-    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 9) * 4, st);
+    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 10) * 4, st);
     if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
     a.piece = a.conv_piece = -1;
     a.slab = a.conv_slab = nullptr;

@@ -342,8 +342,9 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   int p, exch_idx = -1, conv_idx = -1, unit_block = -1;
   int exch_n = E;  // blocks that share the exchange work of this slot
   const bool in_place = sa.dweight_at[0] != nullptr && sa.mc_inbox == nullptr;
-  if ((int)blockIdx.x >= body) {  // three draining slots: no unit blocks, so every block helps with the exchange
-    const int t = blockIdx.x - body;
+  const int bid = role_index(pa.ticket);
+  if (bid >= body) {  // three draining slots: no unit blocks, so every block helps with the exchange
+    const int t = bid - body;
     const int dper = E + pa.conv_blocks;
     p = P + t / dper;
     const int r = t - (p - P) * dper;
@@ -354,8 +355,8 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
       exch_n = (p == P) ? E : dper;
     }
   } else {
-    p = blockIdx.x / per;
-    int r = blockIdx.x - p * per;
+    p = bid / per;
+    int r = bid - p * per;
     if (r < sa.exch_offset) {
       unit_block = r;
     } else if (r < sa.exch_offset + E) {

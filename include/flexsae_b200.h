@@ -63,6 +63,8 @@ const char* flexsae_last_error(void);
  * (what flexsae_choose_segments answers; 0 = derive from the shape), "pipeline" (1: the atomic
  * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct",
  * "direct_f32" (1: with an fp32 decoder the reductions go straight into dweight),
+ * "ticket_order" (1: the blocks of the single-launch backward take their roles from an atomic
+ * ticket, i.e. in the order in which they really start, instead of from blockIdx.x),
  * "convert_steal" (1: in the single-launch backward the slab conversion is not done by blocks at a
  * fixed position but taken in "steal_chunks" chunks by whichever blocks are running, each unit
  * block taking "steal_exit_chunks" after its walk),

@@ -48,6 +48,7 @@ def _auto_options():
     nv.set_option("pipeline", 1)
     nv.set_option("direct_f32", 1)
     nv.set_option("convert_steal", 0)
+    nv.set_option("ticket_order", 0)
     nv.set_option("steal_chunks", 1024)
     nv.set_option("steal_exit_chunks", 1)
     yield
@@ -138,6 +139,24 @@ def test_shared_conversion_queue(name, kind, chunks, exit_chunks):
     nv.set_option("steal_exit_chunks", exit_chunks)
     nv.set_option("direct_f32", 0)       # fp32 decoders through the slab too
     nv.set_option("lanes_bwd", 8)        # many column pieces
+    x = make_inputs(w, "cpu")
+    got = run_fused(kind, x)
+    want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
+    assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
+
+
+@unverified_on_gpu
+@pytest.mark.parametrize("steal", [0, 1])
+@pytest.mark.parametrize("kind", ["topk", "hier"])
+@pytest.mark.parametrize("name", ["t16_64_128_1024_bfloat16", "mixed_bf16w_f32v", "c1"])
+def test_roles_by_starting_order(name, kind, steal):
+    """Blocks of the single-launch backward take their roles from an atomic ticket, not from blockIdx.x."""
+    path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
+    w, kind, gold = load_golden(path)
+    nv.set_option("ticket_order", 1)
+    nv.set_option("convert_steal", steal)
+    nv.set_option("direct_f32", 0)
+    nv.set_option("lanes_bwd", 8)
     x = make_inputs(w, "cpu")
     got = run_fused(kind, x)
     want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
