@@ -48,6 +48,7 @@ CASES = [  # B, F, K, dtype, kind of data
     (5, 64, 8, torch.float32, "normal"), (3, 4096, 128, torch.bfloat16, "normal"), (2, 65536, 128, torch.bfloat16, "normal"),
     (4, 1000, 33, torch.float32, "relu"), (4, 1024, 1024, torch.float16, "normal"), (3, 512, 100, torch.bfloat16, "ties"),
     (2, 131072, 64, torch.float32, "normal"), (1, 8, 1, torch.float16, "ties"), (6, 8192, 256, torch.float16, "relu"),
+    (2, 8192, 16, torch.bfloat16, "const"), (2, 16384, 40, torch.float32, "ties"),      # candidate list overflows
 ]
 
 
@@ -58,7 +59,9 @@ CASES = [  # B, F, K, dtype, kind of data
 def test_gpu_selection_matches_oracle(B, F, K, dtype, data, relu):
     from flexsae_b200 import producer
     g = torch.Generator().manual_seed(B * 131 + F + K)
-    if data == "ties":
+    if data == "const":
+        acts = torch.full((B, F), 0.25).to(dtype)
+    elif data == "ties":
         acts = torch.randint(-3, 4, (B, F), generator=g).to(dtype)
     else:
         acts = torch.randn(B, F, generator=g).to(dtype)
