@@ -41,7 +41,7 @@ def main() -> None:
     args = ap.parse_args()
 
     from . import build as _build
-    if not os.path.exists(_build.TRACE_LIB_PATH):
+    if _build._stale(_build.TRACE_LIB_PATH):     # missing, or older than the sources
         raise SystemExit("build the tuning library first: python -m flexsae_b200.build --trace")
     os.environ["FLEXSAE_LIB"] = _build.TRACE_LIB_PATH
 
