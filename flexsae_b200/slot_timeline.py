@@ -41,8 +41,11 @@ def main() -> None:
     args = ap.parse_args()
 
     from . import build as _build
-    if _build._stale(_build.TRACE_LIB_PATH):     # missing, or older than the sources
+    if not os.path.exists(_build.TRACE_LIB_PATH):
         raise SystemExit("build the tuning library first: python -m flexsae_b200.build --trace")
+    if _build._stale(_build.TRACE_LIB_PATH) and int(os.environ.get("RANK", 0)) == 0:
+        sys.stderr.write("slot_timeline: the tuning library looks older than the sources; "
+                         "rebuild it with python -m flexsae_b200.build --trace\n")
     os.environ["FLEXSAE_LIB"] = _build.TRACE_LIB_PATH
 
     import numpy as np
