@@ -25,6 +25,8 @@ namespace flexsae {
 //   exchange blocks of slot p: every rank's scatter flag >= slot p-1 (the inbox copies of piece p-2
 //     are complete) and, because the gather buffer is double-buffered as well, every rank's exchange
 //     flag >= slot p-1 (piece p-3 has been broadcast, piece p-4 copied out).
+// A rank publishes its flags strictly in slot order (the last block of slot p first waits for the
+// rank's own flag of slot p-1), so a flag value really means "all slots up to this one".
 // With peer-mapped dweight tables there is no gather buffer and the exchange blocks wait for the
 // scatter flags only (plus, in the very last slot, for every rank's last broadcast): an exchange may
 // then take longer than one slot without holding anything up.  Waits are bounded like the local
@@ -412,24 +414,48 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   }
   __syncthreads();
   if (exch_idx >= 0) { FLEXSAE_TRACE_MAX(p, kTrExchEnd); }
-  // The last block of its kind in the slot tells every rank: thread 0 alone, one release store after
-  // the other, or (fan_out) one thread per destination so that the stores travel side by side.
+  // The last block of its kind in the slot tells every rank.
   __shared__ int s_publish;
   const bool scatter = conv_idx >= 0;
   if (threadIdx.x == 0) {
     __threadfence_system();  // this block's peer stores and dweight writes before the count moves
     const int old = atomicAdd((scatter ? sa.scatter_done : sa.slot_done) + p, 1);
     const bool last = old == (scatter ? pa.conv_blocks : exch_n) - 1;
-    s_publish = last && sa.fan_out;
-    if (last && !sa.fan_out) {
-      __threadfence_system();
-      for (int s = 0; s < sa.world; s++)
-        st_release_sys(sa.flags_at[s] + (scatter ? kScatterFlags : 0) + sa.rank, sa.seq_base + p);
+    if (last) __threadfence_system();  // acquire side: what the other blocks did before THEIR count moved
+    if (last && !(scatter && p == 0)) {
+      // A flag says "everything up to slot p", so it may only move forward in slot order: the blocks
+      // of slot p can finish before those of slot p-1 (nothing else orders them), and then this
+      // rank's flag of slot p-1 -- written by the last block of that slot -- has to go out first.
+      const int* own = sa.flags_at[sa.rank] + (scatter ? kScatterFlags : 0) + sa.rank;
+      int32_t* status = pa.b.status;
+      int spins = 0;
+      while (ld_acquire_sys(own) - (sa.seq_base + p - 1) < 0) {
+        __nanosleep(100);
+        if (++spins > kSpinLimit) {
+          if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+          break;
+        }
+      }
     }
+    s_publish = last;
   }
   __syncthreads();
-  if (s_publish && (int)threadIdx.x < sa.world)  // each release orders what the block has seen before its own store
-    st_release_sys(sa.flags_at[threadIdx.x] + (scatter ? kScatterFlags : 0) + sa.rank, sa.seq_base + p);
+  if (s_publish) {  // uniform over the block
+    // The rank's own copy of the flag is stored LAST: the next slot's publisher starts from it (above),
+    // so whoever has seen it has all the other ranks' copies of this value behind it, and no copy can
+    // ever be overtaken by a later value and then fall back.
+    int* const own_copy = sa.flags_at[sa.rank] + (scatter ? kScatterFlags : 0) + sa.rank;
+    const int value = sa.seq_base + p;
+    if (sa.fan_out) {  // one thread per destination: the stores travel side by side
+      if ((int)threadIdx.x < sa.world && (int)threadIdx.x != sa.rank)
+        st_release_sys(sa.flags_at[threadIdx.x] + (scatter ? kScatterFlags : 0) + sa.rank, value);
+    } else if (threadIdx.x == 0) {
+      for (int s = 0; s < sa.world; s++)
+        if (s != sa.rank) st_release_sys(sa.flags_at[s] + (scatter ? kScatterFlags : 0) + sa.rank, value);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(own_copy, value);  // ordered after everything the block stored
+  }
 }
 
 }  // namespace flexsae

@@ -1,0 +1,257 @@
+"""Event-driven models of the block-level protocols of the single-launch backward kernels.
+
+They model WHO WAITS FOR WHAT and WHO PUBLISHES WHAT, exactly as the kernels do it
+(flexsae_b200/csrc/flexsae_backward.cuh: decoder_loss_bwd_stealing_kernel;
+flexsae_b200/csrc/flexsae_sharded.cuh: decoder_loss_bwd_sharded_kernel), with blocks dispatched in
+index order into a limited number of resident slots and random durations, and check the protocol
+itself: no circular wait whatever the number of resident blocks (down to one), nothing read before
+it is complete, nothing overwritten before it has been read, every conversion exactly once.  They
+say nothing about the CUDA code beyond that; the GPU tests do.  Test infrastructure only.
+"""
+import heapq
+import random
+
+
+class Hazard(AssertionError):
+    pass
+
+
+def run_stealing(P, U, chunks, exit_chunks, tail, slots, seed):
+    """P pieces of U unit blocks, `chunks` conversion chunks per slab, `tail` trailing blocks."""
+    rnd = random.Random(seed)
+    walk_done = [0]*P; conv_done = [0]*P; claim = [0]*P
+    conv_started_after_walk = True; walk_after_conv = True
+    def take(q, limit):
+        n = 0
+        while n < limit:
+            c = claim[q]; claim[q] += 1
+            if c >= chunks: break
+            nonlocal conv_started_after_walk
+            if walk_done[q] < U: conv_started_after_walk = False
+            yield ("work", rnd.uniform(0.5, 2.0))
+            conv_done[q] += 1
+            n += 1
+    def block(b):
+        p = b // U
+        if p >= P:
+            for q in range(max(0, P-2), P):
+                yield ("wait", lambda q=q: walk_done[q] >= U)
+                yield from take(q, 10**9)
+            return
+        if p >= 2:
+            if conv_done[p-2] < chunks:
+                yield ("wait", lambda: walk_done[p-2] >= U)
+                yield from take(p-2, 10**9)
+                yield ("wait", lambda: conv_done[p-2] >= chunks)
+        nonlocal walk_after_conv
+        if p >= 2 and conv_done[p-2] < chunks: walk_after_conv = False
+        yield ("work", rnd.uniform(5, 40))
+        walk_done[p] += 1
+        if p >= 1 and exit_chunks > 0 and walk_done[p-1] >= U and claim[p-1] < chunks:
+            yield from take(p-1, exit_chunks)
+    total = P*U + tail
+    nxt = 0; t = 0.0; running = []  # heap of (time, id, gen); waiting list
+    waiting = []; done = 0; seq = 0
+    def start(gen):
+        nonlocal seq
+        step(gen)
+    def step(gen):
+        nonlocal done, seq
+        try:
+            kind, arg = next(gen)
+        except StopIteration:
+            done += 1; return False
+        if kind == "work":
+            seq += 1; heapq.heappush(running, (t + arg, seq, gen))
+        else:
+            waiting.append((arg, gen))
+        return True
+    active = 0
+    def fill():
+        nonlocal nxt, active
+        while active < slots and nxt < total:
+            g = block(nxt); nxt += 1; active += 1
+            if not step(g): active -= 1
+    fill()
+    guard = 0
+    while done < total:
+        guard += 1
+        assert guard < 10**7
+        # release waiters whose condition holds
+        progressed = True
+        while progressed:
+            progressed = False
+            for i, (cond, g) in enumerate(list(waiting)):
+                if cond():
+                    waiting.remove((cond, g))
+                    if not step(g): active -= 1
+                    progressed = True
+            fill()
+        if done >= total: break
+        if not running:
+            raise Hazard(f"deadlock: {len(waiting)} blocks waiting, {done} of {total} finished")
+        t, _, g = heapq.heappop(running)
+        if not step(g): active -= 1
+        fill()
+    if not all(c == chunks for c in conv_done):
+        raise Hazard(f"chunks converted per piece: {conv_done}")
+    if not (conv_started_after_walk and walk_after_conv):
+        raise Hazard("a slab was converted before its walk ended, or walked before it was converted")
+    return t
+
+
+def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=2, ordered=True):
+    """R ranks, P pieces, per slot U unit / E exchange / C converting blocks; `in_place`: reduced rows go
+    straight into the peers' dweight (exchange waits for scatter flags only); `ordered`: a rank's flags are
+    published strictly in slot order (what the kernel does; False shows what that rule prevents)."""
+    rnd = random.Random(seed)
+    speed = [rnd.uniform(0.5, 2.0) for _ in range(R)]
+    nslots = P + 3
+    flagsE = [[0]*R for _ in range(R)]; flagsC = [[0]*R for _ in range(R)]   # [at rank][of rank]
+    inbox = [[[(-1, 0, -1) for _ in range(R)] for _ in range(2)] for _ in range(R)]     # [owner][parity][sender] = (piece, writes, step)
+    reduced = {}   # (step, owner, piece) -> number of exch blocks that reduced it
+    gathered = [[[(-1, 0, -1) for _ in range(R)] for _ in range(2)] for _ in range(R)]  # [dest][parity][owner]
+    copied = {}    # (step, dest, piece) -> exch blocks that copied
+    landed = {}    # (step, dest, piece, owner) -> blocks that wrote dW rows in place
+    t = 0.0; heap = []; waiting = []; seq = [0]
+    errors = []
+    def exch_count(p): return E if p <= P else E + C
+    def make_rank(r, step_no):
+        seq_base = 1 + step_no * nslots
+        walk_done = [0]*(nslots); conv_done = [0]*nslots; slot_done = [0]*nslots; scat_done = [0]*nslots
+        def publish(kind, p):
+            for s in range(R):
+                (flagsC if kind == "C" else flagsE)[s][r] = seq_base + p
+        def waitE(target): return lambda: all(flagsE[r][s] >= target for s in range(R))
+        def waitC(target): return lambda: all(flagsC[r][s] >= target for s in range(R))
+        def unit(p):
+            if p >= 2: yield ("wait", lambda: conv_done[p-1] >= C)
+            yield ("work", rnd.uniform(5, 30) * speed[r])
+            walk_done[p] += 1
+        def conv(p):
+            if p >= 1 and p - 1 < P:
+                yield ("wait", lambda: walk_done[p-1] >= U)
+                yield ("wait", waitE(seq_base + p - 1))
+                q = p - 1
+                yield ("work", rnd.uniform(1, 6) * speed[r])
+                for o in range(R):
+                    pc, wr, st = inbox[o][q & 1][r]
+                    if (pc, st) != (q, step_no):
+                        # first writer of this piece: previous content must have been reduced completely
+                        if pc >= 0 and reduced.get((st, o, pc), 0) < exch_count(pc + 2):
+                            errors.append(("inbox overwritten before reduce", r, o, q, pc, st))
+                        inbox[o][q & 1][r] = (q, 1, step_no)
+                    else:
+                        inbox[o][q & 1][r] = (q, wr + 1, step_no)
+            conv_done[p] += 1
+            scat_done[p] += 1
+            if scat_done[p] == C:
+                if ordered and p > 0: yield ("wait", lambda: flagsC[r][r] >= seq_base + p - 1)
+                publish("C", p)
+        def exch(p):
+            n = exch_count(p)
+            if p >= 2:
+                if (not in_place) or p == P + 2: yield ("wait", waitE(seq_base + p - 1))
+                yield ("wait", waitC(seq_base + min(p - 1, P)))
+            if p >= 2 and p - 2 < P:
+                q = p - 2
+                for s in range(R):
+                    if inbox[r][q & 1][s] != (q, C, step_no): errors.append(("reduce reads incomplete inbox", r, s, q, inbox[r][q & 1][s]))
+                yield ("work", rnd.uniform(1, 6) * speed[r])
+                for s in range(R):
+                    if inbox[r][q & 1][s] != (q, C, step_no): errors.append(("inbox changed during reduce", r, s, q, inbox[r][q & 1][s]))
+                reduced[(step_no, r, q)] = reduced.get((step_no, r, q), 0) + 1
+                for o in range(R):
+                    if o == r: continue
+                    if in_place:
+                        landed[(step_no, o, q, r)] = landed.get((step_no, o, q, r), 0) + 1
+                    else:
+                        pc, wr, st = gathered[o][q & 1][r]
+                        if (pc, st) != (q, step_no):
+                            if pc >= 0 and copied.get((st, o, pc), 0) < exch_count(pc + 3):
+                                errors.append(("gather buffer overwritten before copy", r, o, q, pc))
+                            gathered[o][q & 1][r] = (q, 1, step_no)
+                        else:
+                            gathered[o][q & 1][r] = (q, wr + 1, step_no)
+            if p >= 3 and p - 3 < P and not in_place:
+                q = p - 3
+                for ow in range(R):
+                    if ow != r and gathered[r][q & 1][ow] != (q, exch_count(q + 2), step_no):
+                        errors.append(("copy reads incomplete gather buffer", r, ow, q, gathered[r][q & 1][ow]))
+                yield ("work", rnd.uniform(0.5, 3) * speed[r])
+                copied[(step_no, r, q)] = copied.get((step_no, r, q), 0) + 1
+            slot_done[p] += 1
+            if slot_done[p] == n:
+                if ordered: yield ("wait", lambda: flagsE[r][r] >= seq_base + p - 1)
+                publish("E", p)
+        order = []
+        for p in range(P):
+            row = []
+            u = 0
+            for i in range(U + C):
+                if i >= conv_off and i < conv_off + C: row.append(("conv", p))
+                else: row.append(("unit", p)); u += 1
+            row = row[:exch_off] + [("exch", p)] * E + row[exch_off:]   # exch_off <= conv_off
+            order += row
+        order += [("exch", P)] * E + [("conv", P)] * C
+        order += [("exch", P + 1)] * (E + C) + [("exch", P + 2)] * (E + C)
+        gens = {"unit": unit, "conv": conv, "exch": exch}
+        return [gens[k](p) for k, p in order]
+    # each rank runs `steps` kernels back to back (stream order): next kernel's blocks start after the previous finished
+    state = []
+    for r in range(R):
+        state.append({"step": 0, "blocks": make_rank(r, 0), "nxt": 0, "active": 0, "done": 0})
+    def step_gen(r, g):
+        st = state[r]
+        try:
+            kind, arg = next(g)
+        except StopIteration:
+            st["active"] -= 1; st["done"] += 1
+            return
+        if kind == "work":
+            seq[0] += 1; heapq.heappush(heap, (t + arg, seq[0], r, g))
+        else:
+            waiting.append((arg, r, g))
+    def fill(r):
+        st = state[r]
+        while True:
+            if st["nxt"] >= len(st["blocks"]):
+                if st["done"] == len(st["blocks"]) and st["step"] + 1 < steps:
+                    # in place: every peer's rows of every piece must have landed before the kernel ended
+                    if in_place:
+                        for q in range(P):
+                            for ow in range(R):
+                                if ow != r and landed.get((st["step"], r, q, ow), 0) < E:
+                                    errors.append(("kernel ended before all rows landed", r, q, ow))
+                    st["step"] += 1; st["blocks"] = make_rank(r, st["step"]); st["nxt"] = 0; st["done"] = 0
+                    continue
+                return
+            if st["active"] >= slots: return
+            g = st["blocks"][st["nxt"]]; st["nxt"] += 1; st["active"] += 1
+            step_gen(r, g)
+    for r in range(R): fill(r)
+    guard = 0
+    def all_done(): return all(s["step"] == steps - 1 and s["done"] == len(s["blocks"]) for s in state)
+    while not all_done():
+        guard += 1; assert guard < 5 * 10**6
+        progressed = True
+        while progressed:
+            progressed = False
+            for item in list(waiting):
+                cond, r, g = item
+                if cond():
+                    waiting.remove(item); step_gen(r, g); progressed = True
+            for r in range(R): fill(r)
+        if all_done(): break
+        if not heap:
+            raise Hazard(f"deadlock: {len(waiting)} blocks waiting")
+        t, _, r, g = heapq.heappop(heap)
+        step_gen(r, g)
+        for rr in range(R): fill(rr)
+    if in_place:
+        for r in range(R):
+            for q in range(P):
+                for ow in range(R):
+                    if ow != r and landed.get((steps - 1, r, q, ow), 0) < E: errors.append(("last kernel: rows missing", r, q, ow))
+    if errors:
+        raise Hazard(str(errors[:5]))
