@@ -258,9 +258,35 @@ def main():
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    def kernels_ok() -> bool:
+        """False (on every rank) if a bounded wait inside a backward kernel gave up on any rank."""
+        try:
+            losses.check_status(dev)
+            ok = 1
+        except RuntimeError:
+            ok = 0
+        if distributed:
+            t = torch.tensor([ok], device=dev, dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            ok = int(t.item())
+        return bool(ok)
+
+    dweight_sum = "in the backward kernel over peer memory" if distributed and fd.config.peer_reduce else \
+                  ("NCCL all-reduce after the backward" if distributed else "none (one GPU)")
     for _ in range(args.warmup):
         step()
     barrier()
+    if not kernels_ok():
+        if not (distributed and fd.config.peer_reduce):
+            raise SystemExit("bench.py: a backward kernel reported a timed-out wait during warm-up; no number is reported")
+        # the peer-memory exchange did not complete on this machine: measure with the plain collective
+        fd.config.peer_reduce = False
+        dweight_sum = "NCCL all-reduce after the backward (the peer-memory exchange timed out during warm-up)"
+        for _ in range(args.warmup):
+            step()
+        barrier()
+        if not kernels_ok():
+            raise SystemExit("bench.py: a backward kernel reported a timed-out wait during warm-up; no number is reported")
     losses.launch_count = 0
     with ClockSampler(local_rank) as clocks:
         start, stop = ev(), ev()
@@ -270,6 +296,8 @@ def main():
         stop.record()
         barrier()
     launches = losses.launch_count
+    if not kernels_ok():
+        raise SystemExit("bench.py: a backward kernel reported a timed-out wait inside the timed region; no number is reported")
     elapsed_ms = start.elapsed_time(stop)
     fwd_ms = sum(a.elapsed_time(b) for a, b, _ in marks) / len(marks)
     bwd_ms = sum(b.elapsed_time(c) for _, b, c in marks) / len(marks)
@@ -320,6 +348,8 @@ def main():
     e2e_loop(e2e_steps)
     barrier()
     e2e_s = time.perf_counter() - t0
+    if not kernels_ok():
+        raise SystemExit("bench.py: a backward kernel reported a timed-out wait in the end-to-end loop; no number is reported")
     if distributed:
         t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -342,6 +372,7 @@ def main():
                        "F": w.F, "D": w.D, "storage": f"{w.weight_dtype} weight/bias/target, {w.vals_dtype} vals",
                        "accumulate": "fp32", "dweight_mode": args.dweight_mode,
                        "parallelism": f"batch-sharded x{world}, decoder replicated" if distributed else "single GPU",
+                       "dweight_sum": dweight_sum,
                        "l2": "no flush: the decoder (302 MB at the headline shape) exceeds the 126 MB L2; the "
                              "library's own fp32 gradient slabs are meant to stay L2-resident between launches"},
             "hbm_gbs": alg / (ms_per_step * 1e-3) / 1e9,
