@@ -111,7 +111,11 @@ class PeerExchange:
 
 def _storage_refs(t: torch.Tensor) -> int:
     """How many tensors (and storage handles) share ``t``'s memory."""
-    return torch._C._storage_Use_Count(t.untyped_storage()._cdata)
+    counter = getattr(torch._C, "_storage_Use_Count", None)
+    if counter is None:
+        raise RuntimeError("flexsae_b200.distributed.config.symmetric_dweight needs torch._C._storage_Use_Count "
+                           "(to refuse overwriting a gradient that is still referenced); this torch build lacks it")
+    return counter(t.untyped_storage()._cdata)
 
 
 _exchanges: Dict[tuple, PeerExchange] = {}
