@@ -75,3 +75,51 @@ def encode_topk(x: torch.Tensor, w_enc: torch.Tensor, b_enc: Optional[torch.Tens
     """Encoder of a TopK sparse autoencoder: ``topk_activations(x @ w_enc.T + b_enc, k)`` with
     ``w_enc`` stored [F, D_in] like ``torch.nn.Linear.weight``."""
     return topk_activations(torch.nn.functional.linear(x, w_enc, b_enc), k, relu, vals_dtype)
+
+
+def _main(argv=None) -> dict:
+    """``python -m flexsae_b200.producer``: time the selection kernel on synthetic activations and
+    print one JSON line (rows/s, achieved GB/s of algorithmic bytes: the activations read once plus
+    the (index, value) pairs written)."""
+    import argparse
+    import json
+
+    ap = argparse.ArgumentParser(description="time flexsae_topk_select on synthetic activations")
+    ap.add_argument("--B", type=int, default=4096)
+    ap.add_argument("--F", type=int, default=65536)
+    ap.add_argument("--K", type=int, default=128)
+    ap.add_argument("--dtype", default="bf16", choices=["fp32", "bf16", "fp16"])
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("flexsae_b200.producer needs a CUDA device")
+    dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[args.dtype]
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(0)
+    # two buffers larger than L2 together, used in turn, so that no step finds its rows cached
+    acts = [torch.randn(args.B, args.F, generator=g, device=dev, dtype=torch.float32).to(dtype) for _ in range(2)]
+    for i in range(args.warmup):
+        select_topk(acts[i & 1], args.K)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        select_topk(acts[i & 1], args.K)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    alg = args.B * args.F * acts[0].element_size() + args.B * args.K * (8 + 4)
+    ref_idx = torch.topk(acts[0].float(), args.K, dim=1, sorted=True).indices
+    same = bool(torch.equal(select_topk(acts[0], args.K)[0], ref_idx))      # random activations: no ties to speak of
+    line = {"metric": "topk_select_throughput", "value": args.B / (ms * 1e-3), "unit": "rows/s", "ms_per_step": ms,
+            "config": {"B": args.B, "F": args.F, "K": args.K, "dtype": args.dtype,
+                       "l2": "two input buffers used in turn" + ("" if 2 * acts[0].numel() * acts[0].element_size() > 256e6
+                                                                 else " (smaller than L2 together: cached reads)")},
+            "algorithmic_bytes": alg, "achieved_gbs": alg / (ms * 1e-3) / 1e9, "matches_torch_topk": same}
+    print(json.dumps(line))
+    return line
+
+
+if __name__ == "__main__":
+    _main()
