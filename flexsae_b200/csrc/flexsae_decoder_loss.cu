@@ -355,6 +355,8 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   pa.conv_done = counters + pieces;       // one counter per slot: pieces + 3 of them
   sa.slot_done = counters + 2 * pieces + 3;  // and pieces + 3 more
   sa.scatter_done = counters + 3 * pieces + 6;  // and again
+  sa.claim = nullptr;
+  sa.chunks = sa.exit_chunks = sa.tail_blocks = 0;
   pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
   const long long units = (long long)b.B * b.NS;
@@ -372,6 +374,43 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   sa.rotate = g_opt.scatter_rotate;
   sa.fan_out = g_opt.flag_fan_out;
   const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks + conv) + 3ll * (sa.exch_blocks + conv);
+  if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
+  kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
+  t_launches++;
+  return cudaGetLastError();
+}
+
+template <typename T, int G, bool HIER>
+static cudaError_t launch_bwd_sharded_stealing(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
+                                               ShardArgs sa, cudaStream_t st) {
+  constexpr int UPC = groups_per_cta(G);
+  const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
+  auto kern = decoder_loss_bwd_sharded_stealing_kernel<T, G, HIER>;
+  if (cudaError_t e = allow_smem(kern, smem)) return e;
+  PipeArgs& pa = sa.p;
+  pa.b = b;
+  pa.slabs[0] = slab0;
+  pa.slabs[1] = slab1;
+  pa.walk_done = counters;
+  pa.conv_done = counters + pieces;          // finished chunks per piece
+  sa.slot_done = counters + 2 * pieces + 3;
+  sa.scatter_done = nullptr;
+  sa.claim = counters + 3 * pieces + 6;      // next chunk per piece
+  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
+  pa.pieces = pieces;
+  const long long units = (long long)b.B * b.NS;
+  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
+  pa.conv_blocks = pa.conv_offset = 0;
+  long long chunks = ((long long)b.F * G + kThreads * 4 - 1) / (kThreads * 4);
+  if (chunks > g_opt.steal_chunks) chunks = g_opt.steal_chunks;
+  sa.chunks = (int)chunks;
+  sa.exit_chunks = g_opt.steal_exit_chunks;
+  sa.tail_blocks = sa.chunks < kConvertBlocks ? sa.chunks : kConvertBlocks;
+  sa.exch_blocks = g_opt.exchange_blocks;
+  sa.exch_offset = (int)((long long)pa.unit_blocks * g_opt.exchange_offset_pct / 100);
+  sa.rotate = g_opt.scatter_rotate;
+  sa.fan_out = g_opt.flag_fan_out;
+  const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks) + 3ll * (sa.exch_blocks + sa.tail_blocks);
   if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
   kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
   t_launches++;
@@ -629,7 +668,10 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
       sa.dweight_at[r] = (peers->dweight && r < peers->world) ? peers->dweight[r] : nullptr;
     }
 #define CALL_SHARD(T, G, H) launch_bwd_sharded<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, sa, st)
-    e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD);
+#define CALL_SHARD_STEAL(T, G, H) launch_bwd_sharded_stealing<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, sa, st)
+    if (g_opt.convert_steal && !sa.mc_inbox) e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD_STEAL);
+    else e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD);
+#undef CALL_SHARD_STEAL
 #undef CALL_SHARD
     if (e != cudaSuccess) return fail((int)e, "sharded backward launch failed: %s", cudaGetErrorString(e));
   } else if (g_opt.pipeline) {

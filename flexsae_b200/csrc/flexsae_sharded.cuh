@@ -40,6 +40,8 @@ struct ShardArgs {
   int world, rank, rows_per_rank, seq_base;
   int exch_blocks;  // blocks per slot that reduce / broadcast / copy older pieces
   int exch_offset;  // unit blocks of a slot dispatched before its exchange blocks (<= conv_offset)
+  int* claim;       // shared scatter queue: [pieces] next chunk of each slab to hand out (else unused)
+  int chunks, exit_chunks, tail_blocks;  // ... chunks per slab, chunks a unit block takes after its walk, trailing blocks
   int rotate;       // 1: each rank starts its scatter sweep at its right-hand neighbour's row block
   int fan_out;      // 1: the flags of a finished slot are stored by one thread per destination rank
   void* mc_inbox;     // multicast address of the inbox region of ALL ranks (NULL: plain peer stores)
@@ -327,6 +329,85 @@ __device__ __forceinline__ void switch_reduce_broadcast(const ShardArgs& sa, int
   }
 }
 
+// One more block of a slot has finished its scatter (`scatter`) or exchange work: count it, and if
+// it was the last of `target`, publish `seq_base + slot` in this rank's flag of that kind on every
+// rank.  All threads of the block call it.
+//  * A flag says "everything up to this slot", so it may only move forward in slot order: the blocks
+//    of one slot can finish before those of the previous one (nothing else orders them), and then
+//    this rank's flag of the previous slot -- written by the last block of that slot -- has to go
+//    out first (`first` = there is no previous slot of this kind in this call).
+//  * The rank's own copy of the flag is stored LAST: the next slot's publisher starts from it, so
+//    whoever has seen it has all the other ranks' copies of this value behind it, and no copy can
+//    ever be overtaken by a later value and then fall back.
+__device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scatter, int* counter, int target, int slot,
+                                                  bool first) {
+  __shared__ int s_publish;
+  const int kind_off = scatter ? kScatterFlags : 0;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // this block's peer stores and dweight writes before the count moves
+    const int old = atomicAdd(counter, 1);
+    const bool last = old == target - 1;
+    if (last) __threadfence_system();  // acquire side: what the other blocks did before THEIR count moved
+    if (last && !first) {
+      const int* own = sa.flags_at[sa.rank] + kind_off + sa.rank;
+      int32_t* status = sa.p.b.status;
+      int spins = 0;
+      while (ld_acquire_sys(own) - (sa.seq_base + slot - 1) < 0) {
+        __nanosleep(100);
+        if (++spins > kSpinLimit) {
+          if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+          break;
+        }
+      }
+    }
+    s_publish = last;
+  }
+  __syncthreads();
+  if (s_publish) {  // uniform over the block
+    const int value = sa.seq_base + slot;
+    if (sa.fan_out) {  // one thread per destination: the stores travel side by side
+      if ((int)threadIdx.x < sa.world && (int)threadIdx.x != sa.rank)
+        st_release_sys(sa.flags_at[threadIdx.x] + kind_off + sa.rank, value);
+    } else if (threadIdx.x == 0) {
+      for (int s = 0; s < sa.world; s++)
+        if (s != sa.rank) st_release_sys(sa.flags_at[s] + kind_off + sa.rank, value);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) st_release_sys(sa.flags_at[sa.rank] + kind_off + sa.rank, value);  // after everything the block stored
+  }
+  __syncthreads();  // s_publish may be rewritten by the caller's next round
+}
+
+// Exchange work of slot p (all threads of an exchange block): wait for what it reads to be
+// complete, reduce + broadcast piece p-2, copy piece p-3 out of the gather buffer.
+template <typename T, int G>
+__device__ __forceinline__ void exchange_slot(const ShardArgs& sa, int p, int exch_idx, int exch_n, bool in_place) {
+  const int P = sa.p.pieces;
+  FLEXSAE_TRACE_MIN(p, kTrExchEntry);
+  // the inbox copies of piece p-2 are complete (the last scatter belongs to slot P); through the
+  // gather buffer also: piece p-3 has arrived in it and piece p-4 has been copied out everywhere;
+  // in place: the very last slot returns only when every rank's last broadcast has landed here
+  if (p >= 2) wait_peers(sa, !in_place || p == P + 2, sa.seq_base + p - 1, true, sa.seq_base + min(p - 1, P));
+  FLEXSAE_TRACE_MIN(p, kTrExchStart);
+  if (p >= 2 && p - 2 < P && sa.mc_inbox) {
+    switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, exch_n);
+  } else if (p >= 2 && p - 2 < P) {
+    if (in_place) {
+      if (sa.world <= 2) reduce_broadcast<T, G, 4, true>(sa, p - 2, exch_idx, exch_n);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2, true>(sa, p - 2, exch_idx, exch_n);
+      else reduce_broadcast<T, G, 1, true>(sa, p - 2, exch_idx, exch_n);
+    } else {
+      if (sa.world <= 2) reduce_broadcast<T, G, 4, false>(sa, p - 2, exch_idx, exch_n);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2, false>(sa, p - 2, exch_idx, exch_n);
+      else reduce_broadcast<T, G, 1, false>(sa, p - 2, exch_idx, exch_n);
+    }
+  }
+  // in-place broadcast: nothing to copy, but slot pieces+2 still waits (above) until every rank's
+  // last broadcast has landed in this rank's dweight
+  if (p >= 3 && p - 3 < P && !in_place) copy_gathered<T, G>(sa, p - 3, exch_idx, exch_n);
+}
+
 // Block roles inside slot p of the sharded launch (slots 0..pieces+2):
 //   exchange blocks (sa.exch_blocks, after the first sa.exch_offset unit blocks): reduce + broadcast
 //     of piece p-2 and the copy of piece p-3 -- local loads and posted stores only, so a few blocks
@@ -389,73 +470,118 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
     signal_done(pa.conv_done + p);
     FLEXSAE_TRACE_MAX(p, kTrConvEnd);
   } else {
-    FLEXSAE_TRACE_MIN(p, kTrExchEntry);
-    // the inbox copies of piece p-2 are complete (the last scatter happens in slot P); through the
-    // gather buffer also: piece p-3 has arrived in it and piece p-4 has been copied out everywhere;
-    // in place: the very last slot returns only when every rank's last broadcast has landed here
-    if (p >= 2) wait_peers(sa, !in_place || p == P + 2, sa.seq_base + p - 1, true, sa.seq_base + min(p - 1, P));
-    FLEXSAE_TRACE_MIN(p, kTrExchStart);
-    if (p >= 2 && p - 2 < P && sa.mc_inbox) {
-      switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, exch_n);
-    } else if (p >= 2 && p - 2 < P) {
-      if (in_place) {
-        if (sa.world <= 2) reduce_broadcast<T, G, 4, true>(sa, p - 2, exch_idx, exch_n);
-        else if (sa.world <= 4) reduce_broadcast<T, G, 2, true>(sa, p - 2, exch_idx, exch_n);
-        else reduce_broadcast<T, G, 1, true>(sa, p - 2, exch_idx, exch_n);
-      } else {
-        if (sa.world <= 2) reduce_broadcast<T, G, 4, false>(sa, p - 2, exch_idx, exch_n);
-        else if (sa.world <= 4) reduce_broadcast<T, G, 2, false>(sa, p - 2, exch_idx, exch_n);
-        else reduce_broadcast<T, G, 1, false>(sa, p - 2, exch_idx, exch_n);
-      }
-    }
-    // in-place broadcast: nothing to copy, but slot pieces+2 still waits (above) until every rank's
-    // last broadcast has landed in this rank's dweight
-    if (p >= 3 && p - 3 < P && !in_place) copy_gathered<T, G>(sa, p - 3, exch_idx, exch_n);
+    exchange_slot<T, G>(sa, p, exch_idx, exch_n, in_place);
   }
   __syncthreads();
   if (exch_idx >= 0) { FLEXSAE_TRACE_MAX(p, kTrExchEnd); }
-  // The last block of its kind in the slot tells every rank.
-  __shared__ int s_publish;
   const bool scatter = conv_idx >= 0;
-  if (threadIdx.x == 0) {
-    __threadfence_system();  // this block's peer stores and dweight writes before the count moves
-    const int old = atomicAdd((scatter ? sa.scatter_done : sa.slot_done) + p, 1);
-    const bool last = old == (scatter ? pa.conv_blocks : exch_n) - 1;
-    if (last) __threadfence_system();  // acquire side: what the other blocks did before THEIR count moved
-    if (last && !(scatter && p == 0)) {
-      // A flag says "everything up to slot p", so it may only move forward in slot order: the blocks
-      // of slot p can finish before those of slot p-1 (nothing else orders them), and then this
-      // rank's flag of slot p-1 -- written by the last block of that slot -- has to go out first.
-      const int* own = sa.flags_at[sa.rank] + (scatter ? kScatterFlags : 0) + sa.rank;
-      int32_t* status = pa.b.status;
-      int spins = 0;
-      while (ld_acquire_sys(own) - (sa.seq_base + p - 1) < 0) {
-        __nanosleep(100);
-        if (++spins > kSpinLimit) {
-          if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-          break;
-        }
+  count_and_publish(sa, scatter, (scatter ? sa.scatter_done : sa.slot_done) + p, scatter ? pa.conv_blocks : exch_n, p,
+                    scatter && p == 0);
+}
+
+// ---- the sharded backward with a shared scatter queue ---------------------------------------------
+// As decoder_loss_bwd_stealing_kernel: no converting blocks at a fixed position.  The scatter of a
+// finished slab (piece q) is cut into sa.chunks chunks behind a claim counter and taken by
+//   unit blocks of piece q+1 after their walk (if piece q's walk is complete and every owner has
+//     reduced what that half of its inbox held -- checked, never waited for),
+//   unit blocks of piece q+2 before their walk, when they find their slab still occupied,
+//   exchange blocks of slot q+2 before they wait for that very scatter, and trailing blocks in slot P
+//     for the last two pieces,
+// so every wait is for chunks already in the hands of running blocks or for lower role indices.  The
+// block that completes a slab's last chunk publishes the rank's scatter flag (value of slot q+1).
+template <typename T, int G>
+__device__ __forceinline__ void take_scatter_chunks(const ShardArgs& sa, int q, int limit, int* s_chunk) {
+  const PipeArgs& pa = sa.p;
+  for (int n = 0; n < limit; n++) {
+    if (threadIdx.x == 0) *s_chunk = atomicAdd(sa.claim + q, 1);
+    __syncthreads();
+    const int c = *s_chunk;
+    __syncthreads();  // everyone has read the chunk number before thread 0 may overwrite it
+    if (c >= sa.chunks) break;
+    slab_scatter<T, G>(pa.slabs[q & 1], sa, q, c, sa.chunks);
+    // conv_done[q] gates the unit blocks that reuse the slab and, when full, the scatter flag of slot q+1
+    count_and_publish(sa, true, pa.conv_done + q, sa.chunks, q + 1, q == 0);
+  }
+}
+
+// wait until piece q may be scattered (its walk is complete, the owners have reduced piece q-2), then take what is left
+template <typename T, int G>
+__device__ __forceinline__ void finish_scatter(const ShardArgs& sa, int q, int* s_chunk) {
+  wait_count(sa.p.walk_done + q, sa.p.unit_blocks, sa.p.b.status);
+  wait_peers(sa, true, sa.seq_base + q, false, 0);
+  take_scatter_chunks<T, G>(sa, q, 0x7fffffff, s_chunk);
+}
+
+template <typename T, int G, bool HIER>
+__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_stealing_kernel(const ShardArgs sa) {
+  extern __shared__ uint4 smem[];
+  __shared__ int s_chunk, s_state;
+  const PipeArgs& pa = sa.p;
+  const int P = pa.pieces;
+  const int E = sa.exch_blocks;
+  const int per = E + pa.unit_blocks;
+  const int body = P * per;
+  const bool in_place = sa.dweight_at[0] != nullptr;
+  const int bid = role_index(pa.ticket);
+  int p, exch_idx = -1, unit_block = -1, exch_n = E;
+  bool tail = false;
+  if (bid >= body) {
+    const int t = bid - body;
+    const int dper = E + sa.tail_blocks;
+    p = P + t / dper;
+    const int r = t - (p - P) * dper;
+    if (p == P && r >= E) {
+      tail = true;
+    } else {
+      exch_idx = r;
+      exch_n = (p == P) ? E : dper;
+    }
+  } else {
+    p = bid / per;
+    const int r = bid - p * per;
+    if (r < sa.exch_offset) unit_block = r;
+    else if (r < sa.exch_offset + E) exch_idx = r - sa.exch_offset;
+    else unit_block = r - E;
+  }
+  if (tail) {
+    for (int q = max(0, P - 2); q < P; q++) finish_scatter<T, G>(sa, q, &s_chunk);
+    return;
+  }
+  if (unit_block >= 0) {
+    if (p >= 2) {
+      if (threadIdx.x == 0) s_state = ld_acquire(pa.conv_done + (p - 2)) >= sa.chunks;
+      __syncthreads();
+      const bool free_slab = s_state != 0;
+      __syncthreads();
+      if (!free_slab) {  // this block's slab still holds piece p-2: help, then wait for the chunks in other hands
+        finish_scatter<T, G>(sa, p - 2, &s_chunk);
+        wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status);
       }
     }
-    s_publish = last;
-  }
-  __syncthreads();
-  if (s_publish) {  // uniform over the block
-    // The rank's own copy of the flag is stored LAST: the next slot's publisher starts from it (above),
-    // so whoever has seen it has all the other ranks' copies of this value behind it, and no copy can
-    // ever be overtaken by a later value and then fall back.
-    int* const own_copy = sa.flags_at[sa.rank] + (scatter ? kScatterFlags : 0) + sa.rank;
-    const int value = sa.seq_base + p;
-    if (sa.fan_out) {  // one thread per destination: the stores travel side by side
-      if ((int)threadIdx.x < sa.world && (int)threadIdx.x != sa.rank)
-        st_release_sys(sa.flags_at[threadIdx.x] + (scatter ? kScatterFlags : 0) + sa.rank, value);
-    } else if (threadIdx.x == 0) {
-      for (int s = 0; s < sa.world; s++)
-        if (s != sa.rank) st_release_sys(sa.flags_at[s] + (scatter ? kScatterFlags : 0) + sa.rank, value);
+    FLEXSAE_TRACE_MIN(p, kTrUnitStart);
+    walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
+    signal_done(pa.walk_done + p);
+    FLEXSAE_TRACE_MAX(p, kTrUnitEnd);
+    if (p >= 1 && sa.exit_chunks > 0) {
+      // may piece p-1 be scattered right now?  its walk complete, chunks left, and every owner done with
+      // the inbox half it goes to: one thread per rank looks at that rank's exchange flag
+      const int q = p - 1;
+      bool ok = true;
+      if ((int)threadIdx.x < sa.world)
+        ok = ld_acquire_sys(sa.flags_at[sa.rank] + threadIdx.x) - (sa.seq_base + q) >= 0;
+      else if ((int)threadIdx.x == 32)
+        ok = ld_acquire(pa.walk_done + q) >= pa.unit_blocks && ld_acquire(sa.claim + q) < sa.chunks;
+      if (__syncthreads_and(ok)) take_scatter_chunks<T, G>(sa, q, sa.exit_chunks, &s_chunk);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_sys(own_copy, value);  // ordered after everything the block stored
+    return;
   }
+  // exchange block: first whatever is left of the scatter it is about to wait for (nobody with a
+  // lower role index is bound to finish it), then the slot's exchange
+  if (p >= 2 && p - 2 < P) finish_scatter<T, G>(sa, p - 2, &s_chunk);
+  exchange_slot<T, G>(sa, p, exch_idx, exch_n, in_place);
+  __syncthreads();
+  FLEXSAE_TRACE_MAX(p, kTrExchEnd);
+  count_and_publish(sa, false, sa.slot_done + p, exch_n, p, false);
 }
 
 }  // namespace flexsae

@@ -100,10 +100,14 @@ def run_stealing(P, U, chunks, exit_chunks, tail, slots, seed):
     return t
 
 
-def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=2, ordered=True):
+def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=2, ordered=True, steal=None):
     """R ranks, P pieces, per slot U unit / E exchange / C converting blocks; `in_place`: reduced rows go
     straight into the peers' dweight (exchange waits for scatter flags only); `ordered`: a rank's flags are
-    published strictly in slot order (what the kernel does; False shows what that rule prevents)."""
+    published strictly in slot order (what the kernel does; False shows what that rule prevents);
+    `steal` = (chunks, exit_chunks): no converting blocks -- the scatter of a finished slab is taken in
+    chunks by unit blocks (after their walk, or before it when their slab is still occupied) and by C
+    tail blocks after the last piece."""
+    writes_per_piece = steal[0] if steal else C
     rnd = random.Random(seed)
     speed = [rnd.uniform(0.5, 2.0) for _ in range(R)]
     nslots = P + 3
@@ -124,10 +128,51 @@ def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=
                 (flagsC if kind == "C" else flagsE)[s][r] = seq_base + p
         def waitE(target): return lambda: all(flagsE[r][s] >= target for s in range(R))
         def waitC(target): return lambda: all(flagsC[r][s] >= target for s in range(R))
+        claim = [0]*nslots; piece_done = [0]*nslots
+        def scatter_into_inboxes(q):
+            for o in range(R):
+                pc, wr, st = inbox[o][q & 1][r]
+                if (pc, st) != (q, step_no):
+                    # first writer of this piece: previous content must have been reduced completely
+                    if pc >= 0 and reduced.get((st, o, pc), 0) < exch_count(pc + 2):
+                        errors.append(("inbox overwritten before reduce", r, o, q, pc, st))
+                    inbox[o][q & 1][r] = (q, 1, step_no)
+                else:
+                    inbox[o][q & 1][r] = (q, wr + 1, step_no)
+        def take(q, limit):
+            n = 0
+            while n < limit:
+                c = claim[q]; claim[q] += 1
+                if c >= steal[0]: break
+                if walk_done[q] < U: errors.append(("slab scattered before its walk ended", r, q))
+                yield ("work", rnd.uniform(0.3, 2) * speed[r])
+                scatter_into_inboxes(q)
+                piece_done[q] += 1
+                if piece_done[q] == steal[0]:
+                    if ordered and q > 0: yield ("wait", lambda: flagsC[r][r] >= seq_base + q)
+                    publish("C", q + 1)
+                n += 1
         def unit(p):
+            if steal:
+                if p >= 2 and piece_done[p-2] < steal[0]:
+                    yield ("wait", lambda: walk_done[p-2] >= U)
+                    yield ("wait", waitE(seq_base + p - 2))
+                    yield from take(p - 2, 10**9)
+                    yield ("wait", lambda: piece_done[p-2] >= steal[0])
+                if p >= 2 and piece_done[p-2] < steal[0]: errors.append(("walk started on an unconverted slab", r, p))
+                yield ("work", rnd.uniform(5, 30) * speed[r])
+                walk_done[p] += 1
+                if p >= 1 and steal[1] > 0 and walk_done[p-1] >= U and claim[p-1] < steal[0] and waitE(seq_base + p - 1)():
+                    yield from take(p - 1, steal[1])
+                return
             if p >= 2: yield ("wait", lambda: conv_done[p-1] >= C)
             yield ("work", rnd.uniform(5, 30) * speed[r])
             walk_done[p] += 1
+        def tail(p):
+            for q in range(max(0, P - 2), P):
+                yield ("wait", lambda q=q: walk_done[q] >= U)
+                yield ("wait", waitE(seq_base + q))
+                yield from take(q, 10**9)
         def conv(p):
             if p >= 1 and p - 1 < P:
                 yield ("wait", lambda: walk_done[p-1] >= U)
@@ -150,16 +195,22 @@ def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=
                 publish("C", p)
         def exch(p):
             n = exch_count(p)
+            if steal and p >= 2 and p - 2 < P:
+                # nobody with a lower index is bound to finish the scatter this block is about to wait
+                # for, so it takes what is left of it first
+                yield ("wait", lambda: walk_done[p-2] >= U)
+                yield ("wait", waitE(seq_base + p - 2))
+                yield from take(p - 2, 10**9)
             if p >= 2:
                 if (not in_place) or p == P + 2: yield ("wait", waitE(seq_base + p - 1))
                 yield ("wait", waitC(seq_base + min(p - 1, P)))
             if p >= 2 and p - 2 < P:
                 q = p - 2
                 for s in range(R):
-                    if inbox[r][q & 1][s] != (q, C, step_no): errors.append(("reduce reads incomplete inbox", r, s, q, inbox[r][q & 1][s]))
+                    if inbox[r][q & 1][s] != (q, writes_per_piece, step_no): errors.append(("reduce reads incomplete inbox", r, s, q, inbox[r][q & 1][s]))
                 yield ("work", rnd.uniform(1, 6) * speed[r])
                 for s in range(R):
-                    if inbox[r][q & 1][s] != (q, C, step_no): errors.append(("inbox changed during reduce", r, s, q, inbox[r][q & 1][s]))
+                    if inbox[r][q & 1][s] != (q, writes_per_piece, step_no): errors.append(("inbox changed during reduce", r, s, q, inbox[r][q & 1][s]))
                 reduced[(step_no, r, q)] = reduced.get((step_no, r, q), 0) + 1
                 for o in range(R):
                     if o == r: continue
@@ -188,14 +239,14 @@ def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=
         for p in range(P):
             row = []
             u = 0
-            for i in range(U + C):
-                if i >= conv_off and i < conv_off + C: row.append(("conv", p))
+            for i in range(U + (0 if steal else C)):
+                if not steal and i >= conv_off and i < conv_off + C: row.append(("conv", p))
                 else: row.append(("unit", p)); u += 1
             row = row[:exch_off] + [("exch", p)] * E + row[exch_off:]   # exch_off <= conv_off
             order += row
-        order += [("exch", P)] * E + [("conv", P)] * C
+        order += [("exch", P)] * E + [("tail" if steal else "conv", P)] * C
         order += [("exch", P + 1)] * (E + C) + [("exch", P + 2)] * (E + C)
-        gens = {"unit": unit, "conv": conv, "exch": exch}
+        gens = {"unit": unit, "conv": conv, "exch": exch, "tail": tail}
         return [gens[k](p) for k, p in order]
     # each rank runs `steps` kernels back to back (stream order): next kernel's blocks start after the previous finished
     state = []

@@ -24,9 +24,12 @@ def _worker(rank, world, port, kind, q, mode):
         from flexsae_b200.workloads import CONFIGS, make_inputs
         fd.config.peer_reduce = mode != "nccl"
         fd.config.use_multicast = mode == "multicast"
-        fd.config.symmetric_dweight = mode in ("inplace", "inplace_small")
+        fd.config.symmetric_dweight = mode in ("inplace", "inplace_small", "inplace_steal")
         fd.config.fused_small_reduce = mode == "inplace_small"
-        if mode in ("inplace", "inplace_small"):       # together with the other non-default exchange settings
+        if mode in ("steal", "inplace_steal"):      # scatter taken from a shared queue instead of by converting blocks
+            fx._native.set_option("convert_steal", 1)
+            fx._native.set_option("steal_chunks", 96 if mode == "steal" else 1024)
+        if mode in ("inplace", "inplace_small", "inplace_steal"):       # together with the other non-default exchange settings
             for name, value in (("exchange_offset_pct", 25), ("scatter_rotate", 1), ("flag_fan_out", 1)):
                 fx._native.set_option(name, value)
         w = CONFIGS["c3_k32"].replace(B=768, F=8190)       # F not a multiple of the world size
@@ -43,7 +46,7 @@ def _worker(rank, world, port, kind, q, mode):
         torch.cuda.synchronize()
         fx.check_status()
         out = (rank, float(loss), weight.grad.float().cpu(), vals.grad.float().cpu(), bias.grad.float().cpu())
-        if mode in ("inplace", "inplace_small"):       # the gradient is a view of the persistent table: a backward that would
+        if fd.config.symmetric_dweight:       # the gradient is a view of the persistent table: a backward that would
             loss = fn(x["indices"], weight, vals, bias, x["target"])   # overwrite it while it is held must refuse
             with pytest.raises(RuntimeError, match="still referenced"):
                 loss.backward(x["grad_out"])
@@ -60,7 +63,9 @@ def _worlds():
 
 @pytest.mark.parametrize("world", _worlds())
 @pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "inplace", "nccl",
-                                         pytest.param("inplace_small", marks=unverified_on_gpu)])
+                                         pytest.param("inplace_small", marks=unverified_on_gpu),
+                                         pytest.param("steal", marks=unverified_on_gpu),
+                                         pytest.param("inplace_steal", marks=unverified_on_gpu)])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
 def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     if torch.cuda.device_count() < world:
@@ -74,7 +79,8 @@ def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
-    port += {"multicast": 13, "stores": 5, "inplace": 17, "inplace_small": 19, "nccl": 0}[peer_reduce] + 29 * world
+    port += {"multicast": 13, "stores": 5, "inplace": 17, "inplace_small": 19, "steal": 21, "inplace_steal": 23,
+             "nccl": 0}[peer_reduce] + 29 * world
     procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce)) for r in range(world)]
     for p in procs:
         p.start()

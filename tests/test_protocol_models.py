@@ -39,3 +39,10 @@ def test_flags_must_be_published_in_slot_order():
         except pm.Hazard:
             hazards += 1
     assert hazards > 0
+
+
+@pytest.mark.parametrize("in_place", [False, True])
+def test_sharded_exchange_with_the_shared_scatter_queue(in_place):
+    for seed in range(150):
+        rnd = random.Random(1000 + seed)
+        pm.run_sharded(in_place=in_place, steal=(rnd.randint(1, 12), rnd.randint(0, 3)), **_shard_case(seed))
