@@ -306,3 +306,81 @@ def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=
                     if ow != r and landed.get((steps - 1, r, q, ow), 0) < E: errors.append(("last kernel: rows missing", r, q, ow))
     if errors:
         raise Hazard(str(errors[:5]))
+
+
+def run_pipelined(P, U, C, conv_off, slots, seed):
+    """decoder_loss_bwd_pipelined_kernel: per piece U unit blocks with the C blocks that convert the
+    PREVIOUS piece inserted at `conv_off`, C trailing blocks for the last piece; unit blocks of piece p
+    wait for the conversion of piece p-2 (same slab), converting blocks for the walk of their piece."""
+    rnd = random.Random(seed)
+    walk_done = [0] * P
+    conv_done = [0] * P
+    problems = []
+
+    def unit(p):
+        if p >= 2:
+            yield ("wait", lambda: conv_done[p - 2] >= C)
+        yield ("work", rnd.uniform(5, 40))
+        walk_done[p] += 1
+
+    def conv(q):
+        if q < 0:
+            return
+        yield ("wait", lambda: walk_done[q] >= U)
+        yield ("work", rnd.uniform(1, 6))
+        conv_done[q] += 1
+
+    order = []
+    for p in range(P):
+        row = [("unit", p)] * U
+        row = row[:conv_off] + [("conv", p - 1)] * C + row[conv_off:]
+        order += row
+    order += [("conv", P - 1)] * C
+    blocks = [(unit if k == "unit" else conv)(i) for k, i in order]
+    t, heap, waiting, seq, nxt, active, done = 0.0, [], [], 0, 0, 0, 0
+
+    def advance(g):
+        nonlocal seq, active, done
+        try:
+            kind, arg = next(g)
+        except StopIteration:
+            active -= 1
+            done += 1
+            return
+        if kind == "work":
+            seq += 1
+            heapq.heappush(heap, (t + arg, seq, g))
+        else:
+            waiting.append((arg, g))
+
+    def fill():
+        nonlocal nxt, active
+        while active < slots and nxt < len(blocks):
+            g = blocks[nxt]
+            nxt += 1
+            active += 1
+            advance(g)
+
+    fill()
+    while done < len(blocks):
+        moved = True
+        while moved:
+            moved = False
+            for item in list(waiting):
+                if item[0]():
+                    waiting.remove(item)
+                    advance(item[1])
+                    moved = True
+            fill()
+        if done >= len(blocks):
+            break
+        if not heap:
+            raise Hazard(f"deadlock: {len(waiting)} blocks waiting, {done} of {len(blocks)} finished")
+        t, _, g = heapq.heappop(heap)
+        advance(g)
+        fill()
+    if any(c != C for c in conv_done) or any(w != U for w in walk_done):
+        problems.append((walk_done, conv_done))
+    if problems:
+        raise Hazard(str(problems))
+    return t

@@ -46,3 +46,11 @@ def test_sharded_exchange_with_the_shared_scatter_queue(in_place):
     for seed in range(150):
         rnd = random.Random(1000 + seed)
         pm.run_sharded(in_place=in_place, steal=(rnd.randint(1, 12), rnd.randint(0, 3)), **_shard_case(seed))
+
+
+def test_pipelined_backward_never_waits_for_a_later_block():
+    for seed in range(300):
+        rnd = random.Random(seed)
+        U = rnd.randint(1, 30)
+        pm.run_pipelined(P=rnd.randint(1, 8), U=U, C=rnd.randint(1, 6), conv_off=rnd.randint(0, U), slots=rnd.randint(1, 20),
+                         seed=seed)
