@@ -384,3 +384,47 @@ def run_pipelined(P, U, C, conv_off, slots, seed):
     if problems:
         raise Hazard(str(problems))
     return t
+
+
+def run_small_allreduce(R, calls, seed):
+    """small_allreduce_kernel: call number n (1, 2, ...) of rank r stores its value into cell [n & 1][r]
+    of every rank, announces n in every rank's flag array, waits until every sender has announced n
+    and reads the cells.  Calls of one rank run one after the other (stream order).  Checked: every
+    read sees the value of the same call number (two cells per sender are enough)."""
+    rnd = random.Random(seed)
+    cells = [[[0] * R for _ in range(2)] for _ in range(R)]      # [at rank][parity][sender] = call number stored
+    flags = [[0] * R for _ in range(R)]                          # [at rank][sender]
+    events = []                                                  # (time, seq, rank, phase, call)
+    seq = 0
+    for r in range(R):
+        heapq.heappush(events, (rnd.uniform(0, 5), seq, r, "push", 1))
+        seq += 1
+    waiting = []
+    finished = [0] * R
+    t = 0.0
+    while events or waiting:
+        if not events:
+            raise Hazard(f"deadlock: {len(waiting)} ranks waiting")
+        t, _, r, phase, n = heapq.heappop(events)
+        if phase == "push":
+            for o in range(R):
+                cells[o][n & 1][r] = n
+            for o in range(R):
+                flags[o][r] = n
+            waiting.append((r, n))
+        elif phase == "read":
+            for s_ in range(R):
+                if cells[r][n & 1][s_] != n:
+                    raise Hazard(f"rank {r} call {n} read sender {s_}'s cell holding call {cells[r][n & 1][s_]}")
+            finished[r] = n
+            if n < calls:
+                seq += 1
+                heapq.heappush(events, (t + rnd.uniform(0, 5), seq, r, "push", n + 1))
+        for item in list(waiting):
+            rr, nn = item
+            if all(flags[rr][s_] >= nn for s_ in range(R)):
+                waiting.remove(item)
+                seq += 1
+                heapq.heappush(events, (t + rnd.uniform(0, 3), seq, rr, "read", nn))    # the read takes a while
+    if any(f != calls for f in finished):
+        raise Hazard(str(finished))

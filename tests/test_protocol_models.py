@@ -54,3 +54,9 @@ def test_pipelined_backward_never_waits_for_a_later_block():
         U = rnd.randint(1, 30)
         pm.run_pipelined(P=rnd.randint(1, 8), U=U, C=rnd.randint(1, 6), conv_off=rnd.randint(0, U), slots=rnd.randint(1, 20),
                          seed=seed)
+
+
+def test_small_allreduce_needs_only_two_cells_per_sender():
+    for seed in range(200):
+        rnd = random.Random(seed)
+        pm.run_small_allreduce(R=rnd.randint(2, 8), calls=rnd.randint(1, 12), seed=seed)
