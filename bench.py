@@ -16,6 +16,12 @@ one process drives one GPU.
 through the public autograd API with the step's indices / vals / target copied from pinned host
 memory and the loss read back every step.  `--impl reference` times the torch restatement of the
 reference losses on the host CPU cores instead (the reference's own CPU-runnable path).
+
+With more than one rank the run first checks the fused cross-GPU gradient sum against a plain NCCL
+all-reduce of the per-rank gradients on the same inputs and refuses to print a number on a mismatch
+(`"parity_checked": true` in the line).  Environment switches (all optional): FLEXSAE_OPTIONS
+(`name=value,...` for flexsae_set_option), FLEXSAE_PEER_REDUCE, FLEXSAE_MULTICAST,
+FLEXSAE_SYMMETRIC_DWEIGHT, FLEXSAE_FUSED_SMALL_REDUCE (0/1: flexsae_b200.distributed.config).
 """
 from __future__ import annotations
 
@@ -40,6 +46,11 @@ FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only withou
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {("c3_k128", "hier", "atomic"): 3416.0e6}
 
 
+# Exchange settings `bench.py` uses when it runs on several GPUs (each can be overridden through the
+# environment, see the module docstring); they are reported in the line's "exchange" object.
+SHARDED_DEFAULTS = {"symmetric_dweight": False, "fused_small_reduce": False, "options": {}}
+
+
 def hbm_peak():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -55,7 +66,7 @@ class ClockSampler:
                0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
                0x100: "display_clock_setting"}
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
@@ -127,23 +138,43 @@ def cpu_reference_rate(w, kind, budget_s: float, chunk_rows: int = 256, repeats:
             "ms_per_step_extrapolated": best / rows * w.B * 1e3}
 
 
+def workload_config(w, kind, rows, global_rows, world, dweight_mode, **extra):
+    """The `config` object of a bench line: the same keys for the native and the reference arm."""
+    cfg = {"workload": w.name, "kind": kind, "B_per_gpu": rows, "global_B": global_rows, "K": w.K, "F": w.F, "D": w.D,
+           "storage": f"{w.weight_dtype} weight/bias/target, {w.vals_dtype} vals", "accumulate": "fp32",
+           "dweight_mode": dweight_mode,
+           "parallelism": f"batch-sharded x{world}, decoder replicated" if world > 1 else "single GPU",
+           "l2": "no flush: the decoder alone (302 MB at the headline shape) exceeds the 126 MB L2; the library's "
+                 "own fp32 gradient slabs are meant to stay L2-resident between launches"}
+    cfg.update(extra)
+    return cfg
+
+
 def run_reference(args, w, kind):
-    """The reference arm: the reference's CPU path (torch eager restatement) on the host cores."""
+    """The reference arm: the reference's CPU path (torch eager restatement) on the host cores.
+
+    A step is the whole per-GPU batch when `(steps + warmup)` such steps fit the time budget
+    (`--reference-seconds`, 300 by default); otherwise every step is the first `sampled_rows` rows of
+    the batch and `ms_per_step` is scaled up to the whole batch, and the line says so."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    per_step_budget = 20.0 / max(1, args.steps + args.warmup)
     chunk = 256
     from oracle import torch_reference as tref
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
     probe = make_inputs(w, "cpu", rows=chunk)
     weight = probe["weight"]
+    tref.chunked_loss_and_grads(kind, probe["indices"], weight, probe["vals"], probe["bias"], probe["target"], chunk_rows=chunk)
     t0 = time.perf_counter()
     tref.chunked_loss_and_grads(kind, probe["indices"], weight, probe["vals"], probe["bias"], probe["target"], chunk_rows=chunk)
     per_chunk = time.perf_counter() - t0
-    rows = chunk * max(1, int(per_step_budget / per_chunk))
-    rows = min(rows, w.B)
+    n_steps = max(1, args.steps + args.warmup)
+    chunks_whole = (w.B + chunk - 1) // chunk
+    if per_chunk * chunks_whole * n_steps <= args.reference_seconds:
+        rows = w.B
+    else:
+        rows = min(w.B, chunk * max(1, int(args.reference_seconds / n_steps / per_chunk)))
     x = make_inputs(w, "cpu", rows=rows, with_weight=False)
     times = []
     for i in range(args.warmup + args.steps):
@@ -152,14 +183,17 @@ def run_reference(args, w, kind):
             times.append(r["seconds"])
     sec = sum(times) / len(times)
     value = rows / sec
-    sample = f"each step = first {rows} of {w.B} rows per GPU-equivalent, {chunk}-row chunks, {cores} threads"
+    whole = rows == w.B
+    sample = (f"each step = all {w.B} rows" if whole else f"each step = first {rows} of {w.B} rows") + \
+             f" in {chunk}-row chunks, {cores} threads, torch {torch.__version__} eager ops of the reference loss"
     line = {
         "impl": "reference", "metric": "hier_topk_fwd_bwd_throughput" if kind == "hier" else "topk_fwd_bwd_throughput",
         "value": value, "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": w.B / value * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "kind": kind, "B_per_gpu": w.B, "K": w.K, "F": w.F, "D": w.D,
-                   "storage": w.weight_dtype, "note": "ms_per_step extrapolated from the sampled rows to B rows"},
+        "config": workload_config(w, kind, w.B, w.B * max(1, args.gpus), max(1, args.gpus), args.dweight_mode),
+        "sampled_rows": None if whole else rows,
+        "note": None if whole else "ms_per_step is scaled from the sampled rows to the whole batch",
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -177,6 +211,10 @@ def main():
     ap.add_argument("--kind", default="hier", choices=["hier", "topk"])
     ap.add_argument("--dweight-mode", default="atomic", choices=["atomic", "deterministic"])
     ap.add_argument("--cpu-seconds", type=float, default=15.0, help="CPU-baseline sample budget (0 = skip)")
+    ap.add_argument("--reference-seconds", type=float, default=300.0,
+                    help="--impl reference: time budget of the whole run; whole batches per step if they fit")
+    ap.add_argument("--topk-steps", type=int, default=-1,
+                    help="steps of the extra TopK leg that gives hier_topk_ratio (0 = skip; default: min(steps, 50))")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = same as --steps")
     ap.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
                     help="weak: every rank keeps the workload's B rows; strong: the workload's B rows are split over "
@@ -205,13 +243,21 @@ def main():
     from flexsae_b200 import distributed as fd
     from flexsae_b200 import losses
 
+    def env_flag(name, default):
+        return os.environ.get(name, "1" if default else "0") != "0"
+
     fx.config.dweight_mode = args.dweight_mode
-    fd.config.use_multicast = os.environ.get("FLEXSAE_MULTICAST", "0") != "0"
-    fd.config.peer_reduce = os.environ.get("FLEXSAE_PEER_REDUCE", "1") != "0"
-    fd.config.symmetric_dweight = os.environ.get("FLEXSAE_SYMMETRIC_DWEIGHT", "0") != "0"
+    fd.config.use_multicast = env_flag("FLEXSAE_MULTICAST", False)
+    fd.config.peer_reduce = env_flag("FLEXSAE_PEER_REDUCE", True)
+    # the measured-best exchange settings of a batch-sharded run (see SHARDED_DEFAULTS) unless overridden
+    fd.config.symmetric_dweight = env_flag("FLEXSAE_SYMMETRIC_DWEIGHT", distributed and SHARDED_DEFAULTS["symmetric_dweight"])
+    fd.config.fused_small_reduce = env_flag("FLEXSAE_FUSED_SMALL_REDUCE", distributed and SHARDED_DEFAULTS["fused_small_reduce"])
+    options = dict(SHARDED_DEFAULTS["options"]) if distributed else {}
     for item in filter(None, os.environ.get("FLEXSAE_OPTIONS", "").split(",")):   # e.g. "lanes_bwd=8,segments=2"
         name, value = item.split("=")
-        nv.set_option(name, int(value))
+        options[name] = int(value)
+    for name, value in options.items():
+        nv.set_option(name, value)
     scaling = args.scaling if args.scaling != "auto" else ("strong" if w.name == "c5" else "weak")
     if scaling == "strong":
         if w.B % world:
@@ -228,27 +274,25 @@ def main():
     vals = x["vals"].requires_grad_(True)
     indices, target = x["indices"], x["target"]
 
-    if distributed:
-        sharded = fd.sharded_hierarchical_sae_loss if kind == "hier" else fd.sharded_topk_sae_loss
+    def loss_function(which):
+        if distributed:
+            sharded = fd.sharded_hierarchical_sae_loss if which == "hier" else fd.sharded_topk_sae_loss
+            return lambda i, wt, v, b, t: sharded(i, wt, v, b, t, global_rows=global_rows)
+        return fx.triton_hierarchical_sae_loss if which == "hier" else fx.triton_topk_sae_loss
 
-        def loss_fn(i, wt, v, b, t):
-            return sharded(i, wt, v, b, t, global_rows=global_rows)
-    else:
-        loss_fn = fx.triton_hierarchical_sae_loss if kind == "hier" else fx.triton_topk_sae_loss
-
+    loss_fn = loss_function(kind)
     ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
-    marks = []
 
-    def step(record=False):
+    def step(fn=None, marks=None):
         weight.grad = vals.grad = bias.grad = None
-        if record:
+        if marks is not None:
             e0, e1, e2 = ev(), ev(), ev()
             e0.record()
-        loss = loss_fn(indices, weight, vals, bias, target)
-        if record:
+        loss = (fn or loss_fn)(indices, weight, vals, bias, target)
+        if marks is not None:
             e1.record()
         loss.backward()
-        if record:
+        if marks is not None:
             e2.record()
             marks.append((e0, e1, e2))
         return loss
@@ -259,7 +303,7 @@ def main():
         torch.cuda.synchronize(dev)
 
     def kernels_ok() -> bool:
-        """False (on every rank) if a bounded wait inside a backward kernel gave up on any rank."""
+        """False (on every rank) if a bounded wait inside a kernel gave up on any rank."""
         try:
             losses.check_status(dev)
             ok = 1
@@ -271,42 +315,84 @@ def main():
             ok = int(t.item())
         return bool(ok)
 
-    dweight_sum = "in the backward kernel over peer memory" if distributed and fd.config.peer_reduce else \
+    def timed(fn, n):
+        """n steps between two events; returns (ms per step, per-step (fwd, bwd, whole) ms lists), max over ranks."""
+        marks = []
+        start, stop = ev(), ev()
+        start.record()
+        for _ in range(n):
+            step(fn, marks)
+        stop.record()
+        barrier()
+        total = start.elapsed_time(stop)
+        fwd = [a.elapsed_time(b) for a, b, _ in marks]
+        bwd = [b.elapsed_time(c) for _, b, c in marks]
+        whole = [a.elapsed_time(c) for a, _, c in marks]
+        stats = [total / n, sum(fwd) / n, sum(bwd) / n, statistics.median(whole), min(whole)]
+        if distributed:
+            t = torch.tensor(stats, device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            stats = [float(v) for v in t]
+        return stats
+
+    # ---- several ranks: the fused cross-GPU gradient sum against the plain collective, same inputs ----
+    parity = None
+    fused_exchange = distributed and fd.config.peer_reduce and args.dweight_mode == "atomic"
+    if fused_exchange:
+        def one_step_grads():
+            loss = step()
+            torch.cuda.synchronize(dev)
+            out = (float(loss), weight.grad.float().clone(), bias.grad.float().clone(), vals.grad.float().clone())
+            weight.grad = vals.grad = bias.grad = None
+            return out
+
+        saved_small = fd.config.fused_small_reduce
+        fd.config.peer_reduce, fd.config.fused_small_reduce = False, False
+        ref_loss, ref_dw, ref_db, ref_dv = one_step_grads()         # per-rank kernels + NCCL all-reduce
+        fd.config.peer_reduce, fd.config.fused_small_reduce = True, saved_small
+        got_loss, got_dw, got_db, got_dv = one_step_grads()         # the path that is timed below
+        scale = float(ref_dw.abs().max())
+        errs = torch.tensor([abs(got_loss - ref_loss) / abs(ref_loss), float((got_dw - ref_dw).abs().max()) / scale,
+                             float((got_db - ref_db).abs().max()) / float(ref_db.abs().max()),
+                             0.0 if torch.equal(got_dv, ref_dv) else 1.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(errs, op=dist.ReduceOp.MAX)
+        parity = {"against": "per-rank kernels + NCCL all-reduce of dweight, dbias and loss, same inputs",
+                  "loss_rel": float(errs[0]), "dweight_rel_of_max": float(errs[1]), "dbias_rel_of_max": float(errs[2]),
+                  "dvals_bit_equal": float(errs[3]) == 0.0}
+        del ref_dw, got_dw
+        ok = kernels_ok() and parity["loss_rel"] < 1e-5 and parity["dweight_rel_of_max"] < 1e-2 and \
+            parity["dbias_rel_of_max"] < 1e-2 and parity["dvals_bit_equal"]
+        if not ok:
+            raise SystemExit(f"bench.py: the fused cross-GPU gradient sum disagrees with the NCCL all-reduce: {parity}; "
+                             "no number is reported")
+
+    dweight_sum = "in the backward kernel over peer memory" if fused_exchange else \
                   ("NCCL all-reduce after the backward" if distributed else "none (one GPU)")
     for _ in range(args.warmup):
         step()
     barrier()
     if not kernels_ok():
-        if not (distributed and fd.config.peer_reduce):
-            raise SystemExit("bench.py: a backward kernel reported a timed-out wait during warm-up; no number is reported")
-        # the peer-memory exchange did not complete on this machine: measure with the plain collective
-        fd.config.peer_reduce = False
-        dweight_sum = "NCCL all-reduce after the backward (the peer-memory exchange timed out during warm-up)"
-        for _ in range(args.warmup):
-            step()
-        barrier()
-        if not kernels_ok():
-            raise SystemExit("bench.py: a backward kernel reported a timed-out wait during warm-up; no number is reported")
+        raise SystemExit("bench.py: a kernel reported a timed-out wait during warm-up; no number is reported")
     losses.launch_count = 0
     with ClockSampler(local_rank) as clocks:
-        start, stop = ev(), ev()
-        start.record()
-        for _ in range(args.steps):
-            step(record=True)
-        stop.record()
-        barrier()
+        ms_per_step, fwd_ms, bwd_ms, median_ms, min_ms = timed(loss_fn, args.steps)
     launches = losses.launch_count
     if not kernels_ok():
-        raise SystemExit("bench.py: a backward kernel reported a timed-out wait inside the timed region; no number is reported")
-    elapsed_ms = start.elapsed_time(stop)
-    fwd_ms = sum(a.elapsed_time(b) for a, b, _ in marks) / len(marks)
-    bwd_ms = sum(b.elapsed_time(c) for _, b, c in marks) / len(marks)
-    if distributed:
-        t = torch.tensor([elapsed_ms, fwd_ms, bwd_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, fwd_ms, bwd_ms = (float(v) for v in t)
-    ms_per_step = elapsed_ms / args.steps
+        raise SystemExit("bench.py: a kernel reported a timed-out wait inside the timed region; no number is reported")
     value = global_rows / (ms_per_step * 1e-3)
+
+    # ---- the other loss on the same inputs: the Hierarchical / TopK step-time ratio -----------------
+    other = None
+    other_steps = min(args.steps, 50) if args.topk_steps < 0 else args.topk_steps
+    if other_steps > 0:
+        other_kind = "topk" if kind == "hier" else "hier"
+        other_fn = loss_function(other_kind)
+        for _ in range(max(3, min(args.warmup, 10))):
+            step(other_fn)
+        barrier()
+        o = timed(other_fn, other_steps)
+        if kernels_ok():
+            other = {"kind": other_kind, "ms_per_step": o[0], "fwd_ms": o[1], "bwd_ms": o[2], "steps": other_steps}
 
     # ---- end to end: host inputs in, loss out, every step ------------------------------------
     e2e_steps = args.e2e_steps or args.steps
@@ -316,6 +402,8 @@ def main():
     bufs = [{k: torch.empty_like(x[k].detach()) for k in host} for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_there = [torch.cuda.Event() for _ in range(2)]
 
     def upload(slot):
         with torch.cuda.stream(copy_stream):
@@ -325,10 +413,13 @@ def main():
             ready[slot].record(copy_stream)
 
     def e2e_loop(n):
+        """Every step: its inputs come from pinned host memory (uploaded while the previous step
+        computes) and its loss goes back to the host, where it is read one step later so that the
+        host can already enqueue the next step."""
         for c in consumed:
             c.record()
         upload(0)
-        last = 0.0
+        seen = []
         for i in range(n):
             slot = i & 1
             if i + 1 < n:
@@ -339,17 +430,26 @@ def main():
             loss = loss_fn(bufs[slot]["indices"], weight, v, bias, bufs[slot]["target"])
             loss.backward()
             consumed[slot].record()
-            last = loss.item()                        # device -> host read of the step's result
-        return last
+            if i >= 2:                                # the buffer about to be overwritten: read it first
+                loss_there[slot].synchronize()
+                seen.append(float(loss_host[slot][0]))
+            loss_host[slot].copy_(loss.detach().reshape(1), non_blocking=True)    # device -> host read of the step's result
+            loss_there[slot].record()
+        for i in range(max(0, n - 2), n):
+            loss_there[i & 1].synchronize()
+            seen.append(float(loss_host[i & 1][0]))
+        return seen
 
     e2e_loop(min(5, e2e_steps))
     barrier()
     t0 = time.perf_counter()
-    e2e_loop(e2e_steps)
+    seen = e2e_loop(e2e_steps)
     barrier()
     e2e_s = time.perf_counter() - t0
     if not kernels_ok():
-        raise SystemExit("bench.py: a backward kernel reported a timed-out wait in the end-to-end loop; no number is reported")
+        raise SystemExit("bench.py: a kernel reported a timed-out wait in the end-to-end loop; no number is reported")
+    if len(seen) != e2e_steps or not all(v == v and v > 0 for v in seen):
+        raise SystemExit("bench.py: the end-to-end loop did not read a valid loss for every step")
     if distributed:
         t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -360,35 +460,56 @@ def main():
         peak, peak_kind = hbm_peak()
         alg = algorithmic_bytes(w)                        # per GPU per step
         sw = 2 if w.weight_dtype != "float32" else 4
-        # backward launches of the dominant kernel: one per column piece (+ one conversion-only)
+        # the backward's share of the algorithmic bytes: second row gather + fp32 scatter payload,
+        # dense table (clear + conversion), saved state, indices / vals / dvals
         alg_bwd = (rows * w.K * w.D * (sw + 4) + w.F * w.D * (4 + (4 + sw if sw != 4 else 0))
                    + rows * w.D * 4 + rows * w.K * (8 + 4 + 4))
+        if args.dweight_mode == "deterministic":
+            dominant = "decoder_loss_bwd_kernel<DET> + ordered_sum_items_kernel (one pair of launches per column piece)"
+        elif distributed and fused_exchange:
+            dominant = "decoder_loss_bwd_sharded_kernel (one launch per backward)"
+        else:
+            dominant = "decoder_loss_bwd_pipelined_kernel (one launch per backward)"
+        default_build = not distributed and not os.environ.get("FLEXSAE_OPTIONS")
         line = {
             "metric": "hier_topk_fwd_bwd_throughput" if kind == "hier" else "topk_fwd_bwd_throughput",
             "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "ms_per_step": ms_per_step, "ms_per_step_median": median_ms, "ms_per_step_min": min_ms,
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "config": {"workload": w.name, "kind": kind, "B_per_gpu": rows, "global_B": global_rows, "K": w.K,
-                       "F": w.F, "D": w.D, "storage": f"{w.weight_dtype} weight/bias/target, {w.vals_dtype} vals",
-                       "accumulate": "fp32", "dweight_mode": args.dweight_mode,
-                       "parallelism": f"batch-sharded x{world}, decoder replicated" if distributed else "single GPU",
-                       "dweight_sum": dweight_sum,
-                       "l2": "no flush: the decoder (302 MB at the headline shape) exceeds the 126 MB L2; the "
-                             "library's own fp32 gradient slabs are meant to stay L2-resident between launches"},
+            "config": workload_config(w, kind, rows, global_rows, world, args.dweight_mode),
+            "exchange": {"dweight_sum": dweight_sum,
+                         "loss_and_dbias_sum": ("flexsae_small_allreduce (one launch each, peer memory)"
+                                                if distributed and fd.config.fused_small_reduce else
+                                                ("NCCL all-reduce" if distributed else "none (one GPU)")),
+                         "symmetric_dweight": bool(distributed and fd.config.symmetric_dweight),
+                         "options": options},
             "hbm_gbs": alg / (ms_per_step * 1e-3) / 1e9,
             "fwd_ms": fwd_ms, "bwd_ms": bwd_ms,
-            "roofline": {"bound": "hbm", "kernel": "decoder_loss_bwd_pipelined_kernel (one launch per backward) + its two finalising kernels",
+            "roofline": {"bound": "hbm", "kernel": dominant,
                          "achieved": alg_bwd / (bwd_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
                          "frac": alg_bwd / (bwd_ms * 1e-3) / 1e9 / peak, "peak_source": peak_kind,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((w.name, kind, args.dweight_mode))},
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((w.name, kind, args.dweight_mode)) if default_build else None,
+                         "note": "achieved = the backward's algorithmic bytes / its CUDA-event time (bwd_ms, which also "
+                                 "covers the two small finalising kernels); gathers and fp32 reductions are served by "
+                                 "L2, so DRAM traffic is far below the algorithmic bytes and the binding resource is "
+                                 "the L2 reduction rate (5.7 TB/s measured for red.global.add.v4.f32), not HBM"},
             "roofline_step": {"bound": "hbm", "achieved": alg / (ms_per_step * 1e-3) / 1e9, "peak": peak,
                               "unit": "GB/s", "frac": alg / (ms_per_step * 1e-3) / 1e9 / peak,
                               "algorithmic_bytes": alg},
             "e2e": {"value": e2e_value, "unit": "rows/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                    "ms_per_step": e2e_s / e2e_steps * 1e3},
+                    "ms_per_step": e2e_s / e2e_steps * 1e3, "steps": e2e_steps},
             "gpu_launches": launches,
             "clocks": clocks.summary(),
         }
+        if other is not None:
+            hier_ms, topk_ms = (ms_per_step, other["ms_per_step"]) if kind == "hier" else (other["ms_per_step"], ms_per_step)
+            line["hier_ms"], line["topk_ms"] = hier_ms, topk_ms
+            line["hier_topk_ratio"] = hier_ms / topk_ms
+            line["other_loss"] = other
+        if parity is not None:
+            line["parity_checked"] = True
+            line["parity"] = parity
         if world == 1 and args.cpu_seconds > 0:
             line["cpu_baseline"] = cpu_reference_rate(w, kind, args.cpu_seconds)
         print(json.dumps(line), flush=True)

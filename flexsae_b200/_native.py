@@ -1,6 +1,10 @@
 """ctypes binding of ``libflexsae_b200.so`` (declared in ``include/flexsae_b200.h``).
 
 There is no fallback: if the library is missing or a call is rejected, an exception is raised.
+
+Environment: ``FLEXSAE_LIB`` (path of a library built elsewhere), ``FLEXSAE_NO_BUILD=1`` (never invoke
+nvcc), ``FLEXSAE_OPTIONS="name=value,..."`` (``flexsae_set_option`` calls made once when the library is
+loaded, e.g. ``wait_limit_ms=60000`` for a job whose ranks may drift far apart).
 """
 from __future__ import annotations
 
@@ -42,6 +46,8 @@ SIGNATURES = {
     "flexsae_topk_select": (_c_int, [_c_vp, _c_int, _c_i64, _c_i64, _c_i64, _c_int, _c_vp, _c_int, _c_vp, _c_vp]),
     "flexsae_small_allreduce_bytes": (_c_int, [_c_int, _c_i64, _c_vp]),
     "flexsae_small_allreduce": (_c_int, [_c_vp, _c_vp, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_i64, _c_vp, _c_vp]),
+    "flexsae_sort_workspace_bytes": (_c_sz, [_c_i64, _c_i64]),
+    "flexsae_sort_by_decoder_row": (_c_int, [_c_vp, _c_i64, _c_i64, _c_vp, _c_sz, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
     "flexsae_loss_fwd_static_scratch": (_c_int, [_c_int] + [_c_vp] * 7 + [_c_int] + [_c_i64] * 4 + [_c_int] * 4
                                         + [_c_dbl, _c_vp, _c_vp]),
     "flexsae_loss_bwd": (_c_int, [_c_int] + [_c_vp] * 4 + [_c_int] + [_c_vp] * 5 + [_c_sz] + [_c_i64] * 4
@@ -83,6 +89,9 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
     _lib = lib
+    for item in filter(None, os.environ.get("FLEXSAE_OPTIONS", "").split(",")):
+        name, _, value = item.partition("=")
+        check(lib.flexsae_set_option(name.strip().encode(), int(value)), f"FLEXSAE_OPTIONS: {item}")
     return lib
 
 

@@ -280,8 +280,8 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
 //   converting blocks of piece q wait until all unit blocks of piece q have finished;
 //   unit blocks of piece p wait until piece p-2 (same slab) has been converted and cleared.
 // Every wait is on blocks with LOWER role indices, which start first (see role_index), so the
-// lowest unfinished block never waits on anything unfinished.  Waits are bounded: after
-// kSpinLimit polls a block gives up, sets FLEXSAE_STATUS_PIPELINE_TIMEOUT and carries on (the
+// lowest unfinished block never waits on anything unfinished.  Waits are bounded in time (see
+// BoundedWait): a block that gives up sets FLEXSAE_STATUS_PIPELINE_TIMEOUT and carries on (the
 // result is then invalid but the GPU is not held).
 struct PipeArgs {
   BwdArgs b;
@@ -290,9 +290,8 @@ struct PipeArgs {
   int* conv_done;  // [pieces]
   int pieces, unit_blocks, conv_blocks, conv_offset;
   int* ticket;  // NULL: blocks take their roles by blockIdx.x; else by the order in which they start
+  long long wait_ns;  // how long one wait may last before the block gives up (option "wait_limit_ms")
 };
-
-constexpr int kSpinLimit = 1000000;  // polls of >= 0.2 us each: a fraction of a second
 
 __device__ __forceinline__ int ld_acquire(const int* p) {
   int v;
@@ -300,19 +299,43 @@ __device__ __forceinline__ int ld_acquire(const int* p) {
   return v;
 }
 
-__device__ __forceinline__ void wait_count(const int* ctr, int target, int32_t* status) {
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// The bound of every polling loop in this library, in wall-clock time on the GPU's nanosecond
+// timer (a poll count would make the limit depend on clock speed and on how long a poll takes
+// across NVLink).  Every 64th poll looks at the timer and at the status word; the first look
+// sets the deadline.  give_up() answers true when the deadline has passed or when another block
+// has already given up (then nobody waits any more and the launch drains quickly), and records
+// FLEXSAE_STATUS_PIPELINE_TIMEOUT.
+struct BoundedWait {
+  unsigned long long deadline = 0;
+  int polls = 0;
+  __device__ __forceinline__ bool give_up(int32_t* status, long long limit_ns) {
+    if ((++polls & 63) != 0) return false;
+    const unsigned long long now = global_ns();
+    if (deadline == 0) {
+      deadline = now + (unsigned long long)limit_ns;
+      return false;
+    }
+    const bool abandoned = status && (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+    if (now > deadline || abandoned) {
+      if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
+      return true;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ void wait_count(const int* ctr, int target, int32_t* status, long long wait_ns) {
   if (threadIdx.x == 0) {
-    int spins = 0;
+    BoundedWait bw;
     while (ld_acquire(ctr) < target) {
       __nanosleep(200);
-      ++spins;
-      // once any block has given up, nobody waits any more: the launch drains quickly
-      const bool abandoned = status && (spins & 1023) == 0 &&
-                             (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-      if (spins > kSpinLimit || abandoned) {
-        if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-        break;
-      }
+      if (bw.give_up(status, wait_ns)) break;
     }
   }
   __syncthreads();
@@ -355,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
   if (conv_idx >= 0) {
     const int q = p - 1;
     if (q < 0) return;
-    wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status);
+    wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status, pa.wait_ns);
     convert_slab<T, G, true>(pa.slabs[q & 1], pa.b.dweight, pa.b.F, pa.b.D, q, conv_idx, pa.conv_blocks);
     signal_done(pa.conv_done + q);
     return;
@@ -367,7 +390,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
                                   smem);
     return;
   }
-  if (p >= 2) wait_count(pa.conv_done + (p - 2), pa.conv_blocks, pa.b.status);
+  if (p >= 2) wait_count(pa.conv_done + (p - 2), pa.conv_blocks, pa.b.status, pa.wait_ns);
   walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
   signal_done(pa.walk_done + p);
 }
@@ -414,7 +437,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   const int p = bid / pa.unit_blocks;
   if (p >= pa.pieces) {  // tail: the last two pieces have no later unit blocks to convert them
     for (int q = max(0, pa.pieces - 2); q < pa.pieces; q++) {
-      wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status);
+      wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status, pa.wait_ns);
       take_chunks<T, G>(sa, q, 0x7fffffff, &s_chunk);
     }
     return;
@@ -426,9 +449,9 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
     const bool converted = s_state != 0;
     __syncthreads();
     if (!converted) {  // this block's slab still holds piece p-2: help, then wait for the chunks in other hands
-      wait_count(pa.walk_done + (p - 2), pa.unit_blocks, pa.b.status);
+      wait_count(pa.walk_done + (p - 2), pa.unit_blocks, pa.b.status, pa.wait_ns);
       take_chunks<T, G>(sa, p - 2, 0x7fffffff, &s_chunk);
-      wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status);
+      wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status, pa.wait_ns);
     }
   }
   walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);

@@ -49,6 +49,7 @@ struct Options {
   int convert_steal = 0;        // single-launch backward: slab conversion taken in chunks by whichever blocks run
   int steal_chunks = 1024;      // ... chunks per slab
   int steal_exit_chunks = 1;    // ... chunks a unit block takes after its walk
+  int wait_limit_ms = 5000;     // how long one in-kernel wait (for other blocks, for other GPUs) may last
 };
 static Options g_opt;
 
@@ -93,6 +94,10 @@ static int check_shape(int kind, const Shape& s, int wdt) {
     return fail(FLEXSAE_EUNSUPPORTED, "D=%lld must be a multiple of %d (16-byte row pieces)", (long long)s.D, vec);
   if (s.F > (1ll << 30) || s.D > (1ll << 20) || s.B > (1ll << 27) || s.B * s.K > (1ll << 31) - 1)
     return fail(FLEXSAE_EUNSUPPORTED, "shape too large for 32-bit row/position arithmetic");
+  // decoder rows are addressed in 16-byte units held in 32 bits: the table must stay below 2^36 bytes (64 GiB)
+  if ((double)s.F * (double)s.D * (double)dtype_size(wdt) >= 68719476736.0)
+    return fail(FLEXSAE_EUNSUPPORTED, "decoder of %lld x %lld elements is 64 GiB or more: beyond the 32-bit row-piece offsets",
+                (long long)s.F, (long long)s.D);
   // 8 (+4 in deterministic mode) bytes per (unit, step) are staged in shared memory next to the
   // 32 KiB row-piece ring: 16 units * K * 12 bytes must fit
   if (s.K > 960) return fail(FLEXSAE_EUNSUPPORTED, "K=%lld above the supported maximum of 960", (long long)s.K);
@@ -292,6 +297,7 @@ static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* s
   pa.conv_done = counters + pieces;
   pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
+  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
   const long long items = (long long)b.F * G;
@@ -324,6 +330,7 @@ static cudaError_t launch_bwd_stealing(const BwdArgs& b, float* slab0, float* sl
   sa.claim = counters + 2 * pieces + 3;
   pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
+  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
   pa.conv_blocks = pa.conv_offset = 0;
@@ -359,6 +366,7 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   sa.chunks = sa.exit_chunks = sa.tail_blocks = 0;
   pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
+  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
   const long long items = (long long)b.F * G;
@@ -398,6 +406,7 @@ static cudaError_t launch_bwd_sharded_stealing(const BwdArgs& b, float* slab0, f
   sa.claim = counters + 3 * pieces + 6;      // next chunk per piece
   pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
   pa.pieces = pieces;
+  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
   const long long units = (long long)b.B * b.NS;
   pa.unit_blocks = (int)((units + UPC - 1) / UPC);
   pa.conv_blocks = pa.conv_offset = 0;
@@ -461,6 +470,7 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "flag_fan_out") && (value == 0 || value == 1)) { g_opt.flag_fan_out = (int)value; return 0; }
   if (!strcmp(name, "sharded_convert_blocks") && value >= 0 && value <= 8192) { g_opt.sharded_convert_blocks = (int)value; return 0; }
   if (!strcmp(name, "sharded_convert_offset_pct") && value >= -1 && value <= 100) { g_opt.sharded_convert_offset_pct = (int)value; return 0; }
+  if (!strcmp(name, "wait_limit_ms") && value >= 1 && value <= 600000) { g_opt.wait_limit_ms = (int)value; return 0; }
   return fail(FLEXSAE_EINVAL, "unknown option or value: %s=%lld", name, (long long)value);
 }
 
@@ -483,6 +493,7 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "flag_fan_out")) return g_opt.flag_fan_out;
   if (!strcmp(name, "sharded_convert_blocks")) return g_opt.sharded_convert_blocks;
   if (!strcmp(name, "sharded_convert_offset_pct")) return g_opt.sharded_convert_offset_pct;
+  if (!strcmp(name, "wait_limit_ms")) return g_opt.wait_limit_ms;
   return -1;
 }
 
@@ -859,6 +870,7 @@ int flexsae_small_allreduce(const void* in, void* out, int64_t n, int dtype, int
   a.rank = rank;
   a.seq = seq;
   a.capacity = capacity;
+  a.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
   a.status = status;
   for (int r = 0; r < kMaxRanks; r++) {
     a.buf[r] = r < world ? buf_ptrs[r] : nullptr;
@@ -887,6 +899,32 @@ int flexsae_debug_trace_read(unsigned long long* out, size_t bytes, int clear) {
   return 0;
 }
 #endif
+
+size_t flexsae_sort_workspace_bytes(int64_t n, int64_t F) {
+  if (n < 1 || F < 1 || n > (1ll << 31) - 1 || F > (1ll << 30)) return 0;
+  return det_index_bytes(n, F);
+}
+
+int flexsae_sort_by_decoder_row(const int64_t* indices, int64_t n, int64_t F, void* workspace, size_t workspace_bytes,
+                                int32_t* order, int32_t* slot_of, int32_t* seg_begin, int32_t* item_begin, void* stream) {
+  t_launches = 0;
+  if (n < 1 || F < 1 || n > (1ll << 31) - 1 || F > (1ll << 30))
+    return fail(FLEXSAE_EINVAL, "n = %lld positions / F = %lld decoder rows outside the supported range", (long long)n, (long long)F);
+  if (!indices || !workspace) return fail(FLEXSAE_EINVAL, "null pointer argument");
+  if (!aligned16(workspace)) return fail(FLEXSAE_EINVAL, "workspace must be 16-byte aligned");
+  const size_t need = det_index_bytes(n, F);
+  if (workspace_bytes < need) return fail(FLEXSAE_EWORKSPACE, "sort workspace too small: %zu < %zu bytes", workspace_bytes, need);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  DetIndex ix;
+  cudaError_t e = det_prepare(indices, n, F, reinterpret_cast<char*>(workspace), &ix, st, &t_launches);
+  const size_t nb = (size_t)n * 4, fb = (size_t)(F + 1) * 4;
+  if (e == cudaSuccess && order) e = cudaMemcpyAsync(order, ix.order, nb, cudaMemcpyDeviceToDevice, st);
+  if (e == cudaSuccess && slot_of) e = cudaMemcpyAsync(slot_of, ix.slot_of, nb, cudaMemcpyDeviceToDevice, st);
+  if (e == cudaSuccess && seg_begin) e = cudaMemcpyAsync(seg_begin, ix.seg_begin, fb, cudaMemcpyDeviceToDevice, st);
+  if (e == cudaSuccess && item_begin) e = cudaMemcpyAsync(item_begin, ix.item_begin, fb, cudaMemcpyDeviceToDevice, st);
+  if (e != cudaSuccess) return fail((int)e, "sort launches failed: %s", cudaGetErrorString(e));
+  return 0;
+}
 
 int flexsae_shard_slots(int64_t F, int64_t D, int weight_dtype) {
   Shape s{1, 1, F, D};

@@ -93,16 +93,10 @@ __device__ __forceinline__ void wait_peers(const ShardArgs& sa, bool need_exchan
     int32_t* status = sa.p.b.status;
     const int* flag = sa.flags_at[sa.rank] + kind * kScatterFlags + s;
     const int target = kind == 0 ? exchange_target : scatter_target;
-    int spins = 0;
+    BoundedWait bw;
     while (ld_acquire_sys(flag) - target < 0) {  // difference: robust to wrap-around
       __nanosleep(100);
-      ++spins;
-      const bool abandoned = status && (spins & 1023) == 0 &&
-                             (*reinterpret_cast<volatile int32_t*>(status) & FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-      if (spins > kSpinLimit || abandoned) {
-        if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-        break;
-      }
+      if (bw.give_up(status, sa.p.wait_ns)) break;
     }
   }
   __syncthreads();
@@ -351,14 +345,10 @@ __device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scat
     if (last) __threadfence_system();  // acquire side: what the other blocks did before THEIR count moved
     if (last && !first) {
       const int* own = sa.flags_at[sa.rank] + kind_off + sa.rank;
-      int32_t* status = sa.p.b.status;
-      int spins = 0;
+      BoundedWait bw;
       while (ld_acquire_sys(own) - (sa.seq_base + slot - 1) < 0) {
         __nanosleep(100);
-        if (++spins > kSpinLimit) {
-          if (status) atomicOr(status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-          break;
-        }
+        if (bw.give_up(sa.p.b.status, sa.p.wait_ns)) break;
       }
     }
     s_publish = last;
@@ -451,7 +441,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
     }
   }
   if (unit_block >= 0) {
-    if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status);  // slot p-1 cleared this slab
+    if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status, pa.wait_ns);  // slot p-1 cleared this slab
     FLEXSAE_TRACE_MIN(p, kTrUnitStart);
     walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
     signal_done(pa.walk_done + p);
@@ -461,7 +451,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   if (conv_idx >= 0) {
     FLEXSAE_TRACE_MIN(p, kTrConvEntry);
     if (p >= 1 && p - 1 < P) {
-      wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status);  // the local slab is complete
+      wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status, pa.wait_ns);  // the local slab is complete
       wait_peers(sa, true, sa.seq_base + p - 1, false, 0);  // the owners have reduced what this half of their inbox held
       FLEXSAE_TRACE_MIN(p, kTrConvStart);
       if (sa.mc_inbox) slab_to_own_copy<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
@@ -507,7 +497,7 @@ __device__ __forceinline__ void take_scatter_chunks(const ShardArgs& sa, int q, 
 // wait until piece q may be scattered (its walk is complete, the owners have reduced piece q-2), then take what is left
 template <typename T, int G>
 __device__ __forceinline__ void finish_scatter(const ShardArgs& sa, int q, int* s_chunk) {
-  wait_count(sa.p.walk_done + q, sa.p.unit_blocks, sa.p.b.status);
+  wait_count(sa.p.walk_done + q, sa.p.unit_blocks, sa.p.b.status, sa.p.wait_ns);
   wait_peers(sa, true, sa.seq_base + q, false, 0);
   take_scatter_chunks<T, G>(sa, q, 0x7fffffff, s_chunk);
 }
@@ -555,7 +545,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
       __syncthreads();
       if (!free_slab) {  // this block's slab still holds piece p-2: help, then wait for the chunks in other hands
         finish_scatter<T, G>(sa, p - 2, &s_chunk);
-        wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status);
+        wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status, pa.wait_ns);
       }
     }
     FLEXSAE_TRACE_MIN(p, kTrUnitStart);

@@ -15,6 +15,7 @@ struct SmallReduceArgs {
   void* out;
   int n, dtype, world, rank, seq;
   long long capacity;  // floats per (parity, sender) cell of the exchange buffer
+  long long wait_ns;   // how long the wait for the other ranks may last
   int32_t* status;
   void* buf[kMaxRanks];  // rank o's buffer: flags, then float data[2][world][capacity]
 };
@@ -37,13 +38,10 @@ __global__ void __launch_bounds__(kSmallThreads) small_allreduce_kernel(const Sm
     st_release_sys(reinterpret_cast<int*>(a.buf[threadIdx.x]) + a.rank, a.seq);
   if ((int)threadIdx.x < a.world) {
     const int* flag = reinterpret_cast<const int*>(a.buf[a.rank]) + threadIdx.x;
-    int spins = 0;
+    BoundedWait bw;
     while (ld_acquire_sys(flag) - a.seq < 0) {
       __nanosleep(100);
-      if (++spins > kSpinLimit) {
-        if (a.status) atomicOr(a.status, FLEXSAE_STATUS_PIPELINE_TIMEOUT);
-        break;
-      }
+      if (bw.give_up(a.status, a.wait_ns)) break;
     }
   }
   __syncthreads();

@@ -33,7 +33,11 @@ struct SelKey;
 template <>
 struct SelKey<float> {
   static constexpr int BYTES = 4;
-  __device__ __forceinline__ static uint32_t key(uint32_t u) { return (u & 0x80000000u) ? ~u : (u | 0x80000000u); }
+  __device__ __forceinline__ static uint32_t key(uint32_t u) {
+    if ((u & 0x7fffffffu) > 0x7f800000u) return 0xffffffffu;  // NaN of either sign: above everything, like torch.topk
+    if (u == 0x80000000u) u = 0u;                             // -0.0 ranks with +0.0 (they compare equal)
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  }
   __device__ __forceinline__ static float value(uint32_t k) {
     return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k);
   }
@@ -41,7 +45,11 @@ struct SelKey<float> {
 template <>
 struct SelKey<__nv_bfloat16> {
   static constexpr int BYTES = 2;
-  __device__ __forceinline__ static uint32_t key(uint32_t h) { return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u); }
+  __device__ __forceinline__ static uint32_t key(uint32_t h) {
+    if ((h & 0x7fffu) > 0x7f80u) return 0xffffu;  // NaN of either sign: above everything, like torch.topk
+    if (h == 0x8000u) h = 0u;                     // -0.0 ranks with +0.0
+    return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+  }
   __device__ __forceinline__ static float value(uint32_t k) {
     const uint32_t h = (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
     return __uint_as_float(h << 16);
@@ -50,7 +58,11 @@ struct SelKey<__nv_bfloat16> {
 template <>
 struct SelKey<__half> {
   static constexpr int BYTES = 2;
-  __device__ __forceinline__ static uint32_t key(uint32_t h) { return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u); }
+  __device__ __forceinline__ static uint32_t key(uint32_t h) {
+    if ((h & 0x7fffu) > 0x7c00u) return 0xffffu;  // NaN of either sign: above everything
+    if (h == 0x8000u) h = 0u;                     // -0.0 ranks with +0.0
+    return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+  }
   __device__ __forceinline__ static float value(uint32_t k) {
     const uint32_t h = (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
     return __half2float(__ushort_as_half((unsigned short)h));
@@ -196,7 +208,7 @@ __global__ void __launch_bounds__(kSelThreads, 1) topk_select_kernel(const Selec
   // ---- 1. pre-filter.  The K-th largest of the per-thread maxima is a lower bound of the K-th
   // largest element (the K largest maxima are K different elements), and for K << F it is so tight
   // that barely more than K elements reach it.
-  uint32_t mine = 0;  // key 0 is below every real key
+  uint32_t mine = 0;  // key 0 is below every real key: the lowest one, that of -inf, is still positive
   for (int v = tid; v < nvec; v += kSelThreads) {
     uint32_t k[VEC];
     vector_keys<T>(CACHED ? src[v] : __ldg(src + v), k);
@@ -340,7 +352,7 @@ __global__ void __launch_bounds__(kSelThreads, 1) topk_select_kernel(const Selec
   for (int i = tid; i < a.K; i += kSelThreads) {
     const unsigned long long e = sorted[i];
     float val = SelKey<T>::value((uint32_t)(e >> 32));
-    if (a.relu) val = fmaxf(val, 0.f);
+    if (a.relu) val = val < 0.f ? 0.f : val;  // a NaN stays a NaN (fmaxf would hide it)
     store_scalar(a.vals, a.vals_dtype, (size_t)blockIdx.x * a.K + i, val);
     a.indices[(size_t)blockIdx.x * a.K + i] = (int64_t)(uint32_t)~(uint32_t)e;
   }

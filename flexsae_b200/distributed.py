@@ -5,12 +5,22 @@ The reference is single-GPU.  Here every rank holds a shard of the batch rows
 Each rank runs the ordinary fused kernels on its rows with the GLOBAL normaliser
 1/(B_global*D) resp. 1/(B_global*K*D), so its loss is its additive share of the global mean and
 its gradients are its additive share of the global gradients.  The scalar loss and ``dbias`` (D
-values) are all-reduced with NCCL.  The dense ``dweight`` table is summed over the ranks INSIDE the
-backward kernel: its converting blocks reduce-scatter and all-gather each finished column piece over
-NVLink peer loads while the next pieces are still being accumulated
-(``flexsae_loss_bwd_sharded``), so no separate all-reduce of the [F, D] gradient is exposed.
-``config.peer_reduce = False`` falls back to an NCCL all-reduce of ``dweight`` after the backward.
-``dvals`` belongs to the local rows and needs no exchange.
+values) are summed over the ranks by NCCL or, with ``config.fused_small_reduce``, by the library's own
+single-launch exchange.  The dense ``dweight`` table is summed over the ranks INSIDE the backward
+kernel: its converting blocks push each finished column piece to the ranks that own its rows and the
+owners push the reduced rows back, all as posted NVLink peer STORES (no remote loads), while the next
+pieces are still being accumulated (``flexsae_loss_bwd_sharded``), so no separate all-reduce of the
+[F, D] gradient is exposed.  ``config.peer_reduce = False`` falls back to an NCCL all-reduce of
+``dweight`` after the backward.  ``dvals`` belongs to the local rows and needs no exchange.
+
+The in-kernel exchange makes the ranks wait for one another on the GPU, with a time limit
+(``flexsae_set_option("wait_limit_ms")``, 5 s by default).  A rank whose backward is enqueued later
+than that after the others' makes them give up: they set ``FLEXSAE_STATUS_PIPELINE_TIMEOUT`` in their
+status word and their gradients of that step are INVALID.  The sharded losses look at the status word
+of the previous step at the start of every call (an asynchronous copy to pinned memory, no
+synchronisation) and raise ``RuntimeError`` when the bit is set, so a bad step is reported one step
+late at the latest; ``flexsae_b200.check_status()`` reports it at once, at the price of a
+synchronisation.
 """
 from __future__ import annotations
 
@@ -57,6 +67,7 @@ class PeerExchange:
         import torch.distributed._symmetric_memory as symm_mem
 
         lib = nv.load()
+        self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         wdt = nv.DTYPE_CODES[dtype]
@@ -75,6 +86,7 @@ class PeerExchange:
         self.x = arr(*ptrs)
         self.y = arr(*[p + xb.value for p in ptrs])
         self.flags = arr(*[p + xb.value + yb.value for p in ptrs])
+        self.flag_words = self.buffer[xb.value + yb.value:xb.value + yb.value + fb.value]
         mc = 0
         if config.use_multicast:
             try:
@@ -103,10 +115,26 @@ class PeerExchange:
                                "flexsae_b200.distributed.config.symmetric_dweight = False")
         return self.dweight.view(self.dweight.shape), self.dweight_ptrs
 
+    #: the flag values count up from call to call as C ints; long before they would overflow, all
+    #: ranks start again from 1 on zeroed flags
+    SEQ_RESTART = (1 << 31) - (1 << 20)
+
     def next_seq(self) -> int:
+        if self.seq + 2 * self.slots >= self.SEQ_RESTART:
+            self._restart()
         seq = self.seq
         self.seq += self.slots
         return seq
+
+    def _restart(self) -> None:
+        """Collective (every rank gets here at the same call, because all ranks count alike): nobody is
+        inside a kernel that uses the flags, then zero them and count from 1 again."""
+        torch.cuda.synchronize(self.buffer.device)
+        dist.barrier(self.group)
+        self.flag_words.zero_()
+        torch.cuda.synchronize(self.buffer.device)
+        dist.barrier(self.group)
+        self.seq = 1
 
 
 def _storage_refs(t: torch.Tensor) -> int:
@@ -155,6 +183,7 @@ class SmallExchange:
         import torch.distributed._symmetric_memory as symm_mem
 
         lib = nv.load()
+        self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         nbytes = ctypes.c_size_t()
@@ -175,6 +204,13 @@ class SmallExchange:
             raise ValueError("SmallExchange.all_reduce_ takes a contiguous fp32/bf16/fp16 CUDA tensor of at most "
                              f"{self.CAPACITY} values")
         lib = nv.load()
+        if self.seq >= PeerExchange.SEQ_RESTART:      # same collective restart as PeerExchange._restart
+            torch.cuda.synchronize(t.device)
+            dist.barrier(self.group)
+            self.buffer.zero_()
+            torch.cuda.synchronize(t.device)
+            dist.barrier(self.group)
+            self.seq = 0
         self.seq += 1
         with torch.cuda.device(t.device):
             rc = lib.flexsae_small_allreduce(t.data_ptr(), t.data_ptr(), t.numel(), nv.DTYPE_CODES[t.dtype], self.world,
@@ -215,6 +251,44 @@ def _sum_over_ranks_(t: torch.Tensor, group, fused: bool) -> torch.Tensor:
     return t
 
 
+class _StatusWatch:
+    """Pinned host mirror of one device's status word.  ``post`` enqueues a copy of the word behind
+    the work already on the current stream; ``poll`` looks at the last copy that has arrived, without
+    waiting for anything."""
+
+    def __init__(self):
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event: Optional[torch.cuda.Event] = None
+
+    def post(self, dev: torch.device) -> None:
+        self.host.copy_(_losses._status_word(dev), non_blocking=True)
+        self.event = torch.cuda.Event()
+        self.event.record(torch.cuda.current_stream(dev))
+
+    def poll(self) -> int:
+        if self.event is None or not self.event.query():
+            return 0
+        return int(self.host[0])
+
+
+_watches: Dict[int, _StatusWatch] = {}
+
+
+def _raise_if_previous_step_timed_out(dev: torch.device) -> None:
+    watch = _watches.get(dev.index)
+    if watch is not None and watch.poll() & nv.STATUS_PIPELINE_TIMEOUT:
+        watch.event = None
+        raise RuntimeError(
+            "flexsae_b200: an earlier batch-sharded backward on this GPU gave up waiting for another rank "
+            "(FLEXSAE_STATUS_PIPELINE_TIMEOUT): the gradients of that step are invalid and must not be applied. "
+            "A rank enqueued its backward more than wait_limit_ms after the others, or died. "
+            "flexsae_b200.check_status() clears the flag.")
+
+
+def _post_status(dev: torch.device) -> None:
+    _watches.setdefault(dev.index, _StatusWatch()).post(dev)
+
+
 def _fused_local_forward(kind, indices, weight, vals, bias, target, inv_norm):
     loss, saved, (idx_c, w_c, v_c) = _losses.fused_forward(kind, indices, weight, vals, bias, target, inv_norm)
     return loss, (idx_c, w_c, v_c, saved)
@@ -246,6 +320,8 @@ class _ShardedDecoderLoss(torch.autograd.Function):
         D = weight.shape[1]
         inv_norm = 1.0 / (float(global_rows) * D * (K if kind == nv.HIER else 1))
         fwd, _ = impl
+        if impl is FUSED_IMPL:
+            _raise_if_previous_step_timed_out(weight.device)
         loss, saved = fwd(kind, indices, weight, vals, bias, target, inv_norm)
         loss = _sum_over_ranks_(loss.clone(), group, impl is FUSED_IMPL and config.fused_small_reduce)
         ctx.kind, ctx.group, ctx.impl, ctx.inv_norm, ctx.bias_dtype = kind, group, impl, inv_norm, bias.dtype
@@ -266,6 +342,8 @@ class _ShardedDecoderLoss(torch.autograd.Function):
             dist.all_reduce(dweight, op=dist.ReduceOp.SUM, group=ctx.group)
         ctx.saved = None
         dbias = _sum_over_ranks_(dbias, ctx.group, ctx.impl is FUSED_IMPL and config.fused_small_reduce)
+        if ctx.impl is FUSED_IMPL:
+            _post_status(dweight.device)
         return None, None, None, None, None, dweight, dvals, dbias, None
 
 

@@ -48,7 +48,8 @@ extern "C" {
 
 /* bits of the optional device status word */
 #define FLEXSAE_STATUS_BAD_INDEX 1 /* an index outside [0,F) was met; it was read as row 0 */
-#define FLEXSAE_STATUS_PIPELINE_TIMEOUT 2 /* a bounded wait inside the single-launch backward gave up: gradients invalid */
+#define FLEXSAE_STATUS_PIPELINE_TIMEOUT 2 /* a bounded wait inside a kernel gave up (option "wait_limit_ms"): the results of
+                                             that call are invalid; read the word after every step of a sharded run */
 
 /* Library version (major*10000 + minor*100 + patch). No reference counterpart. */
 int flexsae_version(void);
@@ -73,7 +74,11 @@ const char* flexsae_last_error(void);
  * (1: each rank starts its scatter at a different owner's rows), "flag_fan_out" (1: a finished
  * slot is announced to all ranks by parallel stores), "sharded_convert_blocks" and
  * "sharded_convert_offset_pct" (sharded backward: number and placement of the converting blocks
- * when they differ from the single-GPU kernel's; 0 / -1 = the same).
+ * when they differ from the single-GPU kernel's; 0 / -1 = the same), "wait_limit_ms" (how long any
+ * one wait inside a kernel -- for other blocks of the launch, for another GPU -- may last before it
+ * gives up and sets FLEXSAE_STATUS_PIPELINE_TIMEOUT; 5000 by default, measured on the GPU's own
+ * nanosecond timer; a rank of a sharded run that enqueues its backward later than that after the
+ * others makes them give up, so keep it well above any host-side stall).
  * Stands in for the literal tile constants at the reference's launch sites
  * (torch-ext/flex_sae/hierarchical_kernels.py:220-224,263-267; topk_kernels.py:64-66,181-183).
  * Returns 0, or FLEXSAE_EINVAL for an unknown name or value. */
@@ -163,7 +168,8 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
  *       whatever read the previous contents must precede the call in stream order.  Not with the
  *       multicast path.  NULL = through the gather buffer
  *   seq_base   first call: 1; every later call on the same buffers: previous seq_base +
- *       flexsae_shard_slots(F, D, weight_dtype); identical on all ranks
+ *       flexsae_shard_slots(F, D, weight_dtype); identical on all ranks.  Before it would pass
+ *       INT32_MAX, start again: all ranks idle, flag buffers zeroed, seq_base = 1
  * Only FLEXSAE_DW_ATOMIC accumulation.  All ranks must issue the same sequence of calls.  Waits on
  * other GPUs are bounded; if one gives up, FLEXSAE_STATUS_PIPELINE_TIMEOUT is set in `status` and the
  * gradients of that call are invalid.
@@ -203,14 +209,35 @@ int flexsae_topk_select(const void* acts, int acts_dtype, int64_t B, int64_t F, 
  *   buf_ptrs   host array of `world` device pointers, entry r = rank r's exchange buffer of
  *       flexsae_small_allreduce_bytes(world, capacity) bytes, mapped into this process, zero before
  *       the first call; peers only store into it
- *   seq        1 on the first call on these buffers, then +1 per call; identical on all ranks, which
- *       must issue the same sequence of calls (each rank: in stream order)
+ *   seq        1 on the first call on these buffers, then +1 per call (before INT32_MAX start again:
+ *       all ranks idle, buffers zeroed, seq = 1); identical on all ranks, which must issue the same
+ *       sequence of calls (each rank: in stream order)
  * The wait for the other ranks is bounded; if it gives up, FLEXSAE_STATUS_PIPELINE_TIMEOUT is set in
  * `status` and `out` is invalid.
  */
 int flexsae_small_allreduce_bytes(int world, int64_t capacity, size_t* bytes);
 int flexsae_small_allreduce(const void* in, void* out, int64_t n, int dtype, int world, int rank, int seq,
                             void* const* buf_ptrs, int64_t capacity, int32_t* status, void* stream);
+
+/*
+ * The integer part of the deterministic dweight mode on its own: the n = B*K positions (b*K + k) of
+ * indices[B,K] grouped by decoder row, in ascending position inside each group -- a stable sort,
+ * so the result is one fixed permutation (out-of-range indices count as row 0, as in the losses).
+ *   order      [n]    position held by each sorted slot
+ *   slot_of    [n]    sorted slot of each position (the inverse permutation)
+ *   seg_begin  [F+1]  first slot of each decoder row; seg_begin[F] = n
+ *   item_begin [F+1]  first "item" of each decoder row, an item being a run of at most 32 slots of
+ *                     one row and every row owning at least one (the unit of the ordered sums)
+ * Any of the four outputs may be NULL.  All are int32 device arrays.
+ * Replaces count_per_embedding_kernel, the cumsum and map_embeddings_and_outputs_kernel of the
+ * reference's TopK backward (torch-ext/flex_sae/topk_kernels.py:71-94,146-163): seg_begin is its
+ * emb_begin_pos, order its reverse_mapping -- except that the reference places positions with
+ * fetch-add, so its order inside a segment changes from run to run.
+ */
+size_t flexsae_sort_workspace_bytes(int64_t n, int64_t F);
+int flexsae_sort_by_decoder_row(const int64_t* indices, int64_t n, int64_t F, void* workspace,
+                                size_t workspace_bytes, int32_t* order, int32_t* slot_of,
+                                int32_t* seg_begin, int32_t* item_begin, void* stream);
 
 /*
  * flexsae_loss_fwd for callers that must not allocate device memory.  It has no counterpart in
@@ -250,6 +277,16 @@ int flexsae_loss_fwd_static_scratch(int kind, const int64_t* indices, const void
 /* Number of kernels the last flexsae_loss_fwd / flexsae_loss_bwd call of this thread enqueued
  * (for launch accounting in benchmarks). No reference counterpart. */
 int flexsae_last_launch_count(void);
+
+#ifdef FLEXSAE_TRACE
+/* Tuning builds only (compiled with -DFLEXSAE_TRACE; `python -m flexsae_b200.build --trace` makes
+ * libflexsae_b200_trace.so): the sharded backward records, per slot and block role, when the first
+ * block started and the last one ended on the GPU's nanosecond timer.  This call synchronises the
+ * current device, copies the table of 64 slots x 8 fields to `out` (bytes must be 64*8*8) and clears
+ * it when `clear` is non-zero.  `python -m flexsae_b200.slot_timeline` prints it.  The default build
+ * has neither the hooks nor this symbol.  No reference counterpart. */
+int flexsae_debug_trace_read(unsigned long long* out, size_t bytes, int clear);
+#endif
 
 #ifdef __cplusplus
 }

@@ -115,12 +115,15 @@ def digest(dweight: np.ndarray, n_rows: int = 4) -> Dict[str, np.ndarray]:
 def topk_select(acts, k: int, relu: bool = True):
     """The producer step in front of the losses: per row the ``k`` largest activations, values in
     descending order, equal values by ascending index (what ``torch.topk(acts, k, sorted=True)``
-    returns up to the order of ties, which torch leaves open).  The reference has no such function
+    returns up to the order of ties, which torch leaves open; like torch.topk, a NaN counts as larger
+    than every number, and -0.0 equals +0.0).  The reference has no such function
     (its tests draw indices and vals at random, tests/test_all_kernels.py:20-33), so this one is
     pinned to torch.topk itself in ``tests/test_producer.py`` rather than to a golden file.
     Returns ``(indices int64 [B,k], vals float64 [B,k])``."""
     a = _as64(acts)
-    order = np.argsort(-a, axis=1, kind="stable")[:, :k]
+    nan = np.isnan(a)
+    key = np.where(nan, np.inf, a) + 0.0                    # + 0.0 turns -0.0 into +0.0
+    order = np.lexsort((-key, ~nan), axis=1)[:, :k]         # NaN first, then descending value, then ascending index
     vals = np.take_along_axis(a, order, axis=1)
     if relu:
         vals = np.maximum(vals, 0.0)

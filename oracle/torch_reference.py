@@ -63,7 +63,7 @@ def chunked_loss_and_grads(kind: str, indices, weight, vals, bias, target, grad_
         share = (r1 - r0) / B
         loss.backward(torch.tensor(go * share, dtype=torch.float32, device=loss.device))
         dvals[r0:r1] = v.grad
-        loss_total += float(loss) * share
+        loss_total += float(loss.detach()) * share
         rows_done = r1
     if w.device.type == "cuda":
         torch.cuda.synchronize(w.device)

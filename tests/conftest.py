@@ -8,6 +8,11 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 
+# GPU tests keep every in-kernel wait short: a protocol mistake then shows up as a reported
+# time-out within a second instead of after the production limit.  Spawned rank processes inherit it.
+os.environ.setdefault("FLEXSAE_OPTIONS", "wait_limit_ms=1500")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 

@@ -12,6 +12,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def header_prototypes():
     text = open(os.path.join(ROOT, "include", "flexsae_b200.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"#ifdef FLEXSAE_TRACE.*?#endif", "", text, flags=re.S)    # tuning builds only: not in the default library
     protos = {}
     for m in re.finditer(r"([A-Za-z_][\w\s\*]*?)\b(flexsae_\w+)\s*\(([^;{]*?)\)\s*;", text):
         args = m.group(3).strip()
@@ -142,3 +143,42 @@ def test_small_allreduce_rejects_bad_arguments_without_a_gpu():
     assert call(seq=0) == -1
     assert call(src=None) == -1 and call(bufs=None) == -1
     assert call(bufs=(ctypes.c_void_p * 2)(256, 0)) == -1 and b"rank 1" in lib.flexsae_last_error()
+
+
+def test_wait_limit_option_is_validated():
+    lib = nv.load()
+    before = nv.get_option("wait_limit_ms")
+    assert before >= 1000                                # production default: seconds, not a poll count
+    assert lib.flexsae_set_option(b"wait_limit_ms", 0) == -1
+    assert lib.flexsae_set_option(b"wait_limit_ms", 10 ** 9) == -1
+    nv.set_option("wait_limit_ms", 250)
+    assert nv.get_option("wait_limit_ms") == 250
+    nv.set_option("wait_limit_ms", before)
+
+
+def test_decoder_of_64_gib_or_more_is_refused():
+    """Row-piece offsets are 32-bit counts of 16-byte units: a decoder whose bytes do not fit is refused
+    instead of being addressed modulo 2^36."""
+    lib = nv.load()
+    assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 64, 8, 1 << 21, 16384, nv.BF16) == 0      # exactly 64 GiB
+    assert b"64 GiB" in lib.flexsae_last_error()
+    assert lib.flexsae_fwd_workspace_bytes(nv.HIER, 64, 8, 1 << 21, 16384 - 8, nv.BF16) > 0
+    assert lib.flexsae_choose_segments(nv.HIER, 64, 8, 1 << 22, 4096, nv.F32) == 0           # 64 GiB in fp32
+    rc = lib.flexsae_loss_bwd(nv.HIER, None, None, None, None, 1, None, None, None, None, None, 0, 64, 8, 1 << 21, 16384,
+                              nv.BF16, nv.F32, nv.BF16, 0.0, nv.DW_ATOMIC, None, None)
+    assert rc == -3
+
+
+def test_sort_entry_rejects_bad_arguments_without_a_gpu():
+    lib = nv.load()
+    need = lib.flexsae_sort_workspace_bytes(1000, 64)
+    assert need >= 5 * 1000 * 4 + 3 * 65 * 4
+    assert lib.flexsae_sort_workspace_bytes(0, 64) == 0 and lib.flexsae_sort_workspace_bytes(10, 0) == 0
+
+    def call(idx=64, n=1000, F=64, ws=256, ws_bytes=need):
+        return lib.flexsae_sort_by_decoder_row(idx, n, F, ws, ws_bytes, None, None, None, None, None)
+
+    assert call(n=0) == -1 and call(F=0) == -1
+    assert call(idx=None) == -1 and call(ws=None) == -1 and b"null" in lib.flexsae_last_error()
+    assert call(ws=264) == -1 and b"aligned" in lib.flexsae_last_error()
+    assert call(ws_bytes=need - 1) == -2 and b"too small" in lib.flexsae_last_error()

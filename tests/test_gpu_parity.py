@@ -264,6 +264,30 @@ def test_config3_bf16_full_size(name, kind):
     _compare_with_torch_reference_on_gpu(CONFIGS[name], kind, tol=1e-2, loss_tol=1e-5, chunk_rows=128)
 
 
+@pytest.mark.parametrize("mode", ["atomic", "deterministic"])
+def test_config4_zipf_full_size_both_dweight_modes(mode):
+    """F=65536 D=2304 K=64 B=16384 bf16, Zipf(1.1) indices: the hottest decoder rows receive thousands of
+    contributions each, the stress case of the scatter-add and of the ordered sums' item tree."""
+    fx.config.dweight_mode = mode
+    try:
+        got, _ = _compare_with_torch_reference_on_gpu(CONFIGS["c4"], "hier", tol=1e-2, loss_tol=1e-5, chunk_rows=128)
+        if mode == "deterministic":        # bit for bit, run to run, at full size too
+            x = make_inputs(CONFIGS["c4"], "cuda")
+            go = torch.tensor(float(CONFIGS["c4"].B * CONFIGS["c4"].D) / 2.0 * CONFIGS["c4"].K * 0.37)
+            again = run_fused("hier", x, grad_out=go)
+            for k in ("dweight", "dvals", "dbias"):
+                assert np.array_equal(got[k], again[k]), k
+            assert got["loss"] == again["loss"]
+    finally:
+        fx.config.dweight_mode = "atomic"
+
+
+def test_config5_one_gpu_shard_full_size():
+    """F=131072 D=4096 K=128 bf16 with the 8192 rows one GPU of eight holds of the 65536-row batch:
+    the widest decoder of the five set-ups (8 lanes per row, 64 column pieces)."""
+    _compare_with_torch_reference_on_gpu(CONFIGS["c5"].replace(B=8192), "hier", tol=1e-2, loss_tol=1e-5, chunk_rows=64)
+
+
 def test_out_of_range_index_is_reported_not_dereferenced():
     w = Workload("bad", B=8, K=4, F=16, D=256, indices="dup", seed=31)
     x = make_inputs(w, "cuda")
@@ -357,6 +381,43 @@ def test_deterministic_mode_is_bitwise_reproducible_and_right(w, kind, determini
     assert abs(float(runs[0][0]) - ref["loss"]) <= 1e-5 * abs(ref["loss"])
     for got, name in zip(runs[0][1:], ("dweight", "dvals", "dbias")):
         assert rel_err(got.float().cpu().numpy(), ref[name].float().cpu().numpy()) < TIGHT[w.weight_dtype], name
+
+
+SORT_CASES = DET_CASES + [
+    Workload("sort_zipf_wide", B=4096, K=64, F=65536, D=8, weight_dtype="bfloat16", indices="zipf", seed=55),
+    Workload("sort_tiny", B=1, K=1, F=1, D=8, indices="dup", seed=56),
+]
+
+
+@pytest.mark.parametrize("w", SORT_CASES, ids=lambda w: w.name)
+def test_sort_tables_match_stable_argsort(w):
+    """Integer work of the deterministic mode, bit for bit against numpy's stable argsort: the
+    permutation, its inverse, the segment starts (the reference's emb_begin_pos,
+    topk_kernels.py:152) and the 32-slot item table."""
+    import ctypes
+
+    lib = nv.load()
+    idx = make_inputs(w, "cuda", with_weight=False)["indices"].reshape(-1).contiguous()
+    n, F = idx.numel(), w.F
+    if n > 8:                               # out-of-range entries count as decoder row 0, as in the losses
+        idx[3], idx[n - 2] = F, -5
+    ws = torch.empty(lib.flexsae_sort_workspace_bytes(n, F), dtype=torch.uint8, device="cuda")
+    order, slot_of = (torch.full((n,), -1, dtype=torch.int32, device="cuda") for _ in range(2))
+    seg_begin, item_begin = (torch.full((F + 1,), -1, dtype=torch.int32, device="cuda") for _ in range(2))
+    rc = lib.flexsae_sort_by_decoder_row(idx.data_ptr(), n, F, ws.data_ptr(), ws.numel(), order.data_ptr(), slot_of.data_ptr(),
+                                         seg_begin.data_ptr(), item_begin.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.flexsae_last_error()
+    keys = idx.cpu().numpy().copy()
+    keys[(keys < 0) | (keys >= F)] = 0
+    want_order = np.argsort(keys, kind="stable")
+    assert np.array_equal(order.cpu().numpy(), want_order)
+    want_slot = np.empty(n, dtype=np.int64)
+    want_slot[want_order] = np.arange(n)
+    assert np.array_equal(slot_of.cpu().numpy(), want_slot)
+    want_seg = np.searchsorted(keys[want_order], np.arange(F + 1), side="left")
+    assert np.array_equal(seg_begin.cpu().numpy(), want_seg)
+    items = np.maximum(1, (np.diff(want_seg) + 31) // 32)
+    assert np.array_equal(item_begin.cpu().numpy(), np.concatenate([[0], np.cumsum(items)]))
 
 
 def test_atomic_and_deterministic_modes_agree():

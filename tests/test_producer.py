@@ -28,6 +28,16 @@ def test_oracle_orders_ties_by_index_and_clamps():
     assert vals.tolist() == [[2.0, 0.5, 0.5, 0.5, 0.0]]
 
 
+def test_oracle_special_values_follow_torch_topk():
+    nan, inf = float("nan"), float("inf")
+    acts = np.array([[0.0, -0.0, nan, 1.0, inf, -inf, -0.0, 0.0, nan, -1.0]])
+    idx, vals = orc.topk_select(acts, 8, relu=False)
+    assert idx.tolist() == [[2, 8, 4, 3, 0, 1, 6, 7]]          # NaNs (by index), +inf, 1, then the four zeros by index
+    tv, ti = torch.topk(torch.from_numpy(acts), 4, dim=1, sorted=True)
+    assert sorted(ti[0, :2].tolist()) == [2, 8] and ti[0, 2:].tolist() == [4, 3]     # torch: NaN above +inf too
+    assert np.isnan(vals[0, :2]).all() and vals[0, 2] == inf
+
+
 def test_entry_rejects_bad_arguments_without_a_gpu():
     lib = nv.load()
 
@@ -49,6 +59,7 @@ CASES = [  # B, F, K, dtype, kind of data
     (4, 1000, 33, torch.float32, "relu"), (4, 1024, 1024, torch.float16, "normal"), (3, 512, 100, torch.bfloat16, "ties"),
     (2, 131072, 64, torch.float32, "normal"), (1, 8, 1, torch.float16, "ties"), (6, 8192, 256, torch.float16, "relu"),
     (2, 8192, 16, torch.bfloat16, "const"), (2, 16384, 40, torch.float32, "ties"),      # candidate list overflows
+    (3, 512, 12, torch.float32, "special"), (3, 1024, 20, torch.bfloat16, "special"), (2, 256, 9, torch.float16, "special"),
 ]
 
 
@@ -63,6 +74,14 @@ def test_gpu_selection_matches_oracle(B, F, K, dtype, data, relu):
         acts = torch.full((B, F), 0.25).to(dtype)
     elif data == "ties":
         acts = torch.randint(-3, 4, (B, F), generator=g).to(dtype)
+    elif data == "special":          # signed zeros, NaNs of both signs, infinities among small integers
+        acts = torch.randint(-2, 2, (B, F), generator=g).to(torch.float32)
+        acts[:, 5::37] = -0.0
+        acts[:, 7::53] = float("nan")
+        acts[:, 60::97] = -acts[:, 7::53][:, : acts[:, 60::97].shape[1]]     # NaN with the sign bit set
+        acts[:, 11::101] = float("inf")
+        acts[:, 13::89] = -float("inf")
+        acts = acts.to(dtype)
     else:
         acts = torch.randn(B, F, generator=g).to(dtype)
         if data == "relu":
@@ -71,7 +90,7 @@ def test_gpu_selection_matches_oracle(B, F, K, dtype, data, relu):
     idx, vals = producer.select_topk(acts.cuda(), K, relu=relu, vals_dtype=torch.float32)
     assert idx.dtype == torch.int64 and idx.shape == (B, K) and vals.shape == (B, K)
     assert np.array_equal(idx.cpu().numpy(), want_idx)                      # bit-exact: integer work
-    assert np.array_equal(vals.cpu().numpy(), want_vals.astype(np.float32))
+    assert np.array_equal(vals.cpu().numpy(), want_vals.astype(np.float32), equal_nan=True)
 
 
 @unverified_on_gpu
