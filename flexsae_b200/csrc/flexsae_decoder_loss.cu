@@ -221,9 +221,11 @@ static FwdPlan plan_fwd(const Shape& s, int wdt) {
 
 constexpr size_t kRingBytes = (size_t)kRingSlots * kThreads * sizeof(uint4);  // 2 KiB per slot and CTA
 
+// Dynamic plus static shared memory above 48 KiB needs the opt-in attribute; the kernels declare a few
+// bytes of static shared memory themselves, so the opt-in is asked for a little below the line.
 template <typename K>
 static cudaError_t allow_smem(K kern, size_t smem) {
-  if (smem <= 48 * 1024) return cudaSuccess;
+  if (smem <= 40 * 1024) return cudaSuccess;
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 
@@ -793,19 +795,7 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
 namespace flexsae {
 template <typename T>
 static cudaError_t launch_topk_select(const SelectArgs& a, int64_t B, cudaStream_t st) {
-  const size_t row_bytes = (size_t)a.F * sizeof(T);
-  const bool cached = row_bytes + kSelFixedSmem <= 200 * 1024;  // leaves room below the 227 KB a CTA may have
-  const size_t smem = kSelFixedSmem + (cached ? row_bytes : 0);
-  cudaError_t e;
-  if (cached) {
-    auto kern = topk_select_kernel<T, true>;
-    if ((e = allow_smem(kern, smem)) != cudaSuccess) return e;
-    kern<<<(unsigned)B, kSelThreads, smem, st>>>(a);
-  } else {
-    auto kern = topk_select_kernel<T, false>;
-    if ((e = allow_smem(kern, smem)) != cudaSuccess) return e;
-    kern<<<(unsigned)B, kSelThreads, smem, st>>>(a);
-  }
+  topk_select_kernel<T><<<(unsigned)B, kSelThreads, 0, st>>>(a);
   t_launches++;
   return cudaGetLastError();
 }

@@ -1,32 +1,38 @@
 // Producer step in front of the decoder losses: per batch row, the K largest of F encoder
 // activations, as int64 decoder-row indices plus values sorted in descending order -- exactly the
-// (indices, vals) pair the loss kernels take.  One CTA per row.  The row is read from HBM once into
-// shared memory when it fits (128 KB for F = 65536 in bf16) and every later pass runs out of shared
-// memory; longer rows are re-read (they come back from L2).
+// (indices, vals) pair the loss kernels take.
 //
-// Selection is exact.  A pre-filter first bounds the answer from below: the K-th largest of the 1024
-// per-thread maxima cannot exceed the K-th largest element, and for K << F barely more than K
-// elements reach it (about 1.07 K for K = 128, F = 65536).  Those candidates are collected in index
-// order, and a radix select on an order-preserving integer key (8 bits per pass from the top: 2
-// passes for 16-bit activations, 4 for fp32) finds the key of the K-th largest among them;
-// everything above it plus the lowest-indexed ties are the winners, so the result does not depend on
-// scheduling.  Rows with masses of equal values overflow the candidate list and take the same radix
-// select over the whole row instead.  The K winners are then sorted (value descending, index
-// ascending) with a bitonic network in shared memory.
+// One CTA of 256 threads per row, several CTAs resident per SM, the row streamed from HBM ONCE:
+//   1. every thread takes 16-byte vectors at a stride of the CTA and keeps four running maxima (one per
+//      vector slot modulo 4): 1024 maxima of disjoint element sets per row.  The K-th largest of them
+//      is a lower bound of the K-th largest element, and for K << F a tight one (about 1.07 K elements
+//      reach it at K = 128, F = 65536);
+//   2. that bound is found exactly on the top 16 bits of an order-preserving integer key (two 8-bit
+//      histogram passes over the maxima, which never leave their registers);
+//   3. the row is read again -- it is still in L2 -- and everything not below the bound is appended
+//      to a candidate list in shared memory (any order);
+//   4. the candidates are sorted by (key descending, index ascending) with a bitonic network and
+//      the first K are the answer.
+// The result is exact and independent of scheduling: the candidate SET is determined by the bound,
+// and the sort is a total order.  Rows whose candidates overflow the list (masses of equal values,
+// e.g. fewer than K positive entries after a ReLU) take an exact radix select over the whole row (8
+// bits per pass on the full key, ties by ascending index) instead of step 3.
+// NaN counts as larger than every number (as in torch.topk) and -0.0 equals +0.0.
 #pragma once
 
 #include "flexsae_common.cuh"
 
 namespace flexsae {
 
-constexpr int kSelThreads = 1024;
+constexpr int kSelThreads = 256;
 constexpr int kSelWarps = kSelThreads / 32;
-constexpr int kSelMaxK = 1024;        // <= kSelThreads: the pre-filter needs at least K per-thread maxima
-constexpr int kSelCandidates = 4096;  // capacity of the candidate list
-// shared memory besides the optional row cache: candidate list (doubles as the per-warp histograms of
-// the fallback), sort buffer, per-thread maxima, merged histogram and its suffix sums, scan scratch
-constexpr size_t kSelFixedSmem =
-    (size_t)kSelCandidates * 8 + (size_t)kSelMaxK * 8 + (size_t)kSelThreads * 4 + 256 * 4 * 2 + 64 * 4;
+constexpr int kSelMaxima = 4;                        // running maxima per thread
+constexpr int kSelMaxK = kSelThreads * kSelMaxima;   // the bound needs at least K maxima
+constexpr int kSelCandidates = 2048;                 // capacity of the candidate list (>= kSelMaxK)
+constexpr int kSelInFlight = 8;                      // 16-byte loads in flight per thread
+#ifndef FLEXSAE_SEL_MINB
+#define FLEXSAE_SEL_MINB 4                           // resident CTAs per SM the kernel is compiled for
+#endif
 
 template <typename T>
 struct SelKey;
@@ -94,263 +100,292 @@ struct SelectArgs {
   int relu;          // clamp the reported values at zero
 };
 
-// Block-wide exclusive prefix sum of a packed pair of counters (each field stays below 2^16 per
-// call); `total` receives the block total.  Ends with a barrier, so `scratch` may be reused at once.
-__device__ __forceinline__ uint32_t sel_block_scan(uint32_t cnt, int* scratch, uint32_t* total) {
+// Does this 16-byte vector hold a NaN?  (16-bit types: two elements per word, tested together.)
+template <typename T>
+__device__ __forceinline__ bool vector_has_nan(const uint4& v);
+template <>
+__device__ __forceinline__ bool vector_has_nan<float>(const uint4& v) {
+  return ((v.x & 0x7fffffffu) > 0x7f800000u) | ((v.y & 0x7fffffffu) > 0x7f800000u) | ((v.z & 0x7fffffffu) > 0x7f800000u) |
+         ((v.w & 0x7fffffffu) > 0x7f800000u);
+}
+// (h & 0x7fff) > 0x7f80  <=>  bit 15 of (h & 0x7fff) + 0x007f is set; no carry crosses the halves
+template <>
+__device__ __forceinline__ bool vector_has_nan<__nv_bfloat16>(const uint4& v) {
+  const uint32_t m = 0x7fff7fffu, c = 0x007f007fu;
+  return ((((v.x & m) + c) | ((v.y & m) + c) | ((v.z & m) + c) | ((v.w & m) + c)) & 0x80008000u) != 0u;
+}
+template <>
+__device__ __forceinline__ bool vector_has_nan<__half>(const uint4& v) {
+  const uint32_t m = 0x7fff7fffu, c = 0x03ff03ffu;
+  return ((((v.x & m) + c) | ((v.y & m) + c) | ((v.z & m) + c) | ((v.w & m) + c)) & 0x80008000u) != 0u;
+}
+
+// bit pattern of element j of a 16-byte vector, as SelKey<T>::key takes it
+template <typename T>
+__device__ __forceinline__ uint32_t vector_bits(const uint4& v, int j) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if (SelKey<T>::BYTES == 4) return w[j];
+  return (j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xffffu);
+}
+
+// Block-wide exclusive prefix sum (values stay below 2^31 in total); `total` receives the block
+// total.  Ends with a barrier, so `scratch` (kSelWarps ints) may be reused at once.
+__device__ __forceinline__ int sel_block_scan(int cnt, int* scratch, int* total) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  uint32_t incl = cnt;
+  int incl = cnt;
 #pragma unroll
   for (int d = 1; d < 32; d <<= 1) {
-    const uint32_t up = __shfl_up_sync(0xffffffffu, incl, d);
+    const int up = __shfl_up_sync(0xffffffffu, incl, d);
     if (lane >= d) incl += up;
   }
-  if (lane == 31) scratch[warp] = (int)incl;
+  if (lane == 31) scratch[warp] = incl;
   __syncthreads();
-  if (warp == 0) {
-    uint32_t t = (uint32_t)scratch[lane];
+  int before = incl - cnt, sum = 0;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const uint32_t up = __shfl_up_sync(0xffffffffu, t, d);
-      if (lane >= d) t += up;
-    }
-    scratch[lane] = (int)t;  // inclusive totals of the warps
+  for (int w = 0; w < kSelWarps; w++) {
+    const int t = scratch[w];
+    if (w < warp) before += t;
+    sum += t;
   }
-  __syncthreads();
-  const uint32_t before = (warp ? (uint32_t)scratch[warp - 1] : 0u) + incl - cnt;
-  *total = (uint32_t)scratch[kSelWarps - 1];
+  *total = sum;
   __syncthreads();
   return before;
 }
 
-// From a merged 256-bin histogram of the current digit: the digit in which the `need`-th largest
-// matching element lies, and how many matching elements lie in higher digits.
-__device__ __forceinline__ void sel_pick_digit(int* hist, int* suffix, int* scratch, int need, int* digit, int* above) {
-  const int tid = threadIdx.x;
-  if (tid < 256) suffix[tid] = hist[tid];
-  __syncthreads();
-  for (int d = 1; d < 256; d <<= 1) {  // suffix[i] = hist[i] + hist[i+1] + ... + hist[255]
-    int add = 0;
-    if (tid < 256 && tid + d < 256) add = suffix[tid + d];
-    __syncthreads();
-    if (tid < 256) suffix[tid] += add;
-    __syncthreads();
-  }
-  if (tid < 256) {
-    const int up = tid == 255 ? 0 : suffix[tid + 1];
-    if (suffix[tid] >= need && up < need) {  // exactly one digit: the suffix sums do not increase
-      scratch[32] = tid;
-      scratch[33] = up;
+// From a 256-bin histogram of the current digit (complete, a barrier behind it): the digit in which
+// the `need`-th largest element lies and how many elements lie in higher digits.  Warp 0 works (8
+// bins per lane, suffix sums by shuffles); everybody gets the answer.  Ends with a barrier.
+__device__ __forceinline__ void sel_pick_digit(const int* hist, int* answer, int need, int* digit, int* above) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int h[8], mine = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      h[i] = hist[8 * lane + i];
+      mine += h[i];
     }
-  }
-  __syncthreads();
-  *digit = scratch[32];
-  *above = scratch[33];
-  __syncthreads();
-}
-
-// Exact radix select in a short list held in shared memory (the per-thread maxima, the candidate
-// list): key of the `need`-th largest of `m` keys; *ties_needed = how many elements equal to it
-// complete the selection.  Lanes that hit the same bin add once (match_any), because the keys of a
-// top-K problem crowd into very few bins.
-template <int NPASS, typename KeyAt>
-__device__ __forceinline__ uint32_t sel_list_kth(KeyAt key_at, int m, int need, int* hist, int* suffix, int* scratch,
-                                                 int* ties_needed) {
-  const int tid = threadIdx.x, lane = tid & 31;
-  uint32_t prefix = 0, hi_mask = 0;
-  for (int pass = 0; pass < NPASS; pass++) {
-    const int shift = 8 * (NPASS - 1 - pass);
-    if (tid < 256) hist[tid] = 0;
-    __syncthreads();
-    for (int i0 = 0; i0 < m; i0 += kSelThreads) {
-      const int i = i0 + tid;
-      int bin = -1 - lane;  // lanes without a matching element: a value no other lane has
-      if (i < m) {
-        const uint32_t k = key_at(i);
-        if ((k & hi_mask) == prefix) bin = (int)((k >> shift) & 255u);
+    int incl = mine;  // inclusive suffix sum over lanes: bins of this lane and of all higher lanes
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int dn = __shfl_down_sync(0xffffffffu, incl, d);
+      if (lane + d < 32) incl += dn;
+    }
+    int higher = incl - mine;  // elements in the bins of higher lanes
+    if (incl >= need && higher < need) {  // exactly one lane: the suffix sums do not increase
+#pragma unroll
+      for (int i = 7; i >= 0; i--) {
+        if (higher < need && higher + h[i] >= need) {
+          answer[0] = 8 * lane + i;
+          answer[1] = higher;
+        }
+        higher += h[i];
       }
-      const unsigned peers = __match_any_sync(0xffffffffu, bin);
-      if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(hist + bin, __popc(peers));
     }
-    __syncthreads();
-    int digit, above;
-    sel_pick_digit(hist, suffix, scratch, need, &digit, &above);
-    prefix |= (uint32_t)digit << shift;
-    need -= above;
-    hi_mask |= 255u << shift;
   }
-  *ties_needed = need;
-  return prefix;
+  __syncthreads();
+  *digit = answer[0];
+  *above = answer[1];
+  __syncthreads();
 }
 
-template <typename T, bool CACHED>
-__global__ void __launch_bounds__(kSelThreads, 1) topk_select_kernel(const SelectArgs a) {
+// one more element into a 256-bin histogram in shared memory; lanes of a warp that hit the same bin add
+// once (the keys of a top-K problem crowd into very few bins).  bin < 0: nothing.  All 32 lanes call it.
+__device__ __forceinline__ void sel_hist_add(int* hist, int bin) {
+  const int lane = threadIdx.x & 31;
+  const unsigned peers = __match_any_sync(0xffffffffu, bin < 0 ? -1 - lane : bin);
+  if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(hist + bin, __popc(peers));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_kernel(const SelectArgs a) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int NPASS = SelKey<T>::BYTES;
-  extern __shared__ uint4 sel_smem[];
-  const int nvec = a.F / VEC;
-  uint4* cache = sel_smem;
-  unsigned long long* cand = reinterpret_cast<unsigned long long*>(sel_smem + (CACHED ? nvec : 0));  // [kSelCandidates]
-  int* warp_hist = reinterpret_cast<int*>(cand);                     // fallback only: [warps][256], same memory
-  unsigned long long* sorted = cand + kSelCandidates;                // [Kp] (key << 32) | ~index
-  uint32_t* tmax = reinterpret_cast<uint32_t*>(sorted + kSelMaxK);   // [threads]
-  int* hist = reinterpret_cast<int*>(tmax + kSelThreads);            // [256]
-  int* suffix = hist + 256;                                          // [256]
-  int* scratch = suffix + 256;                                       // [64]: warp totals, digit, count above
+  constexpr int SHORT_SHIFT = 8 * NPASS - 16;  // the top 16 bits of a key are its "short key"
+  constexpr int Q = kSelInFlight;
+  __shared__ unsigned long long cand[kSelCandidates];  // (key << 32) | ~index; the whole-row select reuses it as histograms
+  __shared__ int hist[256];
+  __shared__ int misc[16];  // [0..1] digit / count above, [2] candidates so far, [8..15] scan scratch
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int nvec = a.F / VEC;
   const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.acts) + (size_t)blockIdx.x * a.F);
 
-  if (CACHED) {
-    for (int v = tid; v < nvec; v += kSelThreads) cache[v] = __ldcs(row + v);  // read once: streaming
-    __syncthreads();
-  }
-  const uint4* src = CACHED ? cache : row;
-
-  // ---- 1. pre-filter.  The K-th largest of the per-thread maxima is a lower bound of the K-th
-  // largest element (the K largest maxima are K different elements), and for K << F it is so tight
-  // that barely more than K elements reach it.
-  uint32_t mine = 0;  // key 0 is below every real key: the lowest one, that of -inf, is still positive
-  for (int v = tid; v < nvec; v += kSelThreads) {
-    uint32_t k[VEC];
-    vector_keys<T>(CACHED ? src[v] : __ldg(src + v), k);
+  // ---- 1. stream the row once: four running maxima per thread, NaNs noted per maximum -------------
+  float top[kSelMaxima];
 #pragma unroll
-    for (int j = 0; j < VEC; j++) mine = max(mine, k[j]);
-  }
-  tmax[tid] = mine;
-  for (int i = tid; i < a.Kp; i += kSelThreads) sorted[i] = 0ull;  // padding sorts last
-  __syncthreads();
-  int unused;
-  const uint32_t bound = sel_list_kth<NPASS>([&](int i) { return tmax[i]; }, kSelThreads, a.K, hist, suffix, scratch, &unused);
-
-  // ---- 2. candidates (key >= bound), collected in index order -----------------------------------
-  int n_cand = 0;
-  for (int v0 = 0; v0 < nvec; v0 += kSelThreads) {
-    const int v = v0 + tid;
-    uint32_t k[VEC];
-    int n = 0;
-    if (v < nvec) {
-      vector_keys<T>(CACHED ? src[v] : __ldg(src + v), k);
+  for (int m = 0; m < kSelMaxima; m++) top[m] = -INFINITY;
+  unsigned nan_in = 0;
+  for (int base = 0; base < nvec; base += Q * kSelThreads) {
+    uint4 x[Q];
 #pragma unroll
-      for (int j = 0; j < VEC; j++) n += k[j] >= bound;
+    for (int q = 0; q < Q; q++) {
+      const int v = base + q * kSelThreads + tid;
+      if (v < nvec) x[q] = __ldg(row + v);
     }
-    uint32_t total;
-    int at = n_cand + (int)sel_block_scan((uint32_t)n, scratch, &total);
-    if (v < nvec) {
 #pragma unroll
-      for (int j = 0; j < VEC; j++)
-        if (k[j] >= bound) {
-          if (at < kSelCandidates) cand[at] = ((unsigned long long)k[j] << 32) | (uint32_t)~(uint32_t)(v * VEC + j);
-          at++;
+    for (int q = 0; q < Q; q++) {
+      const int v = base + q * kSelThreads + tid;
+      if (v < nvec) {
+        float f[VEC];
+        Pack<T>::unpack(x[q], f);
+        float mx = f[0];
+#pragma unroll
+        for (int j = 1; j < VEC; j++) mx = fmaxf(mx, f[j]);  // ignores NaNs; they are noted below
+        top[q % kSelMaxima] = fmaxf(top[q % kSelMaxima], mx);
+        if (vector_has_nan<T>(x[q])) nan_in |= 1u << (q % kSelMaxima);
+      }
+    }
+  }
+  uint32_t skey[kSelMaxima];  // short keys of the maxima (a set without elements ranks lowest: -inf)
+#pragma unroll
+  for (int m = 0; m < kSelMaxima; m++) {
+    uint32_t bits;
+    if (SelKey<T>::BYTES == 4) bits = __float_as_uint(top[m]);
+    else if (Pack<T>::DTYPE == FLEXSAE_BF16) bits = __float_as_uint(top[m]) >> 16;
+    else bits = (uint32_t)__half_as_ushort(__float2half_rn(top[m]));  // the maximum IS an fp16 value: exact
+    skey[m] = ((nan_in >> m) & 1u) ? 0xffffu : (SelKey<T>::key(bits) >> SHORT_SHIFT);
+  }
+
+  // ---- 2. K-th largest short key of the 1024 maxima: two 8-bit histogram passes ----------------------
+  int need = a.K, digit, above;
+  hist[tid] = 0;
+  if (tid == 0) misc[2] = 0;
+  __syncthreads();
+#pragma unroll
+  for (int m = 0; m < kSelMaxima; m++) sel_hist_add(hist, (int)(skey[m] >> 8));
+  __syncthreads();
+  sel_pick_digit(hist, misc, need, &digit, &above);
+  need -= above;
+  const uint32_t hi = (uint32_t)digit;
+  hist[tid] = 0;
+  __syncthreads();
+#pragma unroll
+  for (int m = 0; m < kSelMaxima; m++) sel_hist_add(hist, (skey[m] >> 8) == hi ? (int)(skey[m] & 255u) : -1);
+  __syncthreads();
+  sel_pick_digit(hist, misc, need, &digit, &above);
+  // lower edge of the short key's bin as a value: every element not below it is a candidate.  A bound
+  // in the NaN range makes the comparison below true for everything: the row then overflows the list
+  // and is selected exactly by the whole-row path.
+  const uint32_t bound_key = ((hi << 8) | (uint32_t)digit) << SHORT_SHIFT;
+  const float bound = SelKey<T>::value(bound_key);
+
+  // ---- 3. candidates: second read of the row (L2), unordered append ----------------------------------
+  for (int base = 0; base < nvec; base += Q * kSelThreads) {
+    uint4 x[Q];
+#pragma unroll
+    for (int q = 0; q < Q; q++) {
+      const int v = base + q * kSelThreads + tid;
+      if (v < nvec) x[q] = __ldg(row + v);
+    }
+#pragma unroll
+    for (int q = 0; q < Q; q++) {
+      const int v = base + q * kSelThreads + tid;
+      if (v < nvec) {
+        float f[VEC];
+        Pack<T>::unpack(x[q], f);
+        unsigned hits = 0;
+#pragma unroll
+        for (int j = 0; j < VEC; j++) hits |= (unsigned)(!(f[j] < bound)) << j;  // a NaN is never below
+        while (hits) {
+          const int j = __ffs(hits) - 1;
+          hits &= hits - 1;
+          const int at = atomicAdd(&misc[2], 1);
+          if (at < kSelCandidates)
+            cand[at] = ((unsigned long long)SelKey<T>::key(vector_bits<T>(x[q], j)) << 32) | (uint32_t)~(uint32_t)(v * VEC + j);
         }
+      }
     }
-    n_cand += (int)total;
   }
   __syncthreads();
+  int n_cand = misc[2];
+  __syncthreads();
 
-  if (n_cand <= kSelCandidates) {
-    // ---- 3a. exact selection inside the candidate list, then the winners in list (= index) order
-    int need;
-    const uint32_t kth = sel_list_kth<NPASS>([&](int i) { return (uint32_t)(cand[i] >> 32); }, n_cand, a.K, hist, suffix,
-                                             scratch, &need);
-    const int n_above = a.K - need;
-    int above_base = 0, tie_base = 0;
-    for (int i0 = 0; i0 < n_cand; i0 += kSelThreads) {
-      const int i = i0 + tid;
-      const unsigned long long e = i < n_cand ? cand[i] : 0ull;
-      const uint32_t k = (uint32_t)(e >> 32);
-      const bool gt = i < n_cand && k > kth, eq = i < n_cand && k == kth;
-      uint32_t total;
-      const uint32_t before = sel_block_scan((uint32_t)gt | ((uint32_t)eq << 16), scratch, &total);
-      if (gt) sorted[above_base + (int)(before & 0xffffu)] = e;
-      if (eq && tie_base + (int)(before >> 16) < need) sorted[n_above + tie_base + (int)(before >> 16)] = e;
-      above_base += (int)(total & 0xffffu);
-      tie_base += (int)(total >> 16);
-    }
-  } else {
-    // ---- 3b. fallback for rows with masses of equal values: radix select over the whole row, 8 bits
-    // per pass, per-warp histograms; then the winners in index order
+  if (n_cand > kSelCandidates) {
+    // ---- 3b. too many candidates (masses of equal values): exact radix select over the whole row, 8
+    // bits of the full key per pass, per-warp histograms; then the winners: everything above the K-th
+    // key in any order, and of the elements equal to it the ones with the lowest indices
+    int* warp_hist = reinterpret_cast<int*>(cand);  // [kSelWarps][256]
     uint32_t prefix = 0, hi_mask = 0;
-    int need = a.K;
+    need = a.K;
     for (int pass = 0; pass < NPASS; pass++) {
       const int shift = 8 * (NPASS - 1 - pass);
       for (int i = tid; i < kSelWarps * 256; i += kSelThreads) warp_hist[i] = 0;
       __syncthreads();
       int* my_hist = warp_hist + warp * 256;
-      for (int v = tid; v < nvec; v += kSelThreads) {
+      for (int v0 = 0; v0 < nvec; v0 += kSelThreads) {  // uniform trip count: sel_hist_add needs whole warps
+        const int v = v0 + tid;
         uint32_t k[VEC];
-        vector_keys<T>(CACHED ? src[v] : __ldg(src + v), k);
+        if (v < nvec) vector_keys<T>(__ldg(row + v), k);
 #pragma unroll
         for (int j = 0; j < VEC; j++)
-          if ((k[j] & hi_mask) == prefix) atomicAdd(my_hist + ((k[j] >> shift) & 255u), 1);
+          sel_hist_add(my_hist, (v < nvec && (k[j] & hi_mask) == prefix) ? (int)((k[j] >> shift) & 255u) : -1);
       }
       __syncthreads();
-      if (tid < 256) {
-        int sum = 0;
-        for (int w = 0; w < kSelWarps; w++) sum += warp_hist[w * 256 + tid];
-        hist[tid] = sum;
-      }
+      int sum = 0;
+      for (int w = 0; w < kSelWarps; w++) sum += warp_hist[w * 256 + tid];
+      hist[tid] = sum;
       __syncthreads();
-      int digit, above;
-      sel_pick_digit(hist, suffix, scratch, need, &digit, &above);
+      sel_pick_digit(hist, misc, need, &digit, &above);
       prefix |= (uint32_t)digit << shift;
       need -= above;
       hi_mask |= 255u << shift;
     }
     const uint32_t kth = prefix;
-    const int n_above = a.K - need;
-    int above_base = 0, tie_base = 0;
+    const int n_above = a.K - need;  // elements strictly above the K-th key: fewer than K
+    if (tid == 0) misc[2] = 0;
+    __syncthreads();  // the histograms are no longer read: the list may be written
+    int tie_base = 0;
     for (int v0 = 0; v0 < nvec; v0 += kSelThreads) {
       const int v = v0 + tid;
       uint32_t k[VEC];
-      int n_gt = 0, n_eq = 0;
+      int n_eq = 0;
       if (v < nvec) {
-        vector_keys<T>(CACHED ? src[v] : __ldg(src + v), k);
+        vector_keys<T>(__ldg(row + v), k);
 #pragma unroll
         for (int j = 0; j < VEC; j++) {
-          n_gt += k[j] > kth;
           n_eq += k[j] == kth;
+          if (k[j] > kth) cand[atomicAdd(&misc[2], 1)] = ((unsigned long long)k[j] << 32) | (uint32_t)~(uint32_t)(v * VEC + j);
         }
       }
-      uint32_t total;
-      const uint32_t before = sel_block_scan((uint32_t)n_gt | ((uint32_t)n_eq << 16), scratch, &total);
-      int my_above = above_base + (int)(before & 0xffffu);
-      int my_tie = tie_base + (int)(before >> 16);
-      if (v < nvec) {
+      if (tie_base < need) {  // uniform: ties are taken in index order until `need` of them are in
+        int total;
+        int my_tie = tie_base + sel_block_scan(n_eq, misc + 8, &total);
+        if (v < nvec) {
 #pragma unroll
-        for (int j = 0; j < VEC; j++) {
-          const unsigned long long entry = ((unsigned long long)k[j] << 32) | (uint32_t)~(uint32_t)(v * VEC + j);
-          if (k[j] > kth) {
-            sorted[my_above++] = entry;
-          } else if (k[j] == kth) {
-            if (my_tie < need) sorted[n_above + my_tie] = entry;
-            my_tie++;
-          }
+          for (int j = 0; j < VEC; j++)
+            if (k[j] == kth) {
+              if (my_tie < need) cand[n_above + my_tie] = ((unsigned long long)kth << 32) | (uint32_t)~(uint32_t)(v * VEC + j);
+              my_tie++;
+            }
         }
+        tie_base += total;
       }
-      above_base += (int)(total & 0xffffu);
-      tie_base += (int)(total >> 16);
     }
+    __syncthreads();
+    n_cand = a.K;
   }
-  __syncthreads();
 
-  // ---- 4. bitonic sort, descending: larger key first, equal keys by ascending index ---------------
-  for (int k2 = 2; k2 <= a.Kp; k2 <<= 1) {
+  // ---- 4. bitonic sort, descending: larger key first, equal keys by ascending index; padding sorts last
+  int np = a.Kp;
+  while (np < n_cand) np <<= 1;
+  for (int i = n_cand + tid; i < np; i += kSelThreads) cand[i] = 0ull;
+  __syncthreads();
+  for (int k2 = 2; k2 <= np; k2 <<= 1) {
     for (int j = k2 >> 1; j > 0; j >>= 1) {
-      for (int i = tid; i < a.Kp; i += kSelThreads) {
-        const int partner = i ^ j;
-        if (partner > i) {
-          const unsigned long long x = sorted[i], y = sorted[partner];
-          const bool descending = (i & k2) == 0;
-          if (descending ? x < y : x > y) {
-            sorted[i] = y;
-            sorted[partner] = x;
-          }
+      for (int t = tid; t < (np >> 1); t += kSelThreads) {
+        const int i = 2 * t - (t & (j - 1));  // the lower index of the t-th pair at distance j
+        const int partner = i + j;
+        const unsigned long long x = cand[i], y = cand[partner];
+        const bool descending = (i & k2) == 0;
+        if (descending ? x < y : x > y) {
+          cand[i] = y;
+          cand[partner] = x;
         }
       }
       __syncthreads();
     }
   }
   for (int i = tid; i < a.K; i += kSelThreads) {
-    const unsigned long long e = sorted[i];
+    const unsigned long long e = cand[i];
     float val = SelKey<T>::value((uint32_t)(e >> 32));
     if (a.relu) val = val < 0.f ? 0.f : val;  // a NaN stays a NaN (fmaxf would hide it)
     store_scalar(a.vals, a.vals_dtype, (size_t)blockIdx.x * a.K + i, val);

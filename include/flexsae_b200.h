@@ -192,9 +192,12 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
  * (equal values: lower index first) -- the layout and order the loss entry points take.  The
  * reference has no counterpart: its losses start from indices and vals (its tests and example draw
  * them at random, tests/test_all_kernels.py:20-33, example.py:45-51) and a caller is left to run
- * torch.topk on the encoder output.  One launch,
- * no scratch memory; the selection is exact and deterministic (radix select + index-ordered
- * compaction + in-CTA sort).  relu != 0 clamps the reported values at zero.
+ * torch.topk on the encoder output.  One launch, no scratch memory; each row is read from HBM once
+ * (a second pass finds it in L2); the selection is exact and deterministic (a lower bound from 1024
+ * running maxima, an unordered candidate list, a total-order sort; a whole-row radix select for rows
+ * with masses of equal values).  A NaN counts as larger than every number, as in torch.topk; -0.0
+ * and +0.0 are equal (ordered by index, reported as +0.0).  relu != 0 clamps the reported values at
+ * zero (a NaN stays a NaN).
  * Needs F a multiple of 8 (16-bit activations) or 4 (fp32), acts 16-byte aligned, K <= min(F, 1024).
  */
 int flexsae_topk_select(const void* acts, int acts_dtype, int64_t B, int64_t F, int64_t K, int relu,
