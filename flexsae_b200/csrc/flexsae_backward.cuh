@@ -143,6 +143,9 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
   static_assert(kRingSlots == 2 * kUnroll, "the ring holds the batch in use and the batch in flight");
   // Shared memory: a per-lane ring of 2*U row pieces (each lane only ever reads back the 16 bytes
   // it copied itself, so no warp synchronisation is involved), then the staged step records.
+  // The kernels declare `smem` 128-byte aligned: a quarter-warp's 8 x 16 bytes then sit in one
+  // 128-byte line whatever static shared memory a kernel also has (an offset of 16 bytes made every
+  // ring access straddle two lines and cost 7 % of the backward's time).
   uint4* ring = smem + threadIdx.x;  // slot s of this lane: ring[s * kThreads]
   int2* staged = reinterpret_cast<int2*>(smem + kRingSlots * kThreads);
   int* staged_slot = reinterpret_cast<int*>(staged + UPC * a.KS);  // deterministic mode only
@@ -260,7 +263,7 @@ __device__ __forceinline__ void walk_units(const BwdArgs& a, int unit_block, int
 // spread evenly through the grid.
 template <typename T, int G, bool HIER, bool DET>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_kernel(const BwdArgs a) {
-  extern __shared__ uint4 smem[];  // ring, staged pairs [UPC][KS], then (deterministic mode) int slots[UPC][KS]
+  extern __shared__ __align__(128) uint4 smem[];  // ring, staged pairs [UPC][KS], then (deterministic mode) int slots[UPC][KS]
   int unit_block = blockIdx.x;
   if (!DET && a.conv_blocks > 0) {
     const int q = blockIdx.x / a.conv_stride;
@@ -362,7 +365,7 @@ __device__ __forceinline__ int role_index(int* ticket) {
 
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_pipelined_kernel(const PipeArgs pa) {
-  extern __shared__ uint4 smem[];
+  extern __shared__ __align__(128) uint4 smem[];
   const int bid = role_index(pa.ticket);
   const int per = pa.unit_blocks + pa.conv_blocks;
   const int p = bid / per;
@@ -430,7 +433,7 @@ __device__ __forceinline__ void take_chunks(const StealArgs& sa, int q, int limi
 
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_stealing_kernel(const StealArgs sa) {
-  extern __shared__ uint4 smem[];
+  extern __shared__ __align__(128) uint4 smem[];
   __shared__ int s_chunk, s_state;
   const PipeArgs& pa = sa.p;
   const int bid = role_index(pa.ticket);

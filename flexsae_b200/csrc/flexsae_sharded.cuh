@@ -406,7 +406,7 @@ __device__ __forceinline__ void exchange_slot(const ShardArgs& sa, int p, int ex
 //   converting blocks (inserted at conv_offset): slab of piece p-1 -> scattered to the owners, cleared.
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_kernel(const ShardArgs sa) {
-  extern __shared__ uint4 smem[];
+  extern __shared__ __align__(128) uint4 smem[];
   const PipeArgs& pa = sa.p;
   const int P = pa.pieces;
   const int E = sa.exch_blocks;
@@ -504,7 +504,7 @@ __device__ __forceinline__ void finish_scatter(const ShardArgs& sa, int q, int* 
 
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_stealing_kernel(const ShardArgs sa) {
-  extern __shared__ uint4 smem[];
+  extern __shared__ __align__(128) uint4 smem[];
   __shared__ int s_chunk, s_state;
   const PipeArgs& pa = sa.p;
   const int P = pa.pieces;
