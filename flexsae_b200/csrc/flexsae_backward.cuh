@@ -277,20 +277,29 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_k
 }
 
 // ---- single-launch pipelined backward ------------------------------------------------------------
-// All column pieces in ONE grid, ordered piece by piece.  Piece p's blocks are its unit blocks
-// with the blocks that convert piece p-1 inserted after the first quarter.  Two counters per
-// piece carry the only dependencies:
+// All column pieces in ONE grid, ordered slot by slot.  Slot p holds the unit blocks of piece p and,
+// inserted part-way, the blocks that convert piece p - conv_lag.  The fp32 slabs rotate: piece p
+// accumulates into slab p % nslabs.  Two counters per piece carry the only dependencies:
 //   converting blocks of piece q wait until all unit blocks of piece q have finished;
-//   unit blocks of piece p wait until piece p-2 (same slab) has been converted and cleared.
+//   unit blocks of piece p wait until piece p - nslabs (same slab) has been converted and cleared.
+// A unit block runs for about as long as a whole slot lasts, so the last unit blocks of piece q end
+// most of a slot after the first blocks of piece q+1 started; only then can piece q be converted, and
+// with two slabs piece q+2 had to wait for exactly that conversion: the chain walk -> convert -> walk
+// set the pace (70 us per piece at the headline shape against 51 us of work).  With three slabs and a
+// lag of two the conversion of piece q runs a slot later, finds its walk long finished, and has a whole
+// slot before anybody needs the slab back.
 // Every wait is on blocks with LOWER role indices, which start first (see role_index), so the
 // lowest unfinished block never waits on anything unfinished.  Waits are bounded in time (see
 // BoundedWait): a block that gives up sets FLEXSAE_STATUS_PIPELINE_TIMEOUT and carries on (the
 // result is then invalid but the GPU is not held).
+constexpr int kMaxSlabs = 4;
 struct PipeArgs {
   BwdArgs b;
-  float* slabs[2];
+  float* slabs[kMaxSlabs];
+  int nslabs;    // fp32 slabs in rotation: piece p accumulates into slab p % nslabs
+  int conv_lag;  // the converting blocks of slot p convert piece p - conv_lag (1 <= conv_lag < nslabs)
   int* walk_done;  // [pieces]
-  int* conv_done;  // [pieces]
+  int* conv_done;  // [pieces] (sharded kernel: per slot)
   int pieces, unit_blocks, conv_blocks, conv_offset;
   int* ticket;  // NULL: blocks take their roles by blockIdx.x; else by the order in which they start
   long long wait_ns;  // how long one wait may last before the block gives up (option "wait_limit_ms")
@@ -368,21 +377,23 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
   extern __shared__ __align__(128) uint4 smem[];
   const int bid = role_index(pa.ticket);
   const int per = pa.unit_blocks + pa.conv_blocks;
-  const int p = bid / per;
-  const int r = bid - p * per;
-  int conv_idx = -1, unit_block = -1;
-  if (p == pa.pieces) {
-    conv_idx = r;  // the trailing blocks convert the last piece
-  } else if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) {
-    conv_idx = r - pa.conv_offset;
+  const int body = pa.pieces * per;
+  int p, conv_idx = -1, unit_block = -1;
+  if (bid >= body) {  // conv_lag trailing slots: only converting blocks, for the last pieces
+    const int t = bid - body;
+    p = pa.pieces + t / pa.conv_blocks;
+    conv_idx = t - (p - pa.pieces) * pa.conv_blocks;
   } else {
-    unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
+    p = bid / per;
+    const int r = bid - p * per;
+    if (r >= pa.conv_offset && r < pa.conv_offset + pa.conv_blocks) conv_idx = r - pa.conv_offset;
+    else unit_block = r < pa.conv_offset ? r : r - pa.conv_blocks;
   }
   if (conv_idx >= 0) {
-    const int q = p - 1;
+    const int q = p - pa.conv_lag;
     if (q < 0) return;
     wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status, pa.wait_ns);
-    convert_slab<T, G, true>(pa.slabs[q & 1], pa.b.dweight, pa.b.F, pa.b.D, q, conv_idx, pa.conv_blocks);
+    convert_slab<T, G, true>(pa.slabs[q % pa.nslabs], pa.b.dweight, pa.b.F, pa.b.D, q, conv_idx, pa.conv_blocks);
     signal_done(pa.conv_done + q);
     return;
   }
@@ -393,80 +404,9 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_p
                                   smem);
     return;
   }
-  if (p >= 2) wait_count(pa.conv_done + (p - 2), pa.conv_blocks, pa.b.status, pa.wait_ns);
-  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
+  if (p >= pa.nslabs) wait_count(pa.conv_done + (p - pa.nslabs), pa.conv_blocks, pa.b.status, pa.wait_ns);
+  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p % pa.nslabs], smem);
   signal_done(pa.walk_done + p);
-}
-
-// ---- single-launch backward with a shared conversion queue --------------------------------------
-// Same pipeline, but no block is a converter by position.  The slab of a finished piece is cut into
-// `chunks` chunks behind a claim counter, and whoever is running takes them:
-//   a unit block that has finished its walk of piece p takes up to `exit_chunks` chunks of piece
-//     p-1 if that piece's walk is complete (it never waits for it);
-//   a unit block of piece p that finds piece p-2 (same slab) not fully converted yet takes chunks of
-//     it until none is left, then waits for the ones still in other blocks' hands;
-//   `tail` blocks after the last piece take whatever is left of the last two pieces.
-// So a conversion starts the moment its piece's last unit block finishes, at the rate at which
-// blocks retire, instead of when converter blocks placed at a fixed position become resident.
-// Every chunk that is waited for has been claimed by a running block that finishes it without
-// waiting, and a piece's walk depends only on lower block indices: no wait can be circular.
-struct StealArgs {
-  PipeArgs p;       // conv_blocks / conv_offset unused; conv_done counts finished chunks
-  int* claim;       // [pieces] next chunk of each piece's slab to hand out
-  int chunks;       // chunks per slab
-  int exit_chunks;  // chunks a unit block takes after its walk
-};
-
-template <typename T, int G>
-__device__ __forceinline__ void take_chunks(const StealArgs& sa, int q, int limit, int* s_chunk) {
-  const PipeArgs& pa = sa.p;
-  for (int n = 0; n < limit; n++) {
-    if (threadIdx.x == 0) *s_chunk = atomicAdd(sa.claim + q, 1);
-    __syncthreads();
-    const int c = *s_chunk;
-    __syncthreads();  // everyone has read the chunk number before thread 0 may overwrite it
-    if (c >= sa.chunks) break;
-    convert_slab<T, G, true>(pa.slabs[q & 1], pa.b.dweight, pa.b.F, pa.b.D, q, c, sa.chunks);
-    signal_done(pa.conv_done + q);
-  }
-}
-
-template <typename T, int G, bool HIER>
-__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_stealing_kernel(const StealArgs sa) {
-  extern __shared__ __align__(128) uint4 smem[];
-  __shared__ int s_chunk, s_state;
-  const PipeArgs& pa = sa.p;
-  const int bid = role_index(pa.ticket);
-  const int p = bid / pa.unit_blocks;
-  if (p >= pa.pieces) {  // tail: the last two pieces have no later unit blocks to convert them
-    for (int q = max(0, pa.pieces - 2); q < pa.pieces; q++) {
-      wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status, pa.wait_ns);
-      take_chunks<T, G>(sa, q, 0x7fffffff, &s_chunk);
-    }
-    return;
-  }
-  const int unit_block = bid - p * pa.unit_blocks;
-  if (p >= 2) {
-    if (threadIdx.x == 0) s_state = ld_acquire(pa.conv_done + (p - 2)) >= sa.chunks;
-    __syncthreads();
-    const bool converted = s_state != 0;
-    __syncthreads();
-    if (!converted) {  // this block's slab still holds piece p-2: help, then wait for the chunks in other hands
-      wait_count(pa.walk_done + (p - 2), pa.unit_blocks, pa.b.status, pa.wait_ns);
-      take_chunks<T, G>(sa, p - 2, 0x7fffffff, &s_chunk);
-      wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status, pa.wait_ns);
-    }
-  }
-  walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
-  signal_done(pa.walk_done + p);
-  if (p >= 1 && sa.exit_chunks > 0) {
-    if (threadIdx.x == 0)
-      s_state = ld_acquire(pa.walk_done + (p - 1)) >= pa.unit_blocks && ld_acquire(sa.claim + (p - 1)) < sa.chunks;
-    __syncthreads();
-    const bool open = s_state != 0;
-    __syncthreads();
-    if (open) take_chunks<T, G>(sa, p - 1, sa.exit_chunks, &s_chunk);
-  }
 }
 
 // Column sums of a [B, D] fp32 matrix over row blocks: part[rb][d] = sum of rows of block rb.

@@ -46,9 +46,8 @@ struct Options {
   int flag_fan_out = 0;         // sharded backward: a finished slot is announced by one thread per rank
   int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
   int ticket_order = 0;         // single-launch kernels: blocks take their roles in the order they start (atomic ticket)
-  int convert_steal = 0;        // single-launch backward: slab conversion taken in chunks by whichever blocks run
-  int steal_chunks = 1024;      // ... chunks per slab
-  int steal_exit_chunks = 1;    // ... chunks a unit block takes after its walk
+  int slabs = 2;                // fp32 accumulation slabs in rotation (2..4)
+  int convert_lag = 1;          // slot p converts the slab of piece p - convert_lag (1 .. slabs-1)
   int wait_limit_ms = 5000;     // how long one in-kernel wait (for other blocks, for other GPUs) may last
 };
 static Options g_opt;
@@ -165,6 +164,11 @@ static int check_segments(int kind, const Shape& s, int segments, int* KS, int* 
 constexpr int kMaxRowBlocks = 128;  // partial rows of the dbias column sums
 constexpr int kConvertBlocks = FLEXSAE_CONVERT_BLOCKS;  // CTAs per piece that convert the previous piece's slab
 
+// Counters of the single-launch kernels: four arrays of one int per slot (a launch has at most
+// pieces + kMaxSlabs + 1 slots) and the ticket.
+static size_t counter_stride(int pieces) { return (size_t)pieces + kMaxSlabs + 2; }
+static size_t counter_ints(int pieces) { return 4 * counter_stride(pieces) + 2; }
+
 struct BwdPlan {
   int G, PW, pieces, row_blocks, rows_per_block;
   size_t slab_bytes, off_slab, off_dv, off_db, off_s0, off_ctr, off_index, off_stage, off_part, total;
@@ -180,9 +184,9 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   if (p.rows_per_block < 32) p.rows_per_block = 32;
   p.row_blocks = (int)((s.B + p.rows_per_block - 1) / p.rows_per_block);
   size_t off = 0;
-  p.off_slab = off;  // two slabs: one accumulating, one being converted
+  p.off_slab = off;  // the slabs in rotation: one accumulating, the others being converted or waiting for it
   p.slab_bytes = dw_mode == FLEXSAE_DW_ATOMIC ? align_up((size_t)s.F * p.PW * 4, 256) : 0;
-  off += 2 * p.slab_bytes;
+  off += (size_t)g_opt.slabs * p.slab_bytes;
   p.off_index = p.off_stage = p.off_part = off;
   if (dw_mode == FLEXSAE_DW_DETERMINISTIC) {
     const int64_t n = s.B * s.K;
@@ -199,7 +203,7 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   p.off_s0 = off;  // summed prefix residuals of every row (Hierarchical; TopK does not use it)
   off = align_up(off + (size_t)s.B * s.D * 4, 256);
   p.off_ctr = off;  // per-piece completion counters of the single-launch pipeline
-  off = align_up(off + (size_t)(4 * p.pieces + 10) * 4, 256);
+  off = align_up(off + counter_ints(p.pieces) * 4, 256);
   p.total = off;
   return p;
 }
@@ -284,31 +288,36 @@ static cudaError_t launch_bwd(BwdArgs a, cudaStream_t st) {
   return cudaGetLastError();
 }
 
+static void fill_pipe_args(PipeArgs& pa, const BwdArgs& b, float* const* slabs, int* counters, int pieces, int UPC) {
+  pa.b = b;
+  for (int i = 0; i < kMaxSlabs; i++) pa.slabs[i] = i < g_opt.slabs ? slabs[i] : nullptr;
+  pa.nslabs = g_opt.slabs;
+  pa.conv_lag = g_opt.convert_lag;
+  pa.walk_done = counters;
+  pa.conv_done = counters + counter_stride(pieces);
+  pa.ticket = g_opt.ticket_order ? counters + 4 * counter_stride(pieces) : nullptr;
+  pa.pieces = pieces;
+  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
+  const long long units = (long long)b.B * b.NS;
+  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
+}
+
 template <typename T, int G, bool HIER>
-static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
-                                        bool direct, cudaStream_t st) {
+static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* const* slabs, int* counters, int pieces, bool direct,
+                                        cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
   const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
   auto kern = decoder_loss_bwd_pipelined_kernel<T, G, HIER>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   PipeArgs pa;
-  pa.b = b;
-  pa.slabs[0] = slab0;
-  pa.slabs[1] = slab1;
-  pa.walk_done = counters;
-  pa.conv_done = counters + pieces;
-  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
-  pa.pieces = pieces;
-  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
-  const long long units = (long long)b.B * b.NS;
-  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
+  fill_pipe_args(pa, b, slabs, counters, pieces, UPC);
   const long long items = (long long)b.F * G;
   int conv = (int)((items + kThreads * 4 - 1) / (kThreads * 4));
   if (conv > kConvertBlocks) conv = kConvertBlocks;
   if (direct) conv = 0;
   pa.conv_blocks = conv;
   pa.conv_offset = (int)((long long)pa.unit_blocks * g_opt.convert_offset_pct / 100);
-  const long long blocks = (long long)pieces * (pa.unit_blocks + conv) + conv;
+  const long long blocks = (long long)pieces * (pa.unit_blocks + conv) + (long long)pa.conv_lag * conv;
   if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
   kern<<<(unsigned)blocks, kThreads, smem, st>>>(pa);
   t_launches++;
@@ -316,61 +325,16 @@ static cudaError_t launch_bwd_pipelined(const BwdArgs& b, float* slab0, float* s
 }
 
 template <typename T, int G, bool HIER>
-static cudaError_t launch_bwd_stealing(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
-                                       cudaStream_t st) {
-  constexpr int UPC = groups_per_cta(G);
-  const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
-  auto kern = decoder_loss_bwd_stealing_kernel<T, G, HIER>;
-  if (cudaError_t e = allow_smem(kern, smem)) return e;
-  StealArgs sa;
-  PipeArgs& pa = sa.p;
-  pa.b = b;
-  pa.slabs[0] = slab0;
-  pa.slabs[1] = slab1;
-  pa.walk_done = counters;
-  pa.conv_done = counters + pieces;
-  sa.claim = counters + 2 * pieces + 3;
-  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
-  pa.pieces = pieces;
-  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
-  const long long units = (long long)b.B * b.NS;
-  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
-  pa.conv_blocks = pa.conv_offset = 0;
-  const long long items = (long long)b.F * G;
-  long long chunks = (items + kThreads * 4 - 1) / (kThreads * 4);
-  if (chunks > g_opt.steal_chunks) chunks = g_opt.steal_chunks;
-  sa.chunks = (int)chunks;
-  sa.exit_chunks = g_opt.steal_exit_chunks;
-  const int tail = sa.chunks < kConvertBlocks ? sa.chunks : kConvertBlocks;
-  const long long blocks = (long long)pieces * pa.unit_blocks + tail;
-  if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
-  t_launches++;
-  return cudaGetLastError();
-}
-
-template <typename T, int G, bool HIER>
-static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
-                                      ShardArgs sa, cudaStream_t st) {
+static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* const* slabs, int* counters, int pieces, ShardArgs sa,
+                                      cudaStream_t st) {
   constexpr int UPC = groups_per_cta(G);
   const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
   auto kern = decoder_loss_bwd_sharded_kernel<T, G, HIER>;
   if (cudaError_t e = allow_smem(kern, smem)) return e;
   PipeArgs& pa = sa.p;
-  pa.b = b;
-  pa.slabs[0] = slab0;
-  pa.slabs[1] = slab1;
-  pa.walk_done = counters;
-  pa.conv_done = counters + pieces;       // one counter per slot: pieces + 3 of them
-  sa.slot_done = counters + 2 * pieces + 3;  // and pieces + 3 more
-  sa.scatter_done = counters + 3 * pieces + 6;  // and again
-  sa.claim = nullptr;
-  sa.chunks = sa.exit_chunks = sa.tail_blocks = 0;
-  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
-  pa.pieces = pieces;
-  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
-  const long long units = (long long)b.B * b.NS;
-  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
+  fill_pipe_args(pa, b, slabs, counters, pieces, UPC);           // conv_done: one counter per slot here
+  sa.slot_done = counters + 2 * counter_stride(pieces);
+  sa.scatter_done = counters + 3 * counter_stride(pieces);
   const long long items = (long long)b.F * G;
   int conv = (int)((items + kThreads * 4 - 1) / (kThreads * 4));
   const int conv_cap = g_opt.sharded_convert_blocks > 0 ? g_opt.sharded_convert_blocks : kConvertBlocks;
@@ -383,45 +347,8 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* slab0, float* sla
   if (sa.exch_offset > pa.conv_offset) sa.exch_offset = pa.conv_offset;
   sa.rotate = g_opt.scatter_rotate;
   sa.fan_out = g_opt.flag_fan_out;
-  const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks + conv) + 3ll * (sa.exch_blocks + conv);
-  if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
-  kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
-  t_launches++;
-  return cudaGetLastError();
-}
-
-template <typename T, int G, bool HIER>
-static cudaError_t launch_bwd_sharded_stealing(const BwdArgs& b, float* slab0, float* slab1, int* counters, int pieces,
-                                               ShardArgs sa, cudaStream_t st) {
-  constexpr int UPC = groups_per_cta(G);
-  const size_t smem = kRingBytes + (size_t)UPC * b.KS * sizeof(int2);
-  auto kern = decoder_loss_bwd_sharded_stealing_kernel<T, G, HIER>;
-  if (cudaError_t e = allow_smem(kern, smem)) return e;
-  PipeArgs& pa = sa.p;
-  pa.b = b;
-  pa.slabs[0] = slab0;
-  pa.slabs[1] = slab1;
-  pa.walk_done = counters;
-  pa.conv_done = counters + pieces;          // finished chunks per piece
-  sa.slot_done = counters + 2 * pieces + 3;
-  sa.scatter_done = nullptr;
-  sa.claim = counters + 3 * pieces + 6;      // next chunk per piece
-  pa.ticket = g_opt.ticket_order ? counters + 4 * pieces + 9 : nullptr;
-  pa.pieces = pieces;
-  pa.wait_ns = (long long)g_opt.wait_limit_ms * 1000000ll;
-  const long long units = (long long)b.B * b.NS;
-  pa.unit_blocks = (int)((units + UPC - 1) / UPC);
-  pa.conv_blocks = pa.conv_offset = 0;
-  long long chunks = ((long long)b.F * G + kThreads * 4 - 1) / (kThreads * 4);
-  if (chunks > g_opt.steal_chunks) chunks = g_opt.steal_chunks;
-  sa.chunks = (int)chunks;
-  sa.exit_chunks = g_opt.steal_exit_chunks;
-  sa.tail_blocks = sa.chunks < kConvertBlocks ? sa.chunks : kConvertBlocks;
-  sa.exch_blocks = g_opt.exchange_blocks;
-  sa.exch_offset = (int)((long long)pa.unit_blocks * g_opt.exchange_offset_pct / 100);
-  sa.rotate = g_opt.scatter_rotate;
-  sa.fan_out = g_opt.flag_fan_out;
-  const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks) + 3ll * (sa.exch_blocks + sa.tail_blocks);
+  const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks + conv) +
+                           (long long)(pa.conv_lag + 2) * (sa.exch_blocks + conv);
   if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
   kern<<<(unsigned)blocks, kThreads, smem, st>>>(sa);
   t_launches++;
@@ -446,7 +373,7 @@ using namespace flexsae;
 
 extern "C" {
 
-int flexsae_version(void) { return 200; }
+int flexsae_version(void) { return 300; }
 
 const char* flexsae_last_error(void) { return t_err; }
 
@@ -460,10 +387,13 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "l2_budget_mb") && value >= 1 && value <= 4096) { g_opt.l2_budget_mb = (int)value; return 0; }
   if (!strcmp(name, "segments") && value >= 0 && value <= 256) { g_opt.segments = (int)value; return 0; }
   if (!strcmp(name, "pipeline") && (value == 0 || value == 1)) { g_opt.pipeline = (int)value; return 0; }
-  if (!strcmp(name, "convert_steal") && (value == 0 || value == 1)) { g_opt.convert_steal = (int)value; return 0; }
+  if (!strcmp(name, "slabs") && value >= 2 && value <= kMaxSlabs) {
+    g_opt.slabs = (int)value;
+    if (g_opt.convert_lag > g_opt.slabs - 1) g_opt.convert_lag = g_opt.slabs - 1;
+    return 0;
+  }
+  if (!strcmp(name, "convert_lag") && value >= 1 && value <= g_opt.slabs - 1) { g_opt.convert_lag = (int)value; return 0; }
   if (!strcmp(name, "ticket_order") && (value == 0 || value == 1)) { g_opt.ticket_order = (int)value; return 0; }
-  if (!strcmp(name, "steal_chunks") && value >= 1 && value <= 65536) { g_opt.steal_chunks = (int)value; return 0; }
-  if (!strcmp(name, "steal_exit_chunks") && value >= 0 && value <= 64) { g_opt.steal_exit_chunks = (int)value; return 0; }
   if (!strcmp(name, "convert_offset_pct") && value >= 0 && value <= 100) { g_opt.convert_offset_pct = (int)value; return 0; }
   if (!strcmp(name, "direct_f32") && (value == 0 || value == 1)) { g_opt.direct_f32 = (int)value; return 0; }
   if (!strcmp(name, "exchange_blocks") && value >= 1 && value <= 4096) { g_opt.exchange_blocks = (int)value; return 0; }
@@ -483,10 +413,9 @@ int64_t flexsae_get_option(const char* name) {
   if (!strcmp(name, "l2_budget_mb")) return g_opt.l2_budget_mb;
   if (!strcmp(name, "segments")) return g_opt.segments;
   if (!strcmp(name, "pipeline")) return g_opt.pipeline;
-  if (!strcmp(name, "convert_steal")) return g_opt.convert_steal;
+  if (!strcmp(name, "slabs")) return g_opt.slabs;
+  if (!strcmp(name, "convert_lag")) return g_opt.convert_lag;
   if (!strcmp(name, "ticket_order")) return g_opt.ticket_order;
-  if (!strcmp(name, "steal_chunks")) return g_opt.steal_chunks;
-  if (!strcmp(name, "steal_exit_chunks")) return g_opt.steal_exit_chunks;
   if (!strcmp(name, "convert_offset_pct")) return g_opt.convert_offset_pct;
   if (!strcmp(name, "direct_f32")) return g_opt.direct_f32;
   if (!strcmp(name, "exchange_blocks")) return g_opt.exchange_blocks;
@@ -608,7 +537,8 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
 
   BwdArgs a;
   a.indices = indices; a.weight = weight; a.vals = vals; a.state = state; a.grad_out = grad_out;
-  float* slabs[2] = {reinterpret_cast<float*>(ws + p.off_slab), reinterpret_cast<float*>(ws + p.off_slab + p.slab_bytes)};
+  float* slabs[kMaxSlabs];
+  for (int i = 0; i < kMaxSlabs; i++) slabs[i] = reinterpret_cast<float*>(ws + p.off_slab + (size_t)(i < g_opt.slabs ? i : 0) * p.slab_bytes);
   a.dweight = dweight;
   a.stage = nullptr;
   a.slot_of = nullptr;
@@ -656,12 +586,12 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     e = cudaMemsetAsync(dweight, 0, (size_t)F * D * sizeof(float), st);
     a.slab_stride = (int)D;
   } else {
-    e = cudaMemsetAsync(slabs[0], 0, 2 * p.slab_bytes, st);
+    e = cudaMemsetAsync(slabs[0], 0, (size_t)g_opt.slabs * p.slab_bytes, st);
   }
   if (e != cudaSuccess) return fail((int)e, "gradient clear failed: %s", cudaGetErrorString(e));
   if (peers) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
-    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 10) * 4, st);
+    e = cudaMemsetAsync(counters, 0, counter_ints(p.pieces) * 4, st);
     if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
     a.piece = a.conv_piece = -1;
     a.slab = a.conv_slab = nullptr;
@@ -680,26 +610,20 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
       sa.flags_at[r] = r < peers->world ? reinterpret_cast<int*>(peers->flags[r]) : nullptr;
       sa.dweight_at[r] = (peers->dweight && r < peers->world) ? peers->dweight[r] : nullptr;
     }
-#define CALL_SHARD(T, G, H) launch_bwd_sharded<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, sa, st)
-#define CALL_SHARD_STEAL(T, G, H) launch_bwd_sharded_stealing<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, sa, st)
-    if (g_opt.convert_steal && !sa.mc_inbox) e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD_STEAL);
-    else e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD);
-#undef CALL_SHARD_STEAL
+#define CALL_SHARD(T, G, H) launch_bwd_sharded<T, G, H>(a, slabs, counters, p.pieces, sa, st)
+    e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_SHARD);
 #undef CALL_SHARD
     if (e != cudaSuccess) return fail((int)e, "sharded backward launch failed: %s", cudaGetErrorString(e));
   } else if (g_opt.pipeline) {
     int* counters = reinterpret_cast<int*>(ws + p.off_ctr);
-    e = cudaMemsetAsync(counters, 0, (size_t)(4 * p.pieces + 10) * 4, st);
+    e = cudaMemsetAsync(counters, 0, counter_ints(p.pieces) * 4, st);
     if (e != cudaSuccess) return fail((int)e, "counter clear failed: %s", cudaGetErrorString(e));
     a.piece = a.conv_piece = -1;
     a.slab = a.conv_slab = nullptr;
     a.unit_blocks = a.conv_blocks = 0;
     a.conv_stride = 1;
-#define CALL_PIPE(T, G, H) launch_bwd_pipelined<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, direct, st)
-#define CALL_STEAL(T, G, H) launch_bwd_stealing<T, G, H>(a, slabs[0], slabs[1], counters, p.pieces, st)
-    if (g_opt.convert_steal && !direct) e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_STEAL);
-    else e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_PIPE);
-#undef CALL_STEAL
+#define CALL_PIPE(T, G, H) launch_bwd_pipelined<T, G, H>(a, slabs, counters, p.pieces, direct, st)
+    e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_PIPE);
 #undef CALL_PIPE
     if (e != cudaSuccess) return fail((int)e, "pipelined backward launch failed: %s", cudaGetErrorString(e));
   } else
@@ -919,7 +843,7 @@ int flexsae_sort_by_decoder_row(const int64_t* indices, int64_t n, int64_t F, vo
 int flexsae_shard_slots(int64_t F, int64_t D, int weight_dtype) {
   Shape s{1, 1, F, D};
   if (check_shape(FLEXSAE_HIER, s, weight_dtype)) return 0;
-  return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC).pieces + 3;
+  return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC).pieces + kMaxSlabs + 1;  // an upper bound of the launch's slots for any lag
 }
 
 // ---- forward for callers that cannot provide scratch memory ------------------------------------

@@ -11,20 +11,21 @@ namespace flexsae {
 // blocks of the single-launch pipeline do the cross-GPU sum of dweight themselves, piece by piece,
 // overlapped with the accumulation of the following pieces.  All traffic between GPUs is posted
 // STORES into the peers' buffers (a remote load would stall its thread for microseconds; a store
-// does not), all loads are local:
-//   slot p converts the local slab of piece p-1 (decoder dtype) and SCATTERS it: every decoder row
-//     goes to the inbox of the rank that owns that row block (reduce-scatter by push),
-//   reduces piece p-2: this rank sums the N inbox copies of ITS row block (fixed rank order, fp32),
+// does not), all loads are local.  With L = conv_lag, slot p
+//   accumulates piece p (unit blocks) into slab p % nslabs,
+//   converts the local slab of piece p-L (decoder dtype) and SCATTERS it: every decoder row goes to
+//     the inbox of the rank that owns that row block (reduce-scatter by push),
+//   reduces piece p-L-1: this rank sums the N inbox copies of ITS row block (fixed rank order, fp32),
 //     writes its own dweight rows and BROADCASTS the reduced rows into every peer's gather buffer,
-//   copies piece p-3: the other ranks' reduced row blocks from the local gather buffer to dweight.
+//   copies piece p-L-2: the other ranks' reduced row blocks from the local gather buffer to dweight.
 // Two flags per (rank, peer) carry all cross-GPU ordering.  When the last converting block of slot p
 // finishes, the rank publishes seq_base + p in its SCATTER flag on every rank; when the last exchange
 // block of slot p finishes, the same in its EXCHANGE flag.  Who waits for what:
-//   converting blocks of slot p (they overwrite the inbox half that held piece p-3): every rank's
-//     exchange flag >= slot p-1, i.e. the owners have reduced piece p-3;
-//   exchange blocks of slot p: every rank's scatter flag >= slot p-1 (the inbox copies of piece p-2
-//     are complete) and, because the gather buffer is double-buffered as well, every rank's exchange
-//     flag >= slot p-1 (piece p-3 has been broadcast, piece p-4 copied out).
+//   converting blocks of slot p (they overwrite the inbox half that the reduce of slot p-1 read):
+//     every rank's exchange flag >= slot p-1;
+//   exchange blocks of slot p: every rank's scatter flag >= slot p-1 (the inbox copies of the piece
+//     they reduce are complete) and, because the gather buffer is double-buffered as well, every
+//     rank's exchange flag >= slot p-1 (the previous piece has been broadcast, the one before copied).
 // A rank publishes its flags strictly in slot order (the last block of slot p first waits for the
 // rank's own flag of slot p-1), so a flag value really means "all slots up to this one".
 // With peer-mapped dweight tables there is no gather buffer and the exchange blocks wait for the
@@ -40,8 +41,6 @@ struct ShardArgs {
   int world, rank, rows_per_rank, seq_base;
   int exch_blocks;  // blocks per slot that reduce / broadcast / copy older pieces
   int exch_offset;  // unit blocks of a slot dispatched before its exchange blocks (<= conv_offset)
-  int* claim;       // shared scatter queue: [pieces] next chunk of each slab to hand out (else unused)
-  int chunks, exit_chunks, tail_blocks;  // ... chunks per slab, chunks a unit block takes after its walk, trailing blocks
   int rotate;       // 1: each rank starts its scatter sweep at its right-hand neighbour's row block
   int fan_out;      // 1: the flags of a finished slot are stored by one thread per destination rank
   void* mc_inbox;     // multicast address of the inbox region of ALL ranks (NULL: plain peer stores)
@@ -373,42 +372,45 @@ __device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scat
 // complete, reduce + broadcast piece p-2, copy piece p-3 out of the gather buffer.
 template <typename T, int G>
 __device__ __forceinline__ void exchange_slot(const ShardArgs& sa, int p, int exch_idx, int exch_n, bool in_place) {
-  const int P = sa.p.pieces;
+  const int P = sa.p.pieces, L = sa.p.conv_lag;
+  const int reduce_piece = p - L - 1, copy_piece = p - L - 2;
+  const int last_slot = P + L + 1, last_scatter_slot = P + L - 1;
   FLEXSAE_TRACE_MIN(p, kTrExchEntry);
-  // the inbox copies of piece p-2 are complete (the last scatter belongs to slot P); through the
-  // gather buffer also: piece p-3 has arrived in it and piece p-4 has been copied out everywhere;
+  // the inbox copies of the piece to reduce are complete (scattered in slot p-1); through the gather
+  // buffer also: the previous piece has arrived in it and the one before has been copied out everywhere;
   // in place: the very last slot returns only when every rank's last broadcast has landed here
-  if (p >= 2) wait_peers(sa, !in_place || p == P + 2, sa.seq_base + p - 1, true, sa.seq_base + min(p - 1, P));
+  if (p >= 2) wait_peers(sa, !in_place || p == last_slot, sa.seq_base + p - 1, true, sa.seq_base + min(p - 1, last_scatter_slot));
   FLEXSAE_TRACE_MIN(p, kTrExchStart);
-  if (p >= 2 && p - 2 < P && sa.mc_inbox) {
-    switch_reduce_broadcast<T, G>(sa, p - 2, exch_idx, exch_n);
-  } else if (p >= 2 && p - 2 < P) {
+  if (reduce_piece >= 0 && reduce_piece < P && sa.mc_inbox) {
+    switch_reduce_broadcast<T, G>(sa, reduce_piece, exch_idx, exch_n);
+  } else if (reduce_piece >= 0 && reduce_piece < P) {
     if (in_place) {
-      if (sa.world <= 2) reduce_broadcast<T, G, 4, true>(sa, p - 2, exch_idx, exch_n);
-      else if (sa.world <= 4) reduce_broadcast<T, G, 2, true>(sa, p - 2, exch_idx, exch_n);
-      else reduce_broadcast<T, G, 1, true>(sa, p - 2, exch_idx, exch_n);
+      if (sa.world <= 2) reduce_broadcast<T, G, 4, true>(sa, reduce_piece, exch_idx, exch_n);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2, true>(sa, reduce_piece, exch_idx, exch_n);
+      else reduce_broadcast<T, G, 1, true>(sa, reduce_piece, exch_idx, exch_n);
     } else {
-      if (sa.world <= 2) reduce_broadcast<T, G, 4, false>(sa, p - 2, exch_idx, exch_n);
-      else if (sa.world <= 4) reduce_broadcast<T, G, 2, false>(sa, p - 2, exch_idx, exch_n);
-      else reduce_broadcast<T, G, 1, false>(sa, p - 2, exch_idx, exch_n);
+      if (sa.world <= 2) reduce_broadcast<T, G, 4, false>(sa, reduce_piece, exch_idx, exch_n);
+      else if (sa.world <= 4) reduce_broadcast<T, G, 2, false>(sa, reduce_piece, exch_idx, exch_n);
+      else reduce_broadcast<T, G, 1, false>(sa, reduce_piece, exch_idx, exch_n);
     }
   }
-  // in-place broadcast: nothing to copy, but slot pieces+2 still waits (above) until every rank's
+  // in-place broadcast: nothing to copy, but the last slot still waits (above) until every rank's
   // last broadcast has landed in this rank's dweight
-  if (p >= 3 && p - 3 < P && !in_place) copy_gathered<T, G>(sa, p - 3, exch_idx, exch_n);
+  if (copy_piece >= 0 && copy_piece < P && !in_place) copy_gathered<T, G>(sa, copy_piece, exch_idx, exch_n);
 }
 
-// Block roles inside slot p of the sharded launch (slots 0..pieces+2):
+// Block roles inside slot p of the sharded launch (slots 0 .. pieces + conv_lag + 1):
 //   exchange blocks (sa.exch_blocks, after the first sa.exch_offset unit blocks): reduce + broadcast
-//     of piece p-2 and the copy of piece p-3 -- local loads and posted stores only, so a few blocks
-//     keep up; placed a little into the slot so that what they wait for has usually arrived;
+//     and copy of older pieces -- local loads and posted stores only, so a few blocks keep up;
 //   unit blocks: accumulate piece p;
-//   converting blocks (inserted at conv_offset): slab of piece p-1 -> scattered to the owners, cleared.
+//   converting blocks (inserted at conv_offset): slab of piece p - conv_lag -> scattered to the owners, cleared.
+// The conv_lag + 2 draining slots after the last piece have no unit blocks; their blocks are exchange
+// blocks, except that the first conv_lag of them still hold the converting blocks of the last pieces.
 template <typename T, int G, bool HIER>
 __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_kernel(const ShardArgs sa) {
   extern __shared__ __align__(128) uint4 smem[];
   const PipeArgs& pa = sa.p;
-  const int P = pa.pieces;
+  const int P = pa.pieces, L = pa.conv_lag;
   const int E = sa.exch_blocks;
   const int per = E + pa.unit_blocks + pa.conv_blocks;
   const int body = P * per;
@@ -416,16 +418,16 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   int exch_n = E;  // blocks that share the exchange work of this slot
   const bool in_place = sa.dweight_at[0] != nullptr && sa.mc_inbox == nullptr;
   const int bid = role_index(pa.ticket);
-  if (bid >= body) {  // three draining slots: no unit blocks, so every block helps with the exchange
+  if (bid >= body) {  // draining slots: no unit blocks
     const int t = bid - body;
     const int dper = E + pa.conv_blocks;
     p = P + t / dper;
     const int r = t - (p - P) * dper;
-    if (p == P && r >= E) {
-      conv_idx = r - E;  // slot P still has the last slab to convert
+    if (p < P + L && r >= E) {
+      conv_idx = r - E;  // the last conv_lag slabs are still to be converted
     } else {
       exch_idx = r;
-      exch_n = (p == P) ? E : dper;
+      exch_n = (p < P + L) ? E : dper;  // afterwards every block helps with the exchange
     }
   } else {
     p = bid / per;
@@ -441,21 +443,23 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
     }
   }
   if (unit_block >= 0) {
-    if (p >= 2) wait_count(pa.conv_done + (p - 1), pa.conv_blocks, pa.b.status, pa.wait_ns);  // slot p-1 cleared this slab
+    // this slab last held piece p - nslabs, which the converting blocks of slot p - nslabs + L cleared
+    if (p >= pa.nslabs) wait_count(pa.conv_done + (p - pa.nslabs + L), pa.conv_blocks, pa.b.status, pa.wait_ns);
     FLEXSAE_TRACE_MIN(p, kTrUnitStart);
-    walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
+    walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p % pa.nslabs], smem);
     signal_done(pa.walk_done + p);
     FLEXSAE_TRACE_MAX(p, kTrUnitEnd);
     return;
   }
   if (conv_idx >= 0) {
     FLEXSAE_TRACE_MIN(p, kTrConvEntry);
-    if (p >= 1 && p - 1 < P) {
-      wait_count(pa.walk_done + (p - 1), pa.unit_blocks, pa.b.status, pa.wait_ns);  // the local slab is complete
+    const int q = p - L;
+    if (q >= 0 && q < P) {
+      wait_count(pa.walk_done + q, pa.unit_blocks, pa.b.status, pa.wait_ns);  // the local slab is complete
       wait_peers(sa, true, sa.seq_base + p - 1, false, 0);  // the owners have reduced what this half of their inbox held
       FLEXSAE_TRACE_MIN(p, kTrConvStart);
-      if (sa.mc_inbox) slab_to_own_copy<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
-      else slab_scatter<T, G>(pa.slabs[(p - 1) & 1], sa, p - 1, conv_idx, pa.conv_blocks);
+      if (sa.mc_inbox) slab_to_own_copy<T, G>(pa.slabs[q % pa.nslabs], sa, q, conv_idx, pa.conv_blocks);
+      else slab_scatter<T, G>(pa.slabs[q % pa.nslabs], sa, q, conv_idx, pa.conv_blocks);
     }
     signal_done(pa.conv_done + p);
     FLEXSAE_TRACE_MAX(p, kTrConvEnd);
@@ -465,113 +469,9 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   __syncthreads();
   if (exch_idx >= 0) { FLEXSAE_TRACE_MAX(p, kTrExchEnd); }
   const bool scatter = conv_idx >= 0;
-  count_and_publish(sa, scatter, (scatter ? sa.scatter_done : sa.slot_done) + p, scatter ? pa.conv_blocks : exch_n, p,
-                    scatter && p == 0);
-}
-
-// ---- the sharded backward with a shared scatter queue ---------------------------------------------
-// As decoder_loss_bwd_stealing_kernel: no converting blocks at a fixed position.  The scatter of a
-// finished slab (piece q) is cut into sa.chunks chunks behind a claim counter and taken by
-//   unit blocks of piece q+1 after their walk (if piece q's walk is complete and every owner has
-//     reduced what that half of its inbox held -- checked, never waited for),
-//   unit blocks of piece q+2 before their walk, when they find their slab still occupied,
-//   exchange blocks of slot q+2 before they wait for that very scatter, and trailing blocks in slot P
-//     for the last two pieces,
-// so every wait is for chunks already in the hands of running blocks or for lower role indices.  The
-// block that completes a slab's last chunk publishes the rank's scatter flag (value of slot q+1).
-template <typename T, int G>
-__device__ __forceinline__ void take_scatter_chunks(const ShardArgs& sa, int q, int limit, int* s_chunk) {
-  const PipeArgs& pa = sa.p;
-  for (int n = 0; n < limit; n++) {
-    if (threadIdx.x == 0) *s_chunk = atomicAdd(sa.claim + q, 1);
-    __syncthreads();
-    const int c = *s_chunk;
-    __syncthreads();  // everyone has read the chunk number before thread 0 may overwrite it
-    if (c >= sa.chunks) break;
-    slab_scatter<T, G>(pa.slabs[q & 1], sa, q, c, sa.chunks);
-    // conv_done[q] gates the unit blocks that reuse the slab and, when full, the scatter flag of slot q+1
-    count_and_publish(sa, true, pa.conv_done + q, sa.chunks, q + 1, q == 0);
-  }
-}
-
-// wait until piece q may be scattered (its walk is complete, the owners have reduced piece q-2), then take what is left
-template <typename T, int G>
-__device__ __forceinline__ void finish_scatter(const ShardArgs& sa, int q, int* s_chunk) {
-  wait_count(sa.p.walk_done + q, sa.p.unit_blocks, sa.p.b.status, sa.p.wait_ns);
-  wait_peers(sa, true, sa.seq_base + q, false, 0);
-  take_scatter_chunks<T, G>(sa, q, 0x7fffffff, s_chunk);
-}
-
-template <typename T, int G, bool HIER>
-__global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_sharded_stealing_kernel(const ShardArgs sa) {
-  extern __shared__ __align__(128) uint4 smem[];
-  __shared__ int s_chunk, s_state;
-  const PipeArgs& pa = sa.p;
-  const int P = pa.pieces;
-  const int E = sa.exch_blocks;
-  const int per = E + pa.unit_blocks;
-  const int body = P * per;
-  const bool in_place = sa.dweight_at[0] != nullptr;
-  const int bid = role_index(pa.ticket);
-  int p, exch_idx = -1, unit_block = -1, exch_n = E;
-  bool tail = false;
-  if (bid >= body) {
-    const int t = bid - body;
-    const int dper = E + sa.tail_blocks;
-    p = P + t / dper;
-    const int r = t - (p - P) * dper;
-    if (p == P && r >= E) {
-      tail = true;
-    } else {
-      exch_idx = r;
-      exch_n = (p == P) ? E : dper;
-    }
-  } else {
-    p = bid / per;
-    const int r = bid - p * per;
-    if (r < sa.exch_offset) unit_block = r;
-    else if (r < sa.exch_offset + E) exch_idx = r - sa.exch_offset;
-    else unit_block = r - E;
-  }
-  if (tail) {
-    for (int q = max(0, P - 2); q < P; q++) finish_scatter<T, G>(sa, q, &s_chunk);
-    return;
-  }
-  if (unit_block >= 0) {
-    if (p >= 2) {
-      if (threadIdx.x == 0) s_state = ld_acquire(pa.conv_done + (p - 2)) >= sa.chunks;
-      __syncthreads();
-      const bool free_slab = s_state != 0;
-      __syncthreads();
-      if (!free_slab) {  // this block's slab still holds piece p-2: help, then wait for the chunks in other hands
-        finish_scatter<T, G>(sa, p - 2, &s_chunk);
-        wait_count(pa.conv_done + (p - 2), sa.chunks, pa.b.status, pa.wait_ns);
-      }
-    }
-    FLEXSAE_TRACE_MIN(p, kTrUnitStart);
-    walk_units<T, G, HIER, false>(pa.b, unit_block, p, pa.slabs[p & 1], smem);
-    signal_done(pa.walk_done + p);
-    FLEXSAE_TRACE_MAX(p, kTrUnitEnd);
-    if (p >= 1 && sa.exit_chunks > 0) {
-      // may piece p-1 be scattered right now?  its walk complete, chunks left, and every owner done with
-      // the inbox half it goes to: one thread per rank looks at that rank's exchange flag
-      const int q = p - 1;
-      bool ok = true;
-      if ((int)threadIdx.x < sa.world)
-        ok = ld_acquire_sys(sa.flags_at[sa.rank] + threadIdx.x) - (sa.seq_base + q) >= 0;
-      else if ((int)threadIdx.x == 32)
-        ok = ld_acquire(pa.walk_done + q) >= pa.unit_blocks && ld_acquire(sa.claim + q) < sa.chunks;
-      if (__syncthreads_and(ok)) take_scatter_chunks<T, G>(sa, q, sa.exit_chunks, &s_chunk);
-    }
-    return;
-  }
-  // exchange block: first whatever is left of the scatter it is about to wait for (nobody with a
-  // lower role index is bound to finish it), then the slot's exchange
-  if (p >= 2 && p - 2 < P) finish_scatter<T, G>(sa, p - 2, &s_chunk);
-  exchange_slot<T, G>(sa, p, exch_idx, exch_n, in_place);
-  __syncthreads();
-  FLEXSAE_TRACE_MAX(p, kTrExchEnd);
-  count_and_publish(sa, false, sa.slot_done + p, exch_n, p, false);
+  // slot 0 has no earlier slot of this launch to publish behind (the previous launch on this rank has
+  // completed, flags included: launches of one rank are stream-ordered)
+  count_and_publish(sa, scatter, (scatter ? sa.scatter_done : sa.slot_done) + p, scatter ? pa.conv_blocks : exch_n, p, p == 0);
 }
 
 }  // namespace flexsae

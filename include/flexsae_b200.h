@@ -66,9 +66,9 @@ const char* flexsae_last_error(void);
  * "direct_f32" (1: with an fp32 decoder the reductions go straight into dweight),
  * "ticket_order" (1: the blocks of the single-launch backward take their roles from an atomic
  * ticket, i.e. in the order in which they really start, instead of from blockIdx.x),
- * "convert_steal" (1: in the single-launch backward the slab conversion is not done by blocks at a
- * fixed position but taken in "steal_chunks" chunks by whichever blocks are running, each unit
- * block taking "steal_exit_chunks" after its walk),
+ * "slabs" (2..4 fp32 accumulation slabs in rotation) and "convert_lag" (1 .. slabs-1: the slab of a
+ * column piece is converted that many pieces after it was accumulated, so that the conversion never
+ * waits for the piece's last accumulating blocks and nobody waits for the conversion),
  * "exchange_blocks" and "exchange_offset_pct" (sharded backward: how many blocks per column piece
  * do the cross-GPU exchange and how far into the piece's blocks they are placed), "scatter_rotate"
  * (1: each rank starts its scatter at a different owner's rows), "flag_fan_out" (1: a finished
@@ -168,7 +168,8 @@ int flexsae_loss_bwd(int kind, const int64_t* indices, const void* weight, const
  *       whatever read the previous contents must precede the call in stream order.  Not with the
  *       multicast path.  NULL = through the gather buffer
  *   seq_base   first call: 1; every later call on the same buffers: previous seq_base +
- *       flexsae_shard_slots(F, D, weight_dtype); identical on all ranks.  Before it would pass
+ *       flexsae_shard_slots(F, D, weight_dtype) (an upper bound of the flag values one call uses);
+ *       identical on all ranks.  Before it would pass
  *       INT32_MAX, start again: all ranks idle, flag buffers zeroed, seq_base = 1
  * Only FLEXSAE_DW_ATOMIC accumulation.  All ranks must issue the same sequence of calls.  Waits on
  * other GPUs are bounded; if one gives up, FLEXSAE_STATUS_PIPELINE_TIMEOUT is set in `status` and the

@@ -1,8 +1,9 @@
 """Event-driven models of the block-level protocols of the single-launch backward kernels.
 
 They model WHO WAITS FOR WHAT and WHO PUBLISHES WHAT, exactly as the kernels do it
-(flexsae_b200/csrc/flexsae_backward.cuh: decoder_loss_bwd_stealing_kernel;
-flexsae_b200/csrc/flexsae_sharded.cuh: decoder_loss_bwd_sharded_kernel), with blocks dispatched in
+(flexsae_b200/csrc/flexsae_backward.cuh: decoder_loss_bwd_pipelined_kernel;
+flexsae_b200/csrc/flexsae_sharded.cuh: decoder_loss_bwd_sharded_kernel;
+flexsae_b200/csrc/flexsae_small_allreduce.cuh: small_allreduce_kernel), with blocks dispatched in
 index order into a limited number of resident slots and random durations, and check the protocol
 itself: no circular wait whatever the number of resident blocks (down to one), nothing read before
 it is complete, nothing overwritten before it has been read, every conversion exactly once.  They
@@ -16,101 +17,16 @@ class Hazard(AssertionError):
     pass
 
 
-def run_stealing(P, U, chunks, exit_chunks, tail, slots, seed):
-    """P pieces of U unit blocks, `chunks` conversion chunks per slab, `tail` trailing blocks."""
-    rnd = random.Random(seed)
-    walk_done = [0]*P; conv_done = [0]*P; claim = [0]*P
-    conv_started_after_walk = True; walk_after_conv = True
-    def take(q, limit):
-        n = 0
-        while n < limit:
-            c = claim[q]; claim[q] += 1
-            if c >= chunks: break
-            nonlocal conv_started_after_walk
-            if walk_done[q] < U: conv_started_after_walk = False
-            yield ("work", rnd.uniform(0.5, 2.0))
-            conv_done[q] += 1
-            n += 1
-    def block(b):
-        p = b // U
-        if p >= P:
-            for q in range(max(0, P-2), P):
-                yield ("wait", lambda q=q: walk_done[q] >= U)
-                yield from take(q, 10**9)
-            return
-        if p >= 2:
-            if conv_done[p-2] < chunks:
-                yield ("wait", lambda: walk_done[p-2] >= U)
-                yield from take(p-2, 10**9)
-                yield ("wait", lambda: conv_done[p-2] >= chunks)
-        nonlocal walk_after_conv
-        if p >= 2 and conv_done[p-2] < chunks: walk_after_conv = False
-        yield ("work", rnd.uniform(5, 40))
-        walk_done[p] += 1
-        if p >= 1 and exit_chunks > 0 and walk_done[p-1] >= U and claim[p-1] < chunks:
-            yield from take(p-1, exit_chunks)
-    total = P*U + tail
-    nxt = 0; t = 0.0; running = []  # heap of (time, id, gen); waiting list
-    waiting = []; done = 0; seq = 0
-    def start(gen):
-        nonlocal seq
-        step(gen)
-    def step(gen):
-        nonlocal done, seq
-        try:
-            kind, arg = next(gen)
-        except StopIteration:
-            done += 1; return False
-        if kind == "work":
-            seq += 1; heapq.heappush(running, (t + arg, seq, gen))
-        else:
-            waiting.append((arg, gen))
-        return True
-    active = 0
-    def fill():
-        nonlocal nxt, active
-        while active < slots and nxt < total:
-            g = block(nxt); nxt += 1; active += 1
-            if not step(g): active -= 1
-    fill()
-    guard = 0
-    while done < total:
-        guard += 1
-        assert guard < 10**7
-        # release waiters whose condition holds
-        progressed = True
-        while progressed:
-            progressed = False
-            for i, (cond, g) in enumerate(list(waiting)):
-                if cond():
-                    waiting.remove((cond, g))
-                    if not step(g): active -= 1
-                    progressed = True
-            fill()
-        if done >= total: break
-        if not running:
-            raise Hazard(f"deadlock: {len(waiting)} blocks waiting, {done} of {total} finished")
-        t, _, g = heapq.heappop(running)
-        if not step(g): active -= 1
-        fill()
-    if not all(c == chunks for c in conv_done):
-        raise Hazard(f"chunks converted per piece: {conv_done}")
-    if not (conv_started_after_walk and walk_after_conv):
-        raise Hazard("a slab was converted before its walk ended, or walked before it was converted")
-    return t
-
-
-def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=2, ordered=True, steal=None):
-    """R ranks, P pieces, per slot U unit / E exchange / C converting blocks; `in_place`: reduced rows go
-    straight into the peers' dweight (exchange waits for scatter flags only); `ordered`: a rank's flags are
-    published strictly in slot order (what the kernel does; False shows what that rule prevents);
-    `steal` = (chunks, exit_chunks): no converting blocks -- the scatter of a finished slab is taken in
-    chunks by unit blocks (after their walk, or before it when their slab is still occupied) and by C
-    tail blocks after the last piece."""
-    writes_per_piece = steal[0] if steal else C
+def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=2, ordered=True, ns=2, lag=1):
+    """R ranks, P pieces, per slot U unit / E exchange / C converting blocks; `ns` slabs in rotation and
+    the scatter of a piece `lag` slots behind its accumulation (1 <= lag < ns); `in_place`: reduced rows
+    go straight into the peers' dweight (exchange waits for scatter flags only); `ordered`: a rank's
+    flags are published strictly in slot order (what the kernel does; False shows what that rule prevents)."""
+    L = lag
     rnd = random.Random(seed)
     speed = [rnd.uniform(0.5, 2.0) for _ in range(R)]
-    nslots = P + 3
+    nslots = P + L + 2
+    last_slot, last_scatter_slot = P + L + 1, P + L - 1
     flagsE = [[0]*R for _ in range(R)]; flagsC = [[0]*R for _ in range(R)]   # [at rank][of rank]
     inbox = [[[(-1, 0, -1) for _ in range(R)] for _ in range(2)] for _ in range(R)]     # [owner][parity][sender] = (piece, writes, step)
     reduced = {}   # (step, owner, piece) -> number of exch blocks that reduced it
@@ -119,98 +35,57 @@ def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=
     landed = {}    # (step, dest, piece, owner) -> blocks that wrote dW rows in place
     t = 0.0; heap = []; waiting = []; seq = [0]
     errors = []
-    def exch_count(p): return E if p <= P else E + C
+    def exch_count(p): return E if p < P + L else E + C      # blocks that share the exchange work of slot p
     def make_rank(r, step_no):
-        seq_base = 1 + step_no * nslots
+        seq_base = 1 + step_no * (P + 5)      # what flexsae_shard_slots answers: an upper bound of the slots
         walk_done = [0]*(nslots); conv_done = [0]*nslots; slot_done = [0]*nslots; scat_done = [0]*nslots
+        slab = [(-1, "free")] * ns             # (piece, "accumulating" | "free"): what each slab holds
         def publish(kind, p):
             for s in range(R):
                 (flagsC if kind == "C" else flagsE)[s][r] = seq_base + p
         def waitE(target): return lambda: all(flagsE[r][s] >= target for s in range(R))
         def waitC(target): return lambda: all(flagsC[r][s] >= target for s in range(R))
-        claim = [0]*nslots; piece_done = [0]*nslots
-        def scatter_into_inboxes(q):
-            for o in range(R):
-                pc, wr, st = inbox[o][q & 1][r]
-                if (pc, st) != (q, step_no):
-                    # first writer of this piece: previous content must have been reduced completely
-                    if pc >= 0 and reduced.get((st, o, pc), 0) < exch_count(pc + 2):
-                        errors.append(("inbox overwritten before reduce", r, o, q, pc, st))
-                    inbox[o][q & 1][r] = (q, 1, step_no)
-                else:
-                    inbox[o][q & 1][r] = (q, wr + 1, step_no)
-        def take(q, limit):
-            n = 0
-            while n < limit:
-                c = claim[q]; claim[q] += 1
-                if c >= steal[0]: break
-                if walk_done[q] < U: errors.append(("slab scattered before its walk ended", r, q))
-                yield ("work", rnd.uniform(0.3, 2) * speed[r])
-                scatter_into_inboxes(q)
-                piece_done[q] += 1
-                if piece_done[q] == steal[0]:
-                    if ordered and q > 0: yield ("wait", lambda: flagsC[r][r] >= seq_base + q)
-                    publish("C", q + 1)
-                n += 1
         def unit(p):
-            if steal:
-                if p >= 2 and piece_done[p-2] < steal[0]:
-                    yield ("wait", lambda: walk_done[p-2] >= U)
-                    yield ("wait", waitE(seq_base + p - 2))
-                    yield from take(p - 2, 10**9)
-                    yield ("wait", lambda: piece_done[p-2] >= steal[0])
-                if p >= 2 and piece_done[p-2] < steal[0]: errors.append(("walk started on an unconverted slab", r, p))
-                yield ("work", rnd.uniform(5, 30) * speed[r])
-                walk_done[p] += 1
-                if p >= 1 and steal[1] > 0 and walk_done[p-1] >= U and claim[p-1] < steal[0] and waitE(seq_base + p - 1)():
-                    yield from take(p - 1, steal[1])
-                return
-            if p >= 2: yield ("wait", lambda: conv_done[p-1] >= C)
+            if p >= ns: yield ("wait", lambda: conv_done[p - ns + L] >= C)
+            held = slab[p % ns]
+            if held[1] != "free" and held[0] != p: errors.append(("walk started on an unconverted slab", r, p, held))
+            slab[p % ns] = (p, "accumulating")
             yield ("work", rnd.uniform(5, 30) * speed[r])
             walk_done[p] += 1
-        def tail(p):
-            for q in range(max(0, P - 2), P):
-                yield ("wait", lambda q=q: walk_done[q] >= U)
-                yield ("wait", waitE(seq_base + q))
-                yield from take(q, 10**9)
         def conv(p):
-            if p >= 1 and p - 1 < P:
-                yield ("wait", lambda: walk_done[p-1] >= U)
+            q = p - L
+            if 0 <= q < P:
+                yield ("wait", lambda: walk_done[q] >= U)
                 yield ("wait", waitE(seq_base + p - 1))
-                q = p - 1
+                if slab[q % ns][0] != q: errors.append(("converted a slab that holds another piece", r, q, slab[q % ns]))
                 yield ("work", rnd.uniform(1, 6) * speed[r])
                 for o in range(R):
                     pc, wr, st = inbox[o][q & 1][r]
                     if (pc, st) != (q, step_no):
                         # first writer of this piece: previous content must have been reduced completely
-                        if pc >= 0 and reduced.get((st, o, pc), 0) < exch_count(pc + 2):
+                        if pc >= 0 and reduced.get((st, o, pc), 0) < exch_count(pc + L + 1):
                             errors.append(("inbox overwritten before reduce", r, o, q, pc, st))
                         inbox[o][q & 1][r] = (q, 1, step_no)
                     else:
                         inbox[o][q & 1][r] = (q, wr + 1, step_no)
             conv_done[p] += 1
+            if 0 <= q < P and conv_done[p] == C: slab[q % ns] = (q, "free")
             scat_done[p] += 1
             if scat_done[p] == C:
                 if ordered and p > 0: yield ("wait", lambda: flagsC[r][r] >= seq_base + p - 1)
                 publish("C", p)
         def exch(p):
             n = exch_count(p)
-            if steal and p >= 2 and p - 2 < P:
-                # nobody with a lower index is bound to finish the scatter this block is about to wait
-                # for, so it takes what is left of it first
-                yield ("wait", lambda: walk_done[p-2] >= U)
-                yield ("wait", waitE(seq_base + p - 2))
-                yield from take(p - 2, 10**9)
             if p >= 2:
-                if (not in_place) or p == P + 2: yield ("wait", waitE(seq_base + p - 1))
-                yield ("wait", waitC(seq_base + min(p - 1, P)))
-            if p >= 2 and p - 2 < P:
-                q = p - 2
+                if (not in_place) or p == last_slot: yield ("wait", waitE(seq_base + p - 1))
+                yield ("wait", waitC(seq_base + min(p - 1, last_scatter_slot)))
+            q = p - L - 1
+            if 0 <= q < P:
                 for s in range(R):
-                    if inbox[r][q & 1][s] != (q, writes_per_piece, step_no): errors.append(("reduce reads incomplete inbox", r, s, q, inbox[r][q & 1][s]))
+                    if inbox[r][q & 1][s] != (q, C, step_no): errors.append(("reduce reads incomplete inbox", r, s, q, inbox[r][q & 1][s]))
                 yield ("work", rnd.uniform(1, 6) * speed[r])
                 for s in range(R):
-                    if inbox[r][q & 1][s] != (q, writes_per_piece, step_no): errors.append(("inbox changed during reduce", r, s, q, inbox[r][q & 1][s]))
+                    if inbox[r][q & 1][s] != (q, C, step_no): errors.append(("inbox changed during reduce", r, s, q, inbox[r][q & 1][s]))
                 reduced[(step_no, r, q)] = reduced.get((step_no, r, q), 0) + 1
                 for o in range(R):
                     if o == r: continue
@@ -219,34 +94,34 @@ def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=
                     else:
                         pc, wr, st = gathered[o][q & 1][r]
                         if (pc, st) != (q, step_no):
-                            if pc >= 0 and copied.get((st, o, pc), 0) < exch_count(pc + 3):
+                            if pc >= 0 and copied.get((st, o, pc), 0) < exch_count(pc + L + 2):
                                 errors.append(("gather buffer overwritten before copy", r, o, q, pc))
                             gathered[o][q & 1][r] = (q, 1, step_no)
                         else:
                             gathered[o][q & 1][r] = (q, wr + 1, step_no)
-            if p >= 3 and p - 3 < P and not in_place:
-                q = p - 3
+            q = p - L - 2
+            if 0 <= q < P and not in_place:
                 for ow in range(R):
-                    if ow != r and gathered[r][q & 1][ow] != (q, exch_count(q + 2), step_no):
+                    if ow != r and gathered[r][q & 1][ow] != (q, exch_count(q + L + 1), step_no):
                         errors.append(("copy reads incomplete gather buffer", r, ow, q, gathered[r][q & 1][ow]))
                 yield ("work", rnd.uniform(0.5, 3) * speed[r])
                 copied[(step_no, r, q)] = copied.get((step_no, r, q), 0) + 1
             slot_done[p] += 1
             if slot_done[p] == n:
-                if ordered: yield ("wait", lambda: flagsE[r][r] >= seq_base + p - 1)
+                if ordered and p > 0: yield ("wait", lambda: flagsE[r][r] >= seq_base + p - 1)
                 publish("E", p)
         order = []
         for p in range(P):
             row = []
-            u = 0
-            for i in range(U + (0 if steal else C)):
-                if not steal and i >= conv_off and i < conv_off + C: row.append(("conv", p))
-                else: row.append(("unit", p)); u += 1
+            for i in range(U + C):
+                if i >= conv_off and i < conv_off + C: row.append(("conv", p))
+                else: row.append(("unit", p))
             row = row[:exch_off] + [("exch", p)] * E + row[exch_off:]   # exch_off <= conv_off
             order += row
-        order += [("exch", P)] * E + [("tail" if steal else "conv", P)] * C
-        order += [("exch", P + 1)] * (E + C) + [("exch", P + 2)] * (E + C)
-        gens = {"unit": unit, "conv": conv, "exch": exch, "tail": tail}
+        for d in range(L + 2):
+            p = P + d
+            order += ([("exch", p)] * E + [("conv", p)] * C) if d < L else [("exch", p)] * (E + C)
+        gens = {"unit": unit, "conv": conv, "exch": exch}
         return [gens[k](p) for k, p in order]
     # each rank runs `steps` kernels back to back (stream order): next kernel's blocks start after the previous finished
     state = []
@@ -308,18 +183,23 @@ def run_sharded(R, P, U, E, C, exch_off, conv_off, in_place, slots, seed, steps=
         raise Hazard(str(errors[:5]))
 
 
-def run_pipelined(P, U, C, conv_off, slots, seed):
-    """decoder_loss_bwd_pipelined_kernel: per piece U unit blocks with the C blocks that convert the
-    PREVIOUS piece inserted at `conv_off`, C trailing blocks for the last piece; unit blocks of piece p
-    wait for the conversion of piece p-2 (same slab), converting blocks for the walk of their piece."""
+def run_pipelined(P, U, C, conv_off, slots, seed, ns=2, lag=1):
+    """decoder_loss_bwd_pipelined_kernel: slot p holds the U unit blocks of piece p with the C blocks that
+    convert piece p - lag inserted at `conv_off`; `lag` trailing slots of C converting blocks; `ns` slabs in
+    rotation.  Unit blocks of piece p wait for the conversion of piece p - ns (same slab), converting
+    blocks for the walk of their piece."""
     rnd = random.Random(seed)
     walk_done = [0] * P
     conv_done = [0] * P
     problems = []
+    slab = [(-1, "free")] * ns
 
     def unit(p):
-        if p >= 2:
-            yield ("wait", lambda: conv_done[p - 2] >= C)
+        if p >= ns:
+            yield ("wait", lambda: conv_done[p - ns] >= C)
+        if slab[p % ns][1] != "free" and slab[p % ns][0] != p:
+            problems.append(("walk started on an unconverted slab", p, slab[p % ns]))
+        slab[p % ns] = (p, "accumulating")
         yield ("work", rnd.uniform(5, 40))
         walk_done[p] += 1
 
@@ -327,15 +207,20 @@ def run_pipelined(P, U, C, conv_off, slots, seed):
         if q < 0:
             return
         yield ("wait", lambda: walk_done[q] >= U)
+        if slab[q % ns][0] != q:
+            problems.append(("converted a slab that holds another piece", q, slab[q % ns]))
         yield ("work", rnd.uniform(1, 6))
         conv_done[q] += 1
+        if conv_done[q] == C:
+            slab[q % ns] = (q, "free")
 
     order = []
     for p in range(P):
         row = [("unit", p)] * U
-        row = row[:conv_off] + [("conv", p - 1)] * C + row[conv_off:]
+        row = row[:conv_off] + [("conv", p - lag)] * C + row[conv_off:]
         order += row
-    order += [("conv", P - 1)] * C
+    for d in range(lag):
+        order += [("conv", P + d - lag)] * C
     blocks = [(unit if k == "unit" else conv)(i) for k, i in order]
     t, heap, waiting, seq, nxt, active, done = 0.0, [], [], 0, 0, 0, 0
 

@@ -6,8 +6,6 @@ import sys
 import pytest
 import torch
 
-from tests.helpers import unverified_on_gpu
-
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.gpu
 
@@ -24,12 +22,12 @@ def _worker(rank, world, port, kind, q, mode):
         from flexsae_b200.workloads import CONFIGS, make_inputs
         fd.config.peer_reduce = mode != "nccl"
         fd.config.use_multicast = mode == "multicast"
-        fd.config.symmetric_dweight = mode in ("inplace", "inplace_small", "inplace_steal")
+        fd.config.symmetric_dweight = mode in ("inplace", "inplace_small", "inplace_lag2")
         fd.config.fused_small_reduce = mode == "inplace_small"
-        if mode in ("steal", "inplace_steal"):      # scatter taken from a shared queue instead of by converting blocks
-            fx._native.set_option("convert_steal", 1)
-            fx._native.set_option("steal_chunks", 96 if mode == "steal" else 1024)
-        if mode in ("inplace", "inplace_small", "inplace_steal"):       # together with the other non-default exchange settings
+        if mode in ("lag2", "inplace_lag2"):        # three slabs in rotation, scatter two slots behind the accumulation
+            fx._native.set_option("slabs", 3 if mode == "lag2" else 4)
+            fx._native.set_option("convert_lag", 2 if mode == "lag2" else 3)
+        if mode in ("inplace", "inplace_small", "inplace_lag2"):       # together with the other non-default exchange settings
             for name, value in (("exchange_offset_pct", 25), ("scatter_rotate", 1), ("flag_fan_out", 1)):
                 fx._native.set_option(name, value)
         w = CONFIGS["c3_k32"].replace(B=768, F=8190)       # F not a multiple of the world size
@@ -62,10 +60,7 @@ def _worlds():
 
 
 @pytest.mark.parametrize("world", _worlds())
-@pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "inplace", "nccl",
-                                         pytest.param("inplace_small", marks=unverified_on_gpu),
-                                         pytest.param("steal", marks=unverified_on_gpu),
-                                         pytest.param("inplace_steal", marks=unverified_on_gpu)])
+@pytest.mark.parametrize("peer_reduce", ["multicast", "stores", "inplace", "nccl", "inplace_small", "lag2", "inplace_lag2"])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
 def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     if torch.cuda.device_count() < world:
@@ -79,7 +74,7 @@ def test_gpu_shards_match_one_gpu(kind, peer_reduce, world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29800 + os.getpid() % 100 + (7 if kind == "hier" else 0)
-    port += {"multicast": 13, "stores": 5, "inplace": 17, "inplace_small": 19, "steal": 21, "inplace_steal": 23,
+    port += {"multicast": 13, "stores": 5, "inplace": 17, "inplace_small": 19, "lag2": 21, "inplace_lag2": 23,
              "nccl": 0}[peer_reduce] + 29 * world
     procs = [ctx.Process(target=_worker, args=(r, world, port, kind, q, peer_reduce)) for r in range(world)]
     for p in procs:
@@ -137,7 +132,6 @@ def _small_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-@unverified_on_gpu
 @pytest.mark.parametrize("world", _worlds())
 def test_small_allreduce_matches_nccl(world):
     if torch.cuda.device_count() < world:

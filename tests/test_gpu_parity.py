@@ -9,8 +9,7 @@ from flexsae_b200 import _native as nv
 from flexsae_b200.workloads import CONFIGS, Workload, make_inputs
 from oracle import flexsae_oracle as orc
 from oracle import torch_reference as tref
-from tests.helpers import (REFERENCE_TOLS, golden_files, inputs_as_numpy, load_golden, rel_err,
-                           unverified_on_gpu)
+from tests.helpers import REFERENCE_TOLS, golden_files, inputs_as_numpy, load_golden, rel_err
 
 pytestmark = pytest.mark.gpu
 
@@ -47,11 +46,11 @@ def _auto_options():
         nv.set_option(name, 0)
     nv.set_option("pipeline", 1)
     nv.set_option("direct_f32", 1)
-    nv.set_option("convert_steal", 0)
     nv.set_option("ticket_order", 0)
-    nv.set_option("steal_chunks", 1024)
-    nv.set_option("steal_exit_chunks", 1)
+    slabs, lag = nv.get_option("slabs"), nv.get_option("convert_lag")
     yield
+    nv.set_option("slabs", slabs)
+    nv.set_option("convert_lag", lag)
     fx.check_status()
 
 
@@ -126,18 +125,17 @@ def test_fp32_decoder_through_slab(name, kind):
     assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
 
 
-@unverified_on_gpu
-@pytest.mark.parametrize("chunks,exit_chunks", [(1024, 1), (3, 0), (64, 4)])
+@pytest.mark.parametrize("slabs,lag", [(2, 1), (3, 1), (3, 2), (4, 1), (4, 3)])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
 @pytest.mark.parametrize("name", ["t16_64_128_1024_bfloat16", "mixed_bf16w_f32v", "t16_16_64_512_float16", "c1"])
-def test_shared_conversion_queue(name, kind, chunks, exit_chunks):
-    """Single-launch backward whose slab conversion is taken in chunks by whichever blocks run."""
+def test_slab_rotation_and_conversion_lag(name, kind, slabs, lag):
+    """The single-launch backward with 2..4 fp32 slabs in rotation and the conversion of a piece 1..3
+    slots behind its accumulation."""
     path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
     w, kind, gold = load_golden(path)
-    nv.set_option("convert_steal", 1)
-    nv.set_option("steal_chunks", chunks)
-    nv.set_option("steal_exit_chunks", exit_chunks)
-    nv.set_option("direct_f32", 0)       # fp32 decoders through the slab too
+    nv.set_option("slabs", slabs)
+    nv.set_option("convert_lag", lag)
+    nv.set_option("direct_f32", 0)       # fp32 decoders through the slabs too
     nv.set_option("lanes_bwd", 8)        # many column pieces
     x = make_inputs(w, "cpu")
     got = run_fused(kind, x)
@@ -145,29 +143,22 @@ def test_shared_conversion_queue(name, kind, chunks, exit_chunks):
     assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
 
 
-@unverified_on_gpu
-@pytest.mark.parametrize("steal", [0, 1])
+@pytest.mark.parametrize("slabs,lag", [(2, 1), (3, 2)])
 @pytest.mark.parametrize("kind", ["topk", "hier"])
 @pytest.mark.parametrize("name", ["t16_64_128_1024_bfloat16", "mixed_bf16w_f32v", "c1"])
-def test_roles_by_starting_order(name, kind, steal):
+def test_roles_by_starting_order(name, kind, slabs, lag):
     """Blocks of the single-launch backward take their roles from an atomic ticket, not from blockIdx.x."""
     path = [p for p in golden_files() if p.endswith(f"{name}__{kind}.npz")][0]
     w, kind, gold = load_golden(path)
     nv.set_option("ticket_order", 1)
-    nv.set_option("convert_steal", steal)
+    nv.set_option("slabs", slabs)
+    nv.set_option("convert_lag", lag)
     nv.set_option("direct_f32", 0)
     nv.set_option("lanes_bwd", 8)
     x = make_inputs(w, "cpu")
     got = run_fused(kind, x)
     want = orc.LOSSES[kind](**inputs_as_numpy(x), grad_out=float(x["grad_out"]))
     assert_close_to_oracle(got, want, TIGHT[w.weight_dtype])
-
-
-@unverified_on_gpu
-@pytest.mark.parametrize("kind", ["topk", "hier"])
-def test_shared_conversion_queue_full_size(kind):
-    nv.set_option("convert_steal", 1)
-    _compare_with_torch_reference_on_gpu(CONFIGS["c3_k128"], kind, tol=1e-2, loss_tol=1e-5, chunk_rows=128)
 
 
 EDGE = [

@@ -8,7 +8,6 @@ import torch
 
 from flexsae_b200 import _native as nv
 from oracle import flexsae_oracle as orc
-from tests.helpers import unverified_on_gpu
 
 
 @pytest.mark.parametrize("seed", [0, 1, 2])
@@ -63,7 +62,6 @@ CASES = [  # B, F, K, dtype, kind of data
 ]
 
 
-@unverified_on_gpu
 @pytest.mark.gpu
 @pytest.mark.parametrize("B,F,K,dtype,data", CASES)
 @pytest.mark.parametrize("relu", [False, True])
@@ -93,7 +91,6 @@ def test_gpu_selection_matches_oracle(B, F, K, dtype, data, relu):
     assert np.array_equal(vals.cpu().numpy(), want_vals.astype(np.float32), equal_nan=True)
 
 
-@unverified_on_gpu
 @pytest.mark.gpu
 def test_gpu_gradient_and_loss_chain():
     import flexsae_b200 as fx

@@ -12,15 +12,9 @@ def _shard_case(seed):
     R, P, U = rnd.randint(2, 4), rnd.randint(1, 6), rnd.randint(2, 12)
     E, C = rnd.randint(1, 3), rnd.randint(1, 3)
     conv_off = rnd.randint(0, U)
-    return dict(R=R, P=P, U=U, E=E, C=C, exch_off=rnd.randint(0, conv_off), conv_off=conv_off, slots=rnd.randint(1, 12), seed=seed)
-
-
-def test_shared_conversion_queue_never_blocks_and_converts_every_chunk_once():
-    for seed in range(300):
-        rnd = random.Random(seed)
-        chunks = rnd.randint(1, 30)
-        pm.run_stealing(P=rnd.randint(1, 7), U=rnd.randint(1, 40), chunks=chunks, exit_chunks=rnd.randint(0, 3),
-                        tail=min(chunks, 5), slots=rnd.randint(1, 25), seed=seed)
+    ns = rnd.randint(2, 4)
+    return dict(R=R, P=P, U=U, E=E, C=C, exch_off=rnd.randint(0, conv_off), conv_off=conv_off, slots=rnd.randint(1, 12), seed=seed,
+                ns=ns, lag=rnd.randint(1, ns - 1))
 
 
 @pytest.mark.parametrize("in_place", [False, True])
@@ -41,19 +35,13 @@ def test_flags_must_be_published_in_slot_order():
     assert hazards > 0
 
 
-@pytest.mark.parametrize("in_place", [False, True])
-def test_sharded_exchange_with_the_shared_scatter_queue(in_place):
-    for seed in range(150):
-        rnd = random.Random(1000 + seed)
-        pm.run_sharded(in_place=in_place, steal=(rnd.randint(1, 12), rnd.randint(0, 3)), **_shard_case(seed))
-
-
 def test_pipelined_backward_never_waits_for_a_later_block():
     for seed in range(300):
         rnd = random.Random(seed)
         U = rnd.randint(1, 30)
+        ns = rnd.randint(2, 4)
         pm.run_pipelined(P=rnd.randint(1, 8), U=U, C=rnd.randint(1, 6), conv_off=rnd.randint(0, U), slots=rnd.randint(1, 20),
-                         seed=seed)
+                         seed=seed, ns=ns, lag=rnd.randint(1, ns - 1))
 
 
 def test_small_allreduce_needs_only_two_cells_per_sender():
