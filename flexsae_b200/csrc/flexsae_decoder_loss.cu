@@ -34,7 +34,7 @@ namespace flexsae {
 struct Options {
   int lanes_fwd = 0;      // 0 = auto
   int lanes_bwd = 0;      // 0 = auto
-  int l2_budget_mb = 80;  // one piece of decoder columns (+ one fp32 slab) must fit in this many MiB
+  int l2_budget_mb = 64;  // one piece of decoder columns (+ its fp32 slabs) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
   int convert_offset_pct = 60;  // where, inside a piece's unit blocks, the previous piece's converters sit
@@ -103,16 +103,20 @@ static int check_shape(int kind, const Shape& s, int wdt) {
   return 0;
 }
 
-// lanes per batch row: the widest group whose per-piece working set fits the L2 budget
+// lanes per batch row: the widest group whose per-piece working set -- the piece's decoder columns
+// plus, in the backward, all fp32 slabs in rotation -- fits the L2 budget
 static int choose_lanes(int64_t F, int wdt, bool with_slab, int forced) {
   if (forced == 8 || forced == 16 || forced == 32) return forced;
   const int vec = 16 / (int)dtype_size(wdt);
   const double budget = (double)g_opt.l2_budget_mb * 1048576.0;
-  for (int G = 32; G >= 8; G >>= 1) {
-    double bytes = (double)F * G * vec * (dtype_size(wdt) + (with_slab ? 4.0 : 0.0));
-    if (bytes <= budget) return G;
-  }
-  return 32;  // nothing fits: stream from HBM with the widest (most coalesced) row pieces
+  // an fp32 decoder accumulates straight into its dweight columns: one fp32 table instead of the slabs
+  const int tables = !with_slab ? 0 : ((wdt == FLEXSAE_F32 && g_opt.direct_f32 && g_opt.pipeline) ? 1 : g_opt.slabs);
+  auto bytes = [&](int G) { return (double)F * G * vec * (dtype_size(wdt) + 4.0 * tables); };
+  for (int G = 32; G >= 8; G >>= 1)
+    if (bytes(G) <= budget) return G;
+  // nothing fits: the narrowest pieces while they are within reach of the L2, else stream from HBM
+  // with the widest (most coalesced) row pieces
+  return bytes(8) <= 2.0 * budget ? 8 : 32;
 }
 
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }

@@ -3,10 +3,10 @@
 // (indices, vals) pair the loss kernels take.
 //
 // One CTA of 256 threads per row, several CTAs resident per SM, the row streamed from HBM ONCE:
-//   1. every thread takes 16-byte vectors at a stride of the CTA and keeps four running maxima (one per
-//      vector slot modulo 4): 1024 maxima of disjoint element sets per row.  The K-th largest of them
-//      is a lower bound of the K-th largest element, and for K << F a tight one (about 1.07 K elements
-//      reach it at K = 128, F = 65536);
+//   1. every thread takes 16-byte vectors at a stride of the CTA and keeps running maxima of disjoint
+//      element sets (packed NaN-propagating maxima, four instructions per vector): 1024 maxima per row
+//      for fp32, 2048 for 16-bit types.  The K-th largest of them is a lower bound of the K-th largest
+//      element, and for K << F a tight one (about 1.07 K elements reach it at K = 128, F = 65536);
 //   2. that bound is found exactly on the top 16 bits of an order-preserving integer key (two 8-bit
 //      histogram passes over the maxima, which never leave their registers);
 //   3. the row is read again -- it is still in L2 -- and everything not below the bound is appended
@@ -26,8 +26,8 @@ namespace flexsae {
 
 constexpr int kSelThreads = 256;
 constexpr int kSelWarps = kSelThreads / 32;
-constexpr int kSelMaxima = 4;                        // running maxima per thread
-constexpr int kSelMaxK = kSelThreads * kSelMaxima;   // the bound needs at least K maxima
+constexpr int kSelMaxima = 4;                        // accumulators of running maxima per thread
+constexpr int kSelMaxK = kSelThreads * kSelMaxima;   // the bound needs at least K maxima (16-bit types keep twice as many)
 constexpr int kSelCandidates = 2048;                 // capacity of the candidate list (>= kSelMaxK)
 constexpr int kSelInFlight = 8;                      // 16-byte loads in flight per thread
 #ifndef FLEXSAE_SEL_MINB
@@ -99,26 +99,6 @@ struct SelectArgs {
   int vals_dtype;
   int relu;          // clamp the reported values at zero
 };
-
-// Does this 16-byte vector hold a NaN?  (16-bit types: two elements per word, tested together.)
-template <typename T>
-__device__ __forceinline__ bool vector_has_nan(const uint4& v);
-template <>
-__device__ __forceinline__ bool vector_has_nan<float>(const uint4& v) {
-  return ((v.x & 0x7fffffffu) > 0x7f800000u) | ((v.y & 0x7fffffffu) > 0x7f800000u) | ((v.z & 0x7fffffffu) > 0x7f800000u) |
-         ((v.w & 0x7fffffffu) > 0x7f800000u);
-}
-// (h & 0x7fff) > 0x7f80  <=>  bit 15 of (h & 0x7fff) + 0x007f is set; no carry crosses the halves
-template <>
-__device__ __forceinline__ bool vector_has_nan<__nv_bfloat16>(const uint4& v) {
-  const uint32_t m = 0x7fff7fffu, c = 0x007f007fu;
-  return ((((v.x & m) + c) | ((v.y & m) + c) | ((v.z & m) + c) | ((v.w & m) + c)) & 0x80008000u) != 0u;
-}
-template <>
-__device__ __forceinline__ bool vector_has_nan<__half>(const uint4& v) {
-  const uint32_t m = 0x7fff7fffu, c = 0x03ff03ffu;
-  return ((((v.x & m) + c) | ((v.y & m) + c) | ((v.z & m) + c) | ((v.w & m) + c)) & 0x80008000u) != 0u;
-}
 
 // bit pattern of element j of a 16-byte vector, as SelKey<T>::key takes it
 template <typename T>
@@ -196,6 +176,64 @@ __device__ __forceinline__ void sel_hist_add(int* hist, int bin) {
   if (bin >= 0 && lane == __ffs(peers) - 1) atomicAdd(hist + bin, __popc(peers));
 }
 
+// ---- packed running maxima: the two passes over the row cost a handful of instructions per 16 bytes --
+// A NaN must win (it ranks above every number), hence the NaN-propagating maxima.
+template <typename T>
+struct SelMax;
+template <>
+struct SelMax<float> {
+  static constexpr int PER_ACC = 1;  // maxima held by one accumulator
+  using acc_t = float;
+  __device__ __forceinline__ static acc_t lowest() { return -INFINITY; }
+  __device__ __forceinline__ static float max_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+  }
+  __device__ __forceinline__ static acc_t fold(acc_t a, const uint4& v) {
+    return max_nan(max_nan(a, __uint_as_float(v.x)), max_nan(max_nan(__uint_as_float(v.y), __uint_as_float(v.z)), __uint_as_float(v.w)));
+  }
+  __device__ __forceinline__ static uint32_t bits(acc_t a, int) { return __float_as_uint(a); }
+  // true when every element of the vector is below the bound (so none of them is a candidate)
+  __device__ __forceinline__ static bool all_below(const uint4& v, float bound) {
+    return fold(lowest(), v) < bound;  // false for a NaN in the vector or in the bound
+  }
+};
+template <>
+struct SelMax<__nv_bfloat16> {
+  static constexpr int PER_ACC = 2;
+  using acc_t = __nv_bfloat162;
+  __device__ __forceinline__ static acc_t as2(uint32_t w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); }
+  __device__ __forceinline__ static acc_t lowest() { return as2(0xff80ff80u); }
+  __device__ __forceinline__ static acc_t fold(acc_t a, const uint4& v) {
+    return __hmax2_nan(__hmax2_nan(a, as2(v.x)), __hmax2_nan(__hmax2_nan(as2(v.y), as2(v.z)), as2(v.w)));
+  }
+  __device__ __forceinline__ static uint32_t bits(acc_t a, int i) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&a);
+    return i ? (w >> 16) : (w & 0xffffu);
+  }
+  __device__ __forceinline__ static bool all_below(const uint4& v, float bound) {
+    return __hblt2(fold(lowest(), v), __float2bfloat162_rn(bound));  // the bound is a bf16 value: exact
+  }
+};
+template <>
+struct SelMax<__half> {
+  static constexpr int PER_ACC = 2;
+  using acc_t = __half2;
+  __device__ __forceinline__ static acc_t as2(uint32_t w) { return *reinterpret_cast<const __half2*>(&w); }
+  __device__ __forceinline__ static acc_t lowest() { return as2(0xfc00fc00u); }
+  __device__ __forceinline__ static acc_t fold(acc_t a, const uint4& v) {
+    return __hmax2_nan(__hmax2_nan(a, as2(v.x)), __hmax2_nan(__hmax2_nan(as2(v.y), as2(v.z)), as2(v.w)));
+  }
+  __device__ __forceinline__ static uint32_t bits(acc_t a, int i) {
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(&a);
+    return i ? (w >> 16) : (w & 0xffffu);
+  }
+  __device__ __forceinline__ static bool all_below(const uint4& v, float bound) {
+    return __hblt2(fold(lowest(), v), __float2half2_rn(bound));  // the bound is an fp16 value: exact
+  }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_kernel(const SelectArgs a) {
   constexpr int VEC = Pack<T>::VEC;
@@ -209,11 +247,13 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
   const int nvec = a.F / VEC;
   const uint4* row = reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.acts) + (size_t)blockIdx.x * a.F);
 
-  // ---- 1. stream the row once: four running maxima per thread, NaNs noted per maximum -------------
-  float top[kSelMaxima];
+  // ---- 1. stream the row once: four accumulators of running maxima per thread (one per vector slot
+  // modulo 4; a 16-bit accumulator holds two maxima, of the even and the odd elements)
+  using Max = SelMax<T>;
+  constexpr int NKEY = kSelMaxima * Max::PER_ACC;  // maxima per thread: disjoint element sets
+  typename Max::acc_t top[kSelMaxima];
 #pragma unroll
-  for (int m = 0; m < kSelMaxima; m++) top[m] = -INFINITY;
-  unsigned nan_in = 0;
+  for (int m = 0; m < kSelMaxima; m++) top[m] = Max::lowest();
   for (int base = 0; base < nvec; base += Q * kSelThreads) {
     uint4 x[Q];
 #pragma unroll
@@ -224,34 +264,22 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
 #pragma unroll
     for (int q = 0; q < Q; q++) {
       const int v = base + q * kSelThreads + tid;
-      if (v < nvec) {
-        float f[VEC];
-        Pack<T>::unpack(x[q], f);
-        float mx = f[0];
-#pragma unroll
-        for (int j = 1; j < VEC; j++) mx = fmaxf(mx, f[j]);  // ignores NaNs; they are noted below
-        top[q % kSelMaxima] = fmaxf(top[q % kSelMaxima], mx);
-        if (vector_has_nan<T>(x[q])) nan_in |= 1u << (q % kSelMaxima);
-      }
+      if (v < nvec) top[q % kSelMaxima] = Max::fold(top[q % kSelMaxima], x[q]);
     }
   }
-  uint32_t skey[kSelMaxima];  // short keys of the maxima (a set without elements ranks lowest: -inf)
+  uint32_t skey[NKEY];  // short keys of the maxima (a set without elements ranks lowest: -inf)
 #pragma unroll
-  for (int m = 0; m < kSelMaxima; m++) {
-    uint32_t bits;
-    if (SelKey<T>::BYTES == 4) bits = __float_as_uint(top[m]);
-    else if (Pack<T>::DTYPE == FLEXSAE_BF16) bits = __float_as_uint(top[m]) >> 16;
-    else bits = (uint32_t)__half_as_ushort(__float2half_rn(top[m]));  // the maximum IS an fp16 value: exact
-    skey[m] = ((nan_in >> m) & 1u) ? 0xffffu : (SelKey<T>::key(bits) >> SHORT_SHIFT);
-  }
+  for (int m = 0; m < kSelMaxima; m++)
+#pragma unroll
+    for (int i = 0; i < Max::PER_ACC; i++) skey[m * Max::PER_ACC + i] = SelKey<T>::key(Max::bits(top[m], i)) >> SHORT_SHIFT;
 
-  // ---- 2. K-th largest short key of the 1024 maxima: two 8-bit histogram passes ----------------------
+  // ---- 2. K-th largest short key of the maxima (1024 or 2048 per row): two 8-bit histogram passes ----------------------
   int need = a.K, digit, above;
   hist[tid] = 0;
   if (tid == 0) misc[2] = 0;
   __syncthreads();
 #pragma unroll
-  for (int m = 0; m < kSelMaxima; m++) sel_hist_add(hist, (int)(skey[m] >> 8));
+  for (int m = 0; m < NKEY; m++) sel_hist_add(hist, (int)(skey[m] >> 8));
   __syncthreads();
   sel_pick_digit(hist, misc, need, &digit, &above);
   need -= above;
@@ -259,7 +287,7 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
   hist[tid] = 0;
   __syncthreads();
 #pragma unroll
-  for (int m = 0; m < kSelMaxima; m++) sel_hist_add(hist, (skey[m] >> 8) == hi ? (int)(skey[m] & 255u) : -1);
+  for (int m = 0; m < NKEY; m++) sel_hist_add(hist, (skey[m] >> 8) == hi ? (int)(skey[m] & 255u) : -1);
   __syncthreads();
   sel_pick_digit(hist, misc, need, &digit, &above);
   // lower edge of the short key's bin as a value: every element not below it is a candidate.  A bound
@@ -279,7 +307,7 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
 #pragma unroll
     for (int q = 0; q < Q; q++) {
       const int v = base + q * kSelThreads + tid;
-      if (v < nvec) {
+      if (v < nvec && !Max::all_below(x[q], bound)) {  // almost every vector is rejected here
         float f[VEC];
         Pack<T>::unpack(x[q], f);
         unsigned hits = 0;

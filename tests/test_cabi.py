@@ -117,7 +117,9 @@ def test_sharded_entry_rejects_bad_arguments_without_a_gpu():
     assert lib.flexsae_shard_buffer_bytes(65536, 2304, nv.BF16, 8, ctypes.byref(x), ctypes.byref(y), ctypes.byref(f)) == 0
     nv.set_option("lanes_bwd", 0)
     assert x.value == 2 * 65536 * 128 * 2 and y.value == x.value and f.value >= 8 * 4
+    nv.set_option("lanes_bwd", 16)
     assert lib.flexsae_shard_slots(65536, 2304, nv.BF16) == 18 + 5      # pieces + the most draining slots any lag needs
+    nv.set_option("lanes_bwd", 0)
 
 
 def test_small_allreduce_rejects_bad_arguments_without_a_gpu():
