@@ -83,6 +83,12 @@ __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// flag = max(flag, v) with release semantics: a posted update that can never move a flag backwards,
+// whatever order the updates of different publishers arrive in
+__device__ __forceinline__ void red_max_release_sys(int* p, int v) {
+  asm volatile("red.release.sys.global.max.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // One thread per (rank, flag kind) polls: lanes 0..world-1 of warp 0 the exchange flags, of warp 1
 // the scatter flags (this rank's own flags too: its own earlier slots use the same buffers).
 __device__ __forceinline__ void wait_peers(const ShardArgs& sa, bool need_exchange, int exchange_target,
@@ -329,9 +335,12 @@ __device__ __forceinline__ void switch_reduce_broadcast(const ShardArgs& sa, int
 //    of one slot can finish before those of the previous one (nothing else orders them), and then
 //    this rank's flag of the previous slot -- written by the last block of that slot -- has to go
 //    out first (`first` = there is no previous slot of this kind in this call).
-//  * The rank's own copy of the flag is stored LAST: the next slot's publisher starts from it, so
-//    whoever has seen it has all the other ranks' copies of this value behind it, and no copy can
-//    ever be overtaken by a later value and then fall back.
+//  * The rank's own copy is stored FIRST, so that its own waiting blocks and the next slot's
+//    publisher go on without an NVLink round trip; the peers' copies are updated with a posted
+//    atomic max, so that the updates of consecutive slots, issued by different blocks, may arrive in
+//    any order without a flag ever falling back.  (Publishing the peers first and the own copy last
+//    with plain stores is also correct but put two NVLink round trips into every slot's critical
+//    path: measured +0.17 ms per step on two GPUs.)
 __device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scatter, int* counter, int target, int slot,
                                                   bool first) {
   __shared__ int s_publish;
@@ -350,20 +359,19 @@ __device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scat
         if (bw.give_up(sa.p.b.status, sa.p.wait_ns)) break;
       }
     }
+    if (last) st_release_sys(sa.flags_at[sa.rank] + kind_off + sa.rank, sa.seq_base + slot);
     s_publish = last;
   }
   __syncthreads();
   if (s_publish) {  // uniform over the block
     const int value = sa.seq_base + slot;
-    if (sa.fan_out) {  // one thread per destination: the stores travel side by side
+    if (sa.fan_out) {  // one thread per destination: the updates travel side by side
       if ((int)threadIdx.x < sa.world && (int)threadIdx.x != sa.rank)
-        st_release_sys(sa.flags_at[threadIdx.x] + kind_off + sa.rank, value);
+        red_max_release_sys(sa.flags_at[threadIdx.x] + kind_off + sa.rank, value);
     } else if (threadIdx.x == 0) {
       for (int s = 0; s < sa.world; s++)
-        if (s != sa.rank) st_release_sys(sa.flags_at[s] + kind_off + sa.rank, value);
+        if (s != sa.rank) red_max_release_sys(sa.flags_at[s] + kind_off + sa.rank, value);
     }
-    __syncthreads();
-    if (threadIdx.x == 0) st_release_sys(sa.flags_at[sa.rank] + kind_off + sa.rank, value);  // after everything the block stored
   }
   __syncthreads();  // s_publish may be rewritten by the caller's next round
 }

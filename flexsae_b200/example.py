@@ -11,6 +11,10 @@ HierarchicalTopK at K = 32, 64, 128 with F = 65536, D = 2304.
     python -m flexsae_b200.example --kind topk --dtype bf16 --B 4096 --K 128 --F 65536 --D 2304
     python -m flexsae_b200.example --table --B 4096
 
+``--reference-path DIR`` also times the reference's own Triton kernels when a copy of its package
+directory (``torch-ext/flex_sae`` of corl-team/flexsae) is at hand; it is loaded from ``DIR`` under
+another module name and is not part of this library.
+
 The torch side is eager by default (``--compile`` wraps it in ``torch.compile(fullgraph=True)`` as
 the reference script does); it materialises [B, K, D] in fp32, so its batch is processed in chunks
 of ``--torch-chunk`` rows when that would not fit.
@@ -86,9 +90,27 @@ def time_one(fn: Callable, B: int, K: int, F: int, D: int, dtype: torch.dtype, d
             "gib": peak / 2 ** 30, "loss": float(loss)}
 
 
+def load_reference_package(path: str):
+    """The reference's ``flex_sae`` package from a directory that holds its ``__init__.py``, imported
+    as ``flex_sae_reference`` (this repository ships its own ``flex_sae`` alias, so the name is taken)."""
+    import importlib.util
+    import os
+    import sys
+
+    init = os.path.join(path, "__init__.py")
+    if not os.path.exists(init):
+        raise SystemExit(f"--reference-path: {init} not found (point it at the reference's torch-ext/flex_sae directory)")
+    spec = importlib.util.spec_from_file_location("flex_sae_reference", init, submodule_search_locations=[path])
+    module = importlib.util.module_from_spec(spec)
+    sys.modules["flex_sae_reference"] = module
+    spec.loader.exec_module(module)
+    return module
+
+
 def compare(kind: str, B: int, K: int, F: int, D: int, dtype: torch.dtype, device: torch.device, warmup: int, iters: int,
-            compile_torch: bool = False, torch_chunk: int = 0) -> Dict[str, object]:
-    """Both implementations on identical parameters once (closeness), then each timed on its own."""
+            compile_torch: bool = False, torch_chunk: int = 0, reference=None) -> Dict[str, object]:
+    """Both implementations on identical parameters once (closeness), then each timed on its own;
+    with ``reference`` (the reference package) its Triton kernel is timed as well."""
     fused = triton_hierarchical_sae_loss if kind == "hier" else triton_topk_sae_loss
     plain = hierarchical_sae_loss if kind == "hier" else topk_sae_loss
     if compile_torch:
@@ -101,11 +123,15 @@ def compare(kind: str, B: int, K: int, F: int, D: int, dtype: torch.dtype, devic
     _drop_grads(p)
     del p
     tol = 1e-5 if dtype == torch.float32 else 1e-2
-    return {
+    out = {
         "close": abs(loss_fused - loss_plain) <= tol * abs(loss_plain), "loss_fused": loss_fused, "loss_torch": loss_plain,
         "fused": time_one(fused, B, K, F, D, dtype, device, warmup, iters),
         "torch": time_one(plain, B, K, F, D, dtype, device, warmup, iters, chunk),
     }
+    if reference is not None:
+        ref_fn = reference.triton_hierarchical_sae_loss if kind == "hier" else reference.triton_topk_sae_loss
+        out["reference_triton"] = time_one(ref_fn, B, K, F, D, dtype, device, warmup, iters)
+    return out
 
 
 def format_table(rows: Dict[str, Dict[int, Dict[str, float]]], ks: List[int]) -> str:
@@ -130,7 +156,9 @@ def main(argv: Optional[List[str]] = None) -> Dict[str, object]:
     ap.add_argument("--compile", action="store_true", help="torch.compile(fullgraph=True) around the torch loss")
     ap.add_argument("--torch-chunk", type=int, default=0, help="rows per chunk of the torch loss (0 = whole batch)")
     ap.add_argument("--table", action="store_true", help="the README table: F=65536 D=2304 K in 32,64,128, bf16 unless --dtype")
+    ap.add_argument("--reference-path", default="", help="directory of the reference's flex_sae package: time its Triton kernels too")
     args = ap.parse_args(argv)
+    reference = load_reference_package(args.reference_path) if args.reference_path else None
     if not torch.cuda.is_available():
         raise SystemExit("flexsae_b200.example needs a CUDA device: the fused losses have no CPU path")
     device = torch.device("cuda", torch.cuda.current_device())
@@ -141,18 +169,23 @@ def main(argv: Optional[List[str]] = None) -> Dict[str, object]:
         for kind, name in (("topk", "TopK"), ("hier", "HierarchicalTopK")):
             for k in ks:
                 r = compare(kind, args.B, k, 65536, 2304, dtype, device, args.warmup, args.iters, args.compile,
-                            args.torch_chunk or 512)
+                            args.torch_chunk or 512, reference)
                 rows.setdefault(f"torch {name}", {})[k] = r["torch"]
+                if reference is not None:
+                    rows.setdefault(f"reference Triton {name}", {})[k] = r["reference_triton"]
                 rows.setdefault(f"fused (sm_100a) {name}", {})[k] = r["fused"]
         print(format_table(rows, ks))
         return {"rows": rows}
     r = compare(args.kind, args.B, args.K, args.F, args.D, DTYPES[args.dtype], device, args.warmup, args.iters,
-                args.compile, args.torch_chunk)
+                args.compile, args.torch_chunk, reference)
     print("outputs are close" if r["close"] else f"outputs MISMATCH: fused {r['loss_fused']} torch {r['loss_torch']}")
     f, t = r["fused"], r["torch"]
     print(f"fused kernels (ours): {f['ms']:.4f} ± {f['std']:.4f} ms   peak {f['gib']:.2f} GiB")
     print(f"torch loss:           {t['ms']:.4f} ± {t['std']:.4f} ms   peak {t['gib']:.2f} GiB")
     print(f"speed-up: {t['ms'] / f['ms']:.2f}x")
+    if "reference_triton" in r:
+        q = r["reference_triton"]
+        print(f"reference Triton:     {q['ms']:.4f} ± {q['std']:.4f} ms   peak {q['gib']:.2f} GiB   ({q['ms'] / f['ms']:.2f}x ours)")
     return r
 
 
