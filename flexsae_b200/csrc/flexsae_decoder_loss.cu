@@ -175,11 +175,12 @@ static size_t counter_ints(int pieces) { return 4 * counter_stride(pieces) + 2; 
 
 struct BwdPlan {
   int G, PW, pieces, row_blocks, rows_per_block;
-  size_t slab_bytes, off_slab, off_dv, off_db, off_s0, off_ctr, off_index, off_stage, off_part, total;
+  size_t slab_bytes, stage_bytes, part_bytes, off_slab, off_dv, off_db, off_s0, off_ctr, off_index, off_stage, off_part, total;
 };
 
 static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   BwdPlan p;
+  p.stage_bytes = p.part_bytes = 0;
   const int vec = 16 / (int)dtype_size(wdt);
   p.G = choose_lanes(s.F, wdt, true, g_opt.lanes_bwd);
   p.PW = p.G * vec;
@@ -195,10 +196,12 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   if (dw_mode == FLEXSAE_DW_DETERMINISTIC) {
     const int64_t n = s.B * s.K;
     off += det_index_bytes(n, s.F);
-    p.off_stage = off;
-    off = align_up(off + (size_t)n * p.PW * 4, 256);
+    p.off_stage = off;  // two buffers of staged contribution rows: one being filled, one being summed
+    p.stage_bytes = align_up((size_t)n * p.PW * 4, 256);
+    off += 2 * p.stage_bytes;
     p.off_part = off;
-    off = align_up(off + det_part_rows(n, s.F) * p.PW * 4, 256);
+    p.part_bytes = align_up(det_part_rows(n, s.F) * p.PW * 4, 256);
+    off += 2 * p.part_bytes;
   }
   p.off_dv = off;
   off = align_up(off + (size_t)p.pieces * s.B * s.K * 4, 256);
@@ -225,6 +228,34 @@ static FwdPlan plan_fwd(const Shape& s, int wdt) {
   p.pieces = (int)((s.D + p.PW - 1) / p.PW);
   p.total = align_up((size_t)p.pieces * s.B * 4, 256);
   return p;
+}
+
+// Deterministic mode runs the ordered sums of one column piece while the next piece's walk fills the
+// other staging buffer.  The sums go to a helper stream (one per calling thread and device, created on
+// first use together with four events) that is forked from and joined back into the caller's stream
+// inside every call, so the caller sees ordinary stream order.
+struct DetOverlap {
+  cudaStream_t aux = nullptr;
+  cudaEvent_t walked[2] = {nullptr, nullptr}, summed[2] = {nullptr, nullptr};
+};
+static cudaError_t det_overlap(DetOverlap** out) {
+  static thread_local DetOverlap per_device[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  DetOverlap& d = per_device[dev];
+  if (!d.aux) {
+    cudaStream_t aux;
+    if ((e = cudaStreamCreateWithFlags(&aux, cudaStreamNonBlocking)) != cudaSuccess) return e;
+    for (int i = 0; i < 2; i++) {
+      if ((e = cudaEventCreateWithFlags(&d.walked[i], cudaEventDisableTiming)) != cudaSuccess) return e;
+      if ((e = cudaEventCreateWithFlags(&d.summed[i], cudaEventDisableTiming)) != cudaSuccess) return e;
+    }
+    d.aux = aux;
+  }
+  *out = &d;
+  return cudaSuccess;
 }
 
 constexpr size_t kRingBytes = (size_t)kRingSlots * kThreads * sizeof(uint4);  // 2 KiB per slot and CTA
@@ -568,20 +599,33 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     DetIndex ix;
     e = det_prepare(indices, B * K, F, ws + p.off_index, &ix, st, &t_launches);
     if (e != cudaSuccess) return fail((int)e, "sort launches failed: %s", cudaGetErrorString(e));
-    a.stage = reinterpret_cast<float*>(ws + p.off_stage);
     a.slot_of = ix.slot_of;
     a.slab = a.conv_slab = nullptr;
     a.conv_piece = -1;
-    float* part = reinterpret_cast<float*>(ws + p.off_part);
+    DetOverlap* ov = nullptr;
+    e = det_overlap(&ov);
+    if (e != cudaSuccess) return fail((int)e, "helper stream set-up failed: %s", cudaGetErrorString(e));
     for (int i = 0; i < p.pieces; i++) {
+      const int buf = i & 1;
       a.piece = i;
+      a.stage = reinterpret_cast<float*>(ws + p.off_stage + buf * p.stage_bytes);
+      float* part = reinterpret_cast<float*>(ws + p.off_part + buf * p.part_bytes);
+      if (i >= 2) e = cudaStreamWaitEvent(st, ov->summed[buf], 0);  // this staging buffer has been summed
+      if (e != cudaSuccess) return fail((int)e, "stream wait failed: %s", cudaGetErrorString(e));
 #define CALL_DET(T, G, H) launch_bwd_det<T, G, H>(a, st)
       e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_DET);
 #undef CALL_DET
       if (e != cudaSuccess) return fail((int)e, "backward launch failed: %s", cudaGetErrorString(e));
-      e = det_reduce_piece(weight_dtype, p.G, a.stage, ix, (int)F, (int)D, i, part, dweight, st, &t_launches);
+      if ((e = cudaEventRecord(ov->walked[buf], st)) != cudaSuccess || (e = cudaStreamWaitEvent(ov->aux, ov->walked[buf], 0)) != cudaSuccess)
+        return fail((int)e, "stream fork failed: %s", cudaGetErrorString(e));
+      e = det_reduce_piece(weight_dtype, p.G, a.stage, ix, (int)F, (int)D, i, part, dweight, ov->aux, &t_launches);
       if (e != cudaSuccess) return fail((int)e, "ordered sum launch failed: %s", cudaGetErrorString(e));
+      if ((e = cudaEventRecord(ov->summed[buf], ov->aux)) != cudaSuccess)
+        return fail((int)e, "event record failed: %s", cudaGetErrorString(e));
     }
+    for (int buf = 0; buf < 2 && buf < p.pieces; buf++)  // join: dweight is complete in the caller's stream order
+      if ((e = cudaStreamWaitEvent(st, ov->summed[buf], 0)) != cudaSuccess)
+        return fail((int)e, "stream join failed: %s", cudaGetErrorString(e));
   } else {
   // Both slabs are cleared once here; afterwards every conversion leaves its slab cleared.
   // Launch i accumulates piece i into slab i%2 and converts piece i-1 out of the other slab;

@@ -13,7 +13,7 @@
 
 namespace flexsae {
 
-static constexpr int kSortTile = 4096;   // keys per CTA in the histogram / scatter passes
+static constexpr int kSortTile = 1024;   // keys per CTA in the histogram / scatter passes (one warp walks a tile in order)
 static constexpr int kItemSlots = 32;    // sorted slots per first-level item
 
 // ---- stable LSD radix sort of (key = decoder row, value = position) -----------------------------
