@@ -196,12 +196,12 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   if (dw_mode == FLEXSAE_DW_DETERMINISTIC) {
     const int64_t n = s.B * s.K;
     off += det_index_bytes(n, s.F);
-    p.off_stage = off;  // two buffers of staged contribution rows: one being filled, one being summed
+    p.off_stage = off;  // the staged contribution rows of one column piece
     p.stage_bytes = align_up((size_t)n * p.PW * 4, 256);
-    off += 2 * p.stage_bytes;
+    off += p.stage_bytes;
     p.off_part = off;
     p.part_bytes = align_up(det_part_rows(n, s.F) * p.PW * 4, 256);
-    off += 2 * p.part_bytes;
+    off += p.part_bytes;
   }
   p.off_dv = off;
   off = align_up(off + (size_t)p.pieces * s.B * s.K * 4, 256);
@@ -228,34 +228,6 @@ static FwdPlan plan_fwd(const Shape& s, int wdt) {
   p.pieces = (int)((s.D + p.PW - 1) / p.PW);
   p.total = align_up((size_t)p.pieces * s.B * 4, 256);
   return p;
-}
-
-// Deterministic mode runs the ordered sums of one column piece while the next piece's walk fills the
-// other staging buffer.  The sums go to a helper stream (one per calling thread and device, created on
-// first use together with four events) that is forked from and joined back into the caller's stream
-// inside every call, so the caller sees ordinary stream order.
-struct DetOverlap {
-  cudaStream_t aux = nullptr;
-  cudaEvent_t walked[2] = {nullptr, nullptr}, summed[2] = {nullptr, nullptr};
-};
-static cudaError_t det_overlap(DetOverlap** out) {
-  static thread_local DetOverlap per_device[64];
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  DetOverlap& d = per_device[dev];
-  if (!d.aux) {
-    cudaStream_t aux;
-    if ((e = cudaStreamCreateWithFlags(&aux, cudaStreamNonBlocking)) != cudaSuccess) return e;
-    for (int i = 0; i < 2; i++) {
-      if ((e = cudaEventCreateWithFlags(&d.walked[i], cudaEventDisableTiming)) != cudaSuccess) return e;
-      if ((e = cudaEventCreateWithFlags(&d.summed[i], cudaEventDisableTiming)) != cudaSuccess) return e;
-    }
-    d.aux = aux;
-  }
-  *out = &d;
-  return cudaSuccess;
 }
 
 constexpr size_t kRingBytes = (size_t)kRingSlots * kThreads * sizeof(uint4);  // 2 KiB per slot and CTA
@@ -602,30 +574,17 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     a.slot_of = ix.slot_of;
     a.slab = a.conv_slab = nullptr;
     a.conv_piece = -1;
-    DetOverlap* ov = nullptr;
-    e = det_overlap(&ov);
-    if (e != cudaSuccess) return fail((int)e, "helper stream set-up failed: %s", cudaGetErrorString(e));
+    a.stage = reinterpret_cast<float*>(ws + p.off_stage);
+    float* part = reinterpret_cast<float*>(ws + p.off_part);
     for (int i = 0; i < p.pieces; i++) {
-      const int buf = i & 1;
       a.piece = i;
-      a.stage = reinterpret_cast<float*>(ws + p.off_stage + buf * p.stage_bytes);
-      float* part = reinterpret_cast<float*>(ws + p.off_part + buf * p.part_bytes);
-      if (i >= 2) e = cudaStreamWaitEvent(st, ov->summed[buf], 0);  // this staging buffer has been summed
-      if (e != cudaSuccess) return fail((int)e, "stream wait failed: %s", cudaGetErrorString(e));
 #define CALL_DET(T, G, H) launch_bwd_det<T, G, H>(a, st)
       e = FLEXSAE_DISPATCH(weight_dtype, p.G, kind, CALL_DET);
 #undef CALL_DET
       if (e != cudaSuccess) return fail((int)e, "backward launch failed: %s", cudaGetErrorString(e));
-      if ((e = cudaEventRecord(ov->walked[buf], st)) != cudaSuccess || (e = cudaStreamWaitEvent(ov->aux, ov->walked[buf], 0)) != cudaSuccess)
-        return fail((int)e, "stream fork failed: %s", cudaGetErrorString(e));
-      e = det_reduce_piece(weight_dtype, p.G, a.stage, ix, (int)F, (int)D, i, part, dweight, ov->aux, &t_launches);
+      e = det_reduce_piece(weight_dtype, p.G, a.stage, ix, (int)F, (int)D, i, part, dweight, st, &t_launches);
       if (e != cudaSuccess) return fail((int)e, "ordered sum launch failed: %s", cudaGetErrorString(e));
-      if ((e = cudaEventRecord(ov->summed[buf], ov->aux)) != cudaSuccess)
-        return fail((int)e, "event record failed: %s", cudaGetErrorString(e));
     }
-    for (int buf = 0; buf < 2 && buf < p.pieces; buf++)  // join: dweight is complete in the caller's stream order
-      if ((e = cudaStreamWaitEvent(st, ov->summed[buf], 0)) != cudaSuccess)
-        return fail((int)e, "stream join failed: %s", cudaGetErrorString(e));
   } else {
   // Both slabs are cleared once here; afterwards every conversion leaves its slab cleared.
   // Launch i accumulates piece i into slab i%2 and converts piece i-1 out of the other slab;
@@ -767,7 +726,15 @@ int flexsae_loss_bwd_sharded(int kind, const int64_t* indices, const void* weigh
 namespace flexsae {
 template <typename T>
 static cudaError_t launch_topk_select(const SelectArgs& a, int64_t B, cudaStream_t st) {
-  topk_select_kernel<T><<<(unsigned)B, kSelThreads, 0, st>>>(a);
+  // one maximum per 16-byte vector of the row in shared memory, if the row is short enough for that
+  // to leave four CTAs per SM (F = 65536 in bf16: 16 KiB)
+  const size_t per_vec = sizeof(T) == 4 ? 4 : 2;
+  const size_t vmax_bytes = (size_t)(a.F / (16 / (int)sizeof(T))) * per_vec;
+  if (vmax_bytes <= 32 * 1024) {
+    topk_select_kernel<T, true><<<(unsigned)B, kSelThreads, vmax_bytes, st>>>(a);
+  } else {
+    topk_select_kernel<T, false><<<(unsigned)B, kSelThreads, 0, st>>>(a);
+  }
   t_launches++;
   return cudaGetLastError();
 }

@@ -194,10 +194,11 @@ struct SelMax<float> {
     return max_nan(max_nan(a, __uint_as_float(v.x)), max_nan(max_nan(__uint_as_float(v.y), __uint_as_float(v.z)), __uint_as_float(v.w)));
   }
   __device__ __forceinline__ static uint32_t bits(acc_t a, int) { return __float_as_uint(a); }
-  // true when every element of the vector is below the bound (so none of them is a candidate)
-  __device__ __forceinline__ static bool all_below(const uint4& v, float bound) {
-    return fold(lowest(), v) < bound;  // false for a NaN in the vector or in the bound
-  }
+  // the largest element of one vector, as kept in shared memory between the two passes, and the
+  // test "every element of that vector is below the bound" (false for a NaN on either side)
+  using vmax_t = float;
+  __device__ __forceinline__ static vmax_t vector_max(const uint4& v) { return fold(lowest(), v); }
+  __device__ __forceinline__ static bool below(vmax_t m, float bound) { return m < bound; }
 };
 template <>
 struct SelMax<__nv_bfloat16> {
@@ -212,9 +213,12 @@ struct SelMax<__nv_bfloat16> {
     const uint32_t w = *reinterpret_cast<const uint32_t*>(&a);
     return i ? (w >> 16) : (w & 0xffffu);
   }
-  __device__ __forceinline__ static bool all_below(const uint4& v, float bound) {
-    return __hblt2(fold(lowest(), v), __float2bfloat162_rn(bound));  // the bound is a bf16 value: exact
+  using vmax_t = __nv_bfloat16;
+  __device__ __forceinline__ static vmax_t vector_max(const uint4& v) {
+    const acc_t m = fold(lowest(), v);
+    return __hmax_nan(__low2bfloat16(m), __high2bfloat16(m));
   }
+  __device__ __forceinline__ static bool below(vmax_t m, float bound) { return __bfloat162float(m) < bound; }
 };
 template <>
 struct SelMax<__half> {
@@ -229,13 +233,20 @@ struct SelMax<__half> {
     const uint32_t w = *reinterpret_cast<const uint32_t*>(&a);
     return i ? (w >> 16) : (w & 0xffffu);
   }
-  __device__ __forceinline__ static bool all_below(const uint4& v, float bound) {
-    return __hblt2(fold(lowest(), v), __float2half2_rn(bound));  // the bound is an fp16 value: exact
+  using vmax_t = __half;
+  __device__ __forceinline__ static vmax_t vector_max(const uint4& v) {
+    const acc_t m = fold(lowest(), v);
+    return __hmax_nan(__low2half(m), __high2half(m));
   }
+  __device__ __forceinline__ static bool below(vmax_t m, float bound) { return __half2float(m) < bound; }
 };
 
-template <typename T>
+// KEEP_MAX: the maximum of every 16-byte vector is kept in (dynamic) shared memory during the first
+// pass, so that the second pass touches only the few vectors that hold a candidate; without it (rows
+// too long for that) the second pass reads the whole row again, from L2.
+template <typename T, bool KEEP_MAX>
 __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_kernel(const SelectArgs a) {
+  extern __shared__ __align__(16) unsigned char sel_dyn[];
   constexpr int VEC = Pack<T>::VEC;
   constexpr int NPASS = SelKey<T>::BYTES;
   constexpr int SHORT_SHIFT = 8 * NPASS - 16;  // the top 16 bits of a key are its "short key"
@@ -251,6 +262,7 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
   // modulo 4; a 16-bit accumulator holds two maxima, of the even and the odd elements)
   using Max = SelMax<T>;
   constexpr int NKEY = kSelMaxima * Max::PER_ACC;  // maxima per thread: disjoint element sets
+  typename Max::vmax_t* vmax = reinterpret_cast<typename Max::vmax_t*>(sel_dyn);  // [nvec] when KEEP_MAX
   typename Max::acc_t top[kSelMaxima];
 #pragma unroll
   for (int m = 0; m < kSelMaxima; m++) top[m] = Max::lowest();
@@ -264,7 +276,10 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
 #pragma unroll
     for (int q = 0; q < Q; q++) {
       const int v = base + q * kSelThreads + tid;
-      if (v < nvec) top[q % kSelMaxima] = Max::fold(top[q % kSelMaxima], x[q]);
+      if (v < nvec) {
+        top[q % kSelMaxima] = Max::fold(top[q % kSelMaxima], x[q]);
+        if (KEEP_MAX) vmax[v] = Max::vector_max(x[q]);  // read back by this same thread only
+      }
     }
   }
   uint32_t skey[NKEY];  // short keys of the maxima (a set without elements ranks lowest: -inf)
@@ -296,30 +311,37 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
   const uint32_t bound_key = ((hi << 8) | (uint32_t)digit) << SHORT_SHIFT;
   const float bound = SelKey<T>::value(bound_key);
 
-  // ---- 3. candidates: second read of the row (L2), unordered append ----------------------------------
-  for (int base = 0; base < nvec; base += Q * kSelThreads) {
-    uint4 x[Q];
+  // ---- 3. candidates, appended in any order.  With the vector maxima at hand only the vectors that hold
+  // a candidate are read again (a few hundred 16-byte loads per row, L2 hits); else the whole row is.
+  auto take_from = [&](const uint4& x, int v) {
+    float f[VEC];
+    Pack<T>::unpack(x, f);
+    unsigned hits = 0;
 #pragma unroll
-    for (int q = 0; q < Q; q++) {
-      const int v = base + q * kSelThreads + tid;
-      if (v < nvec) x[q] = __ldg(row + v);
+    for (int j = 0; j < VEC; j++) hits |= (unsigned)(!(f[j] < bound)) << j;  // a NaN is never below
+    while (hits) {
+      const int j = __ffs(hits) - 1;
+      hits &= hits - 1;
+      const int at = atomicAdd(&misc[2], 1);
+      if (at < kSelCandidates)
+        cand[at] = ((unsigned long long)SelKey<T>::key(vector_bits<T>(x, j)) << 32) | (uint32_t)~(uint32_t)(v * VEC + j);
     }
+  };
+  if (KEEP_MAX) {
+    for (int v = tid; v < nvec; v += kSelThreads)
+      if (!Max::below(vmax[v], bound)) take_from(__ldg(row + v), v);
+  } else {
+    for (int base = 0; base < nvec; base += Q * kSelThreads) {
+      uint4 x[Q];
 #pragma unroll
-    for (int q = 0; q < Q; q++) {
-      const int v = base + q * kSelThreads + tid;
-      if (v < nvec && !Max::all_below(x[q], bound)) {  // almost every vector is rejected here
-        float f[VEC];
-        Pack<T>::unpack(x[q], f);
-        unsigned hits = 0;
+      for (int q = 0; q < Q; q++) {
+        const int v = base + q * kSelThreads + tid;
+        if (v < nvec) x[q] = __ldg(row + v);
+      }
 #pragma unroll
-        for (int j = 0; j < VEC; j++) hits |= (unsigned)(!(f[j] < bound)) << j;  // a NaN is never below
-        while (hits) {
-          const int j = __ffs(hits) - 1;
-          hits &= hits - 1;
-          const int at = atomicAdd(&misc[2], 1);
-          if (at < kSelCandidates)
-            cand[at] = ((unsigned long long)SelKey<T>::key(vector_bits<T>(x[q], j)) << 32) | (uint32_t)~(uint32_t)(v * VEC + j);
-        }
+      for (int q = 0; q < Q; q++) {
+        const int v = base + q * kSelThreads + tid;
+        if (v < nvec && !Max::below(Max::vector_max(x[q]), bound)) take_from(x[q], v);
       }
     }
   }
@@ -392,28 +414,53 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
     n_cand = a.K;
   }
 
-  // ---- 4. bitonic sort, descending: larger key first, equal keys by ascending index; padding sorts last
-  int np = a.Kp;
-  while (np < n_cand) np <<= 1;
-  for (int i = n_cand + tid; i < np; i += kSelThreads) cand[i] = 0ull;
-  __syncthreads();
-  for (int k2 = 2; k2 <= np; k2 <<= 1) {
-    for (int j = k2 >> 1; j > 0; j >>= 1) {
-      for (int t = tid; t < (np >> 1); t += kSelThreads) {
-        const int i = 2 * t - (t & (j - 1));  // the lower index of the t-th pair at distance j
-        const int partner = i + j;
-        const unsigned long long x = cand[i], y = cand[partner];
-        const bool descending = (i & k2) == 0;
-        if (descending ? x < y : x > y) {
-          cand[i] = y;
-          cand[partner] = x;
-        }
+  // ---- 4. order: larger key first, equal keys by ascending index (entries are distinct: they carry
+  // their index).  Short lists: every thread counts how many entries beat its own -- no barriers;
+  // long lists: a bitonic network.
+  const unsigned long long* sorted = cand;
+  if (n_cand <= 2 * kSelThreads) {
+    constexpr int kOut = kSelCandidates / 2;  // the ranked entries go to the upper half of the list
+    unsigned long long mine[2];
+    int rank[2] = {0, 0};
+#pragma unroll
+    for (int c = 0; c < 2; c++) mine[c] = tid + c * kSelThreads < n_cand ? cand[tid + c * kSelThreads] : 0ull;
+    if (n_cand <= kSelThreads) {
+      for (int j = 0; j < n_cand; j++) rank[0] += cand[j] > mine[0];
+    } else {
+      for (int j = 0; j < n_cand; j++) {
+        const unsigned long long o = cand[j];
+        rank[0] += o > mine[0];
+        rank[1] += o > mine[1];
       }
-      __syncthreads();
+    }
+#pragma unroll
+    for (int c = 0; c < 2; c++)
+      if (tid + c * kSelThreads < n_cand && rank[c] < a.K) cand[kOut + rank[c]] = mine[c];
+    __syncthreads();
+    sorted = cand + kOut;
+  } else {
+    int np = a.Kp;
+    while (np < n_cand) np <<= 1;
+    for (int i = n_cand + tid; i < np; i += kSelThreads) cand[i] = 0ull;  // padding sorts last
+    __syncthreads();
+    for (int k2 = 2; k2 <= np; k2 <<= 1) {
+      for (int j = k2 >> 1; j > 0; j >>= 1) {
+        for (int t = tid; t < (np >> 1); t += kSelThreads) {
+          const int i = 2 * t - (t & (j - 1));  // the lower index of the t-th pair at distance j
+          const int partner = i + j;
+          const unsigned long long x = cand[i], y = cand[partner];
+          const bool descending = (i & k2) == 0;
+          if (descending ? x < y : x > y) {
+            cand[i] = y;
+            cand[partner] = x;
+          }
+        }
+        __syncthreads();
+      }
     }
   }
   for (int i = tid; i < a.K; i += kSelThreads) {
-    const unsigned long long e = cand[i];
+    const unsigned long long e = sorted[i];
     float val = SelKey<T>::value((uint32_t)(e >> 32));
     if (a.relu) val = val < 0.f ? 0.f : val;  // a NaN stays a NaN (fmaxf would hide it)
     store_scalar(a.vals, a.vals_dtype, (size_t)blockIdx.x * a.K + i, val);

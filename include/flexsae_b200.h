@@ -10,10 +10,7 @@
  * pointer unless its name ends in _host; all tensors are dense row-major.  No entry point
  * allocates or frees device memory, synchronises the stream or touches the default stream:
  * work is enqueued on the stream handle passed in (a cudaStream_t cast to void*; NULL is the
- * legacy default stream).  One exception to "only that stream": flexsae_loss_bwd in deterministic
- * mode runs its ordered sums on a helper stream of the library (created with four events on the
- * calling thread's first such call on a device), forked from the caller's stream and joined back into
- * it before the call returns, so that the caller still sees plain stream order.  Scratch memory comes from the caller, sized by the *_workspace_bytes
+ * legacy default stream).  Scratch memory comes from the caller, sized by the *_workspace_bytes
  * functions.  Return value: 0 on success, a negative FLEXSAE_E* code for rejected arguments,
  * or the positive cudaError_t of a failed launch; flexsae_last_error() describes the last
  * failure of the calling thread.
