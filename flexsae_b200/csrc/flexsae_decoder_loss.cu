@@ -182,7 +182,9 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
   BwdPlan p;
   p.stage_bytes = p.part_bytes = 0;
   const int vec = 16 / (int)dtype_size(wdt);
-  p.G = choose_lanes(s.F, wdt, true, g_opt.lanes_bwd);
+  // deterministic mode keeps no fp32 slab in L2 (its contributions stream through a staging buffer),
+  // so only the decoder columns count, and wider pieces mean fewer launches and longer staged rows
+  p.G = choose_lanes(s.F, wdt, dw_mode == FLEXSAE_DW_ATOMIC, g_opt.lanes_bwd);
   p.PW = p.G * vec;
   p.pieces = (int)((s.D + p.PW - 1) / p.PW);
   p.rows_per_block = (int)((s.B + kMaxRowBlocks - 1) / kMaxRowBlocks);

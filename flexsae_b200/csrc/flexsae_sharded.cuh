@@ -116,30 +116,33 @@ __device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, i
   constexpr int IL = FLEXSAE_CONVERT_IL;
   const int F = sa.p.b.F;
   const int rpr = sa.rows_per_rank;
-  const size_t total = (size_t)F * G;
+  const size_t total = (size_t)F * G;  // 16-byte items of the piece
   const size_t stride = (size_t)nctas * kThreads;
   const size_t slot_off = ((size_t)(piece & 1) * sa.world + sa.rank) * rpr * PW;  // [parity][sender = me]
   // Rotated sweep: every rank starts at the row block of its right-hand neighbour; the ranks move
-  // in step, so at any moment they store to different owners instead of all to one.
+  // in step, so at any moment they store to different owners instead of all to one.  Nothing per
+  // item is kept across the loads (the rotated index is recomputed): the loop's loads in flight
+  // are what the conversion's speed hangs on.
   const size_t rot = sa.rotate ? ((size_t)((sa.rank + 1) % sa.world) * rpr % F) * G : 0;
+  auto item_of = [&](size_t j) { return j + rot < total ? j + rot : j + rot - total; };
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
   for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
     float4 lo[IL], hi[IL];
-    size_t item[IL];
 #pragma unroll
     for (int q = 0; q < IL; q++) {
       const size_t j = base + q * stride;
-      item[q] = j + rot < total ? j + rot : j + rot - total;  // only used when j < total
       if (j < total) {
-        float* sp = slab + (item[q] / G) * PW + (item[q] % G) * 4;
+        const size_t i = item_of(j);
+        float* sp = slab + (i / G) * PW + (i % G) * 4;
         lo[q] = __ldcg(reinterpret_cast<const float4*>(sp));
         if (VEC == 8) hi[q] = __ldcg(reinterpret_cast<const float4*>(sp + G * 4));
       }
     }
 #pragma unroll
     for (int q = 0; q < IL; q++) {
-      const size_t i = item[q];
-      if (base + q * stride < total) {
+      const size_t j = base + q * stride;
+      if (j < total) {
+        const size_t i = item_of(j);
         const int f = (int)(i / G), lig = (int)(i % G);
         float* sp = slab + (size_t)f * PW + lig * 4;
         *reinterpret_cast<float4*>(sp) = zero;
@@ -343,8 +346,8 @@ __device__ __forceinline__ void switch_reduce_broadcast(const ShardArgs& sa, int
 //    path: measured +0.17 ms per step on two GPUs.)
 __device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scatter, int* counter, int target, int slot,
                                                   bool first) {
-  __shared__ int s_publish;
   const int kind_off = scatter ? kScatterFlags : 0;
+  int publish = 0;  // decided by thread 0, handed to the block through the barrier's vote (no shared variable)
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();  // this block's peer stores and dweight writes before the count moves
@@ -360,10 +363,9 @@ __device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scat
       }
     }
     if (last) st_release_sys(sa.flags_at[sa.rank] + kind_off + sa.rank, sa.seq_base + slot);
-    s_publish = last;
+    publish = last;
   }
-  __syncthreads();
-  if (s_publish) {  // uniform over the block
+  if (__syncthreads_or(publish)) {  // uniform over the block
     const int value = sa.seq_base + slot;
     if (sa.fan_out) {  // one thread per destination: the updates travel side by side
       if ((int)threadIdx.x < sa.world && (int)threadIdx.x != sa.rank)
@@ -373,7 +375,6 @@ __device__ __forceinline__ void count_and_publish(const ShardArgs& sa, bool scat
         if (s != sa.rank) red_max_release_sys(sa.flags_at[s] + kind_off + sa.rank, value);
     }
   }
-  __syncthreads();  // s_publish may be rewritten by the caller's next round
 }
 
 // Exchange work of slot p (all threads of an exchange block): wait for what it reads to be
@@ -425,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
   int p, exch_idx = -1, conv_idx = -1, unit_block = -1;
   int exch_n = E;  // blocks that share the exchange work of this slot
   const bool in_place = sa.dweight_at[0] != nullptr && sa.mc_inbox == nullptr;
-  const int bid = role_index(pa.ticket);
+  const int bid = role_index(pa.ticket, smem);
   if (bid >= body) {  // draining slots: no unit blocks
     const int t = bid - body;
     const int dper = E + pa.conv_blocks;
