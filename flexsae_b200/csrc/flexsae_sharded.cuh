@@ -1,6 +1,9 @@
 // Batch-sharded backward: the single-launch pipeline with the cross-GPU sum of dweight done by its
 // own blocks over NVLink peer memory.
 #pragma once
+#ifdef FLEXSAE_VAR_OLDKERNEL
+#include FLEXSAE_VAR_OLDKERNEL
+#else
 
 #include "flexsae_backward.cuh"
 
@@ -109,7 +112,12 @@ __device__ __forceinline__ void wait_peers(const ShardArgs& sa, bool need_exchan
 
 // local slab (fp32, permuted columns) -> decoder dtype, natural column order, each decoder row
 // stored into the inbox of the rank owning its row block; clears the slab
-template <typename T, int G>
+// ROTATE: the sweep over the slab is cut into chunks of one grid stride (a few thousand decoder rows)
+// and every rank starts at a different chunk, so that at any moment the ranks store to different
+// owners instead of all to one.  Only the chunk order changes -- the per-item arithmetic is that of
+// the plain sweep: an earlier form that rotated every item index separately made this loop, and
+// with it every slot of the pipeline, 25 % slower even with the rotation switched off.
+template <typename T, int G, bool ROTATE>
 __device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, int piece, int cta, int nctas) {
   constexpr int VEC = Pack<T>::VEC;
   constexpr int PW = G * VEC;
@@ -119,20 +127,26 @@ __device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, i
   const size_t total = (size_t)F * G;  // 16-byte items of the piece
   const size_t stride = (size_t)nctas * kThreads;
   const size_t slot_off = ((size_t)(piece & 1) * sa.world + sa.rank) * rpr * PW;  // [parity][sender = me]
-  // Rotated sweep: every rank starts at the row block of its right-hand neighbour; the ranks move
-  // in step, so at any moment they store to different owners instead of all to one.  Nothing per
-  // item is kept across the loads (the rotated index is recomputed): the loop's loads in flight
-  // are what the conversion's speed hangs on.
-  const size_t rot = sa.rotate ? ((size_t)((sa.rank + 1) % sa.world) * rpr % F) * G : 0;
-  auto item_of = [&](size_t j) { return j + rot < total ? j + rot : j + rot - total; };
   const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (size_t base = (size_t)cta * kThreads + threadIdx.x; base < total; base += stride * IL) {
+  const int n_chunks = (int)((total + stride - 1) / stride);
+  const int shift = ROTATE ? (int)((long long)n_chunks * ((sa.rank + 1) % sa.world) / sa.world) : 0;
+  const size_t first = (size_t)cta * kThreads + threadIdx.x;
+  // item handled as number q of the group of IL chunks that starts at chunk c0 (>= total: none)
+  auto item_at = [&](int c0, int q) -> size_t {
+    int c = c0 + q;
+    if (c >= n_chunks) return total;
+    if (ROTATE) {
+      c += shift;
+      if (c >= n_chunks) c -= n_chunks;
+    }
+    return (size_t)c * stride + first;
+  };
+  for (int c0 = 0; c0 < n_chunks; c0 += IL) {
     float4 lo[IL], hi[IL];
 #pragma unroll
     for (int q = 0; q < IL; q++) {
-      const size_t j = base + q * stride;
-      if (j < total) {
-        const size_t i = item_of(j);
+      const size_t i = item_at(c0, q);
+      if (i < total) {
         float* sp = slab + (i / G) * PW + (i % G) * 4;
         lo[q] = __ldcg(reinterpret_cast<const float4*>(sp));
         if (VEC == 8) hi[q] = __ldcg(reinterpret_cast<const float4*>(sp + G * 4));
@@ -140,9 +154,8 @@ __device__ __forceinline__ void slab_scatter(float* slab, const ShardArgs& sa, i
     }
 #pragma unroll
     for (int q = 0; q < IL; q++) {
-      const size_t j = base + q * stride;
-      if (j < total) {
-        const size_t i = item_of(j);
+      const size_t i = item_at(c0, q);
+      if (i < total) {
         const int f = (int)(i / G), lig = (int)(i % G);
         float* sp = slab + (size_t)f * PW + lig * 4;
         *reinterpret_cast<float4*>(sp) = zero;
@@ -468,7 +481,8 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
       wait_peers(sa, true, sa.seq_base + p - 1, false, 0);  // the owners have reduced what this half of their inbox held
       FLEXSAE_TRACE_MIN(p, kTrConvStart);
       if (sa.mc_inbox) slab_to_own_copy<T, G>(pa.slabs[q % pa.nslabs], sa, q, conv_idx, pa.conv_blocks);
-      else slab_scatter<T, G>(pa.slabs[q % pa.nslabs], sa, q, conv_idx, pa.conv_blocks);
+      else if (sa.rotate) slab_scatter<T, G, true>(pa.slabs[q % pa.nslabs], sa, q, conv_idx, pa.conv_blocks);
+      else slab_scatter<T, G, false>(pa.slabs[q % pa.nslabs], sa, q, conv_idx, pa.conv_blocks);
     }
     signal_done(pa.conv_done + p);
     FLEXSAE_TRACE_MAX(p, kTrConvEnd);
@@ -484,3 +498,4 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
 }
 
 }  // namespace flexsae
+#endif  // FLEXSAE_VAR_OLDKERNEL
