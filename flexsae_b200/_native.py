@@ -18,7 +18,7 @@ from . import build as _build
 
 F32, BF16, F16 = 0, 1, 2
 TOPK, HIER = 0, 1
-DW_ATOMIC, DW_DETERMINISTIC = 0, 1
+DW_ATOMIC, DW_DETERMINISTIC, DW_ATOMIC_SHARDED = 0, 1, 2
 STATUS_BAD_INDEX = 1
 STATUS_PIPELINE_TIMEOUT = 2
 

@@ -34,6 +34,7 @@ namespace flexsae {
 struct Options {
   int lanes_fwd = 0;      // 0 = auto
   int lanes_bwd = 0;      // 0 = auto
+  int lanes_sharded = 0;  // batch-sharded backward; 0 = lanes_bwd if that is set, else auto with 1.5 x the L2 budget
   int l2_budget_mb = 64;  // one piece of decoder columns (+ its fp32 slabs) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
@@ -105,10 +106,10 @@ static int check_shape(int kind, const Shape& s, int wdt) {
 
 // lanes per batch row: the widest group whose per-piece working set -- the piece's decoder columns
 // plus, in the backward, all fp32 slabs in rotation -- fits the L2 budget
-static int choose_lanes(int64_t F, int wdt, bool with_slab, int forced) {
+static int choose_lanes(int64_t F, int wdt, bool with_slab, int forced, double budget_scale = 1.0) {
   if (forced == 8 || forced == 16 || forced == 32) return forced;
   const int vec = 16 / (int)dtype_size(wdt);
-  const double budget = (double)g_opt.l2_budget_mb * 1048576.0;
+  const double budget = (double)g_opt.l2_budget_mb * 1048576.0 * budget_scale;
   // an fp32 decoder accumulates straight into its dweight columns: one fp32 table instead of the slabs
   const int tables = !with_slab ? 0 : ((wdt == FLEXSAE_F32 && g_opt.direct_f32 && g_opt.pipeline) ? 1 : g_opt.slabs);
   auto bytes = [&](int G) { return (double)F * G * vec * (dtype_size(wdt) + 4.0 * tables); };
@@ -178,13 +179,18 @@ struct BwdPlan {
   size_t slab_bytes, stage_bytes, part_bytes, off_slab, off_dv, off_db, off_s0, off_ctr, off_index, off_stage, off_part, total;
 };
 
-static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode) {
+// `sharded`: the plan of flexsae_loss_bwd_sharded.  Its slots carry a cross-GPU hand-shake each, so
+// wider (fewer) pieces pay even when their slabs no longer quite fit: measured on two GPUs at the
+// headline shape, 16 lanes 1.69 ms per step against 1.78 with 8, while one GPU alone prefers 8
+// (1.56 against 1.59).  Hence half as much again of the L2 budget, and its own override.
+static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode, bool sharded = false) {
   BwdPlan p;
   p.stage_bytes = p.part_bytes = 0;
   const int vec = 16 / (int)dtype_size(wdt);
   // deterministic mode keeps no fp32 slab in L2 (its contributions stream through a staging buffer),
   // so only the decoder columns count, and wider pieces mean fewer launches and longer staged rows
-  p.G = choose_lanes(s.F, wdt, dw_mode == FLEXSAE_DW_ATOMIC, g_opt.lanes_bwd);
+  p.G = sharded ? choose_lanes(s.F, wdt, true, g_opt.lanes_sharded ? g_opt.lanes_sharded : g_opt.lanes_bwd, 1.5)
+                : choose_lanes(s.F, wdt, dw_mode == FLEXSAE_DW_ATOMIC, g_opt.lanes_bwd);
   p.PW = p.G * vec;
   p.pieces = (int)((s.D + p.PW - 1) / p.PW);
   p.rows_per_block = (int)((s.B + kMaxRowBlocks - 1) / kMaxRowBlocks);
@@ -393,6 +399,7 @@ int flexsae_set_option(const char* name, int64_t value) {
   const bool lanes_ok = value == 0 || value == 8 || value == 16 || value == 32;
   if (!strcmp(name, "lanes_fwd") && lanes_ok) { g_opt.lanes_fwd = (int)value; return 0; }
   if (!strcmp(name, "lanes_bwd") && lanes_ok) { g_opt.lanes_bwd = (int)value; return 0; }
+  if (!strcmp(name, "lanes_sharded") && lanes_ok) { g_opt.lanes_sharded = (int)value; return 0; }
   if (!strcmp(name, "l2_budget_mb") && value >= 1 && value <= 4096) { g_opt.l2_budget_mb = (int)value; return 0; }
   if (!strcmp(name, "segments") && value >= 0 && value <= 256) { g_opt.segments = (int)value; return 0; }
   if (!strcmp(name, "pipeline") && (value == 0 || value == 1)) { g_opt.pipeline = (int)value; return 0; }
@@ -419,6 +426,7 @@ int64_t flexsae_get_option(const char* name) {
   if (!name) return -1;
   if (!strcmp(name, "lanes_fwd")) return g_opt.lanes_fwd;
   if (!strcmp(name, "lanes_bwd")) return g_opt.lanes_bwd;
+  if (!strcmp(name, "lanes_sharded")) return g_opt.lanes_sharded;
   if (!strcmp(name, "l2_budget_mb")) return g_opt.l2_budget_mb;
   if (!strcmp(name, "segments")) return g_opt.segments;
   if (!strcmp(name, "pipeline")) return g_opt.pipeline;
@@ -458,6 +466,7 @@ size_t flexsae_fwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, in
 size_t flexsae_bwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, int64_t D, int weight_dtype, int dw_mode) {
   Shape s{B, K, F, D};
   if (check_shape(kind, s, weight_dtype)) return 0;
+  if (dw_mode == FLEXSAE_DW_ATOMIC_SHARDED) return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC, true).total;
   if (dw_mode != FLEXSAE_DW_ATOMIC && dw_mode != FLEXSAE_DW_DETERMINISTIC) {
     fail(FLEXSAE_EINVAL, "unknown dweight mode %d", dw_mode);
     return 0;
@@ -537,7 +546,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     return fail(FLEXSAE_EINVAL, "null pointer argument");
   if (!aligned16(weight) || !aligned16(state) || !aligned16(dweight) || !aligned16(workspace))
     return fail(FLEXSAE_EINVAL, "weight, state, dweight and workspace must be 16-byte aligned");
-  const BwdPlan p = plan_bwd(s, weight_dtype, dw_mode);
+  const BwdPlan p = plan_bwd(s, weight_dtype, dw_mode, peers != nullptr);
   if (workspace_bytes < p.total)
     return fail(FLEXSAE_EWORKSPACE, "backward workspace too small: %zu < %zu bytes", workspace_bytes, p.total);
   if (inv_norm <= 0.0) inv_norm = 1.0 / ((double)B * (double)D * (kind == FLEXSAE_HIER ? (double)K : 1.0));
@@ -685,7 +694,7 @@ int flexsae_shard_buffer_bytes(int64_t F, int64_t D, int weight_dtype, int world
   if (int rc = check_shape(FLEXSAE_HIER, s, weight_dtype)) return rc;
   if (world < 2 || world > kMaxRanks) return fail(FLEXSAE_EINVAL, "world size %d outside [2, %d]", world, kMaxRanks);
   if (!x_bytes || !y_bytes || !flag_bytes) return fail(FLEXSAE_EINVAL, "null pointer argument");
-  const BwdPlan p = plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC);
+  const BwdPlan p = plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC, true);
   const size_t rows_per_rank = (size_t)((F + world - 1) / world);
   *x_bytes = align_up(2 * (size_t)world * rows_per_rank * p.PW * dtype_size(weight_dtype), 256);  // inbox
   *y_bytes = *x_bytes;                                                                           // gather buffer
@@ -860,7 +869,7 @@ int flexsae_sort_by_decoder_row(const int64_t* indices, int64_t n, int64_t F, vo
 int flexsae_shard_slots(int64_t F, int64_t D, int weight_dtype) {
   Shape s{1, 1, F, D};
   if (check_shape(FLEXSAE_HIER, s, weight_dtype)) return 0;
-  return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC).pieces + kMaxSlabs + 1;  // an upper bound of the launch's slots for any lag
+  return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC, true).pieces + kMaxSlabs + 1;  // an upper bound of the launch's slots for any lag
 }
 
 // ---- forward for callers that cannot provide scratch memory ------------------------------------

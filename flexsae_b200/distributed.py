@@ -154,7 +154,8 @@ def peer_exchange(group, device: torch.device, F: int, D: int, dtype: torch.dtyp
     group must get here together, which they do when they run the same training step).  ``None``
     when symmetric memory cannot be set up on this machine (agreed on by all ranks)."""
     key = (id(group) if group is not None else 0, device.index, F, D, dtype,
-           nv.get_option("lanes_bwd"), nv.get_option("l2_budget_mb"), nv.get_option("slabs"), config.use_multicast,
+           nv.get_option("lanes_bwd"), nv.get_option("lanes_sharded"), nv.get_option("l2_budget_mb"), nv.get_option("slabs"),
+           config.use_multicast,
            config.symmetric_dweight)
     if key not in _exchanges:
         ex, problem = None, None

@@ -152,7 +152,7 @@ def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype
     mode = {"atomic": nv.DW_ATOMIC, "deterministic": nv.DW_DETERMINISTIC}[dweight_mode or config.dweight_mode]
     with torch.cuda.device(dev):
         go = grad_out.detach().to(device=dev, dtype=torch.float32).reshape(1).contiguous()
-        need = lib.flexsae_bwd_workspace_bytes(kind, B, K, F, D, wdt, mode)
+        need = lib.flexsae_bwd_workspace_bytes(kind, B, K, F, D, wdt, nv.DW_ATOMIC_SHARDED if peers is not None else mode)
         if need == 0:
             raise nv.FlexSaeNativeError("flexsae_loss_bwd: " + lib.flexsae_last_error().decode())
         ws = _workspace(dev, need)

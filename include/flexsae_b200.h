@@ -40,6 +40,7 @@ extern "C" {
 /* how dweight is accumulated */
 #define FLEXSAE_DW_ATOMIC 0        /* vectorised red.global.add.f32 into an L2-resident slab */
 #define FLEXSAE_DW_DETERMINISTIC 1 /* stable sort by decoder row + fixed-order segmented sums */
+#define FLEXSAE_DW_ATOMIC_SHARDED 2 /* only for flexsae_bwd_workspace_bytes: what flexsae_loss_bwd_sharded needs */
 
 /* error codes */
 #define FLEXSAE_EINVAL (-1)      /* bad shape, dtype code, null pointer or misaligned pointer */
@@ -58,8 +59,9 @@ int flexsae_version(void);
  * validates nothing and fails inside Triton. */
 const char* flexsae_last_error(void);
 
-/* Tuning knobs, process-wide: "lanes_fwd", "lanes_bwd" (8, 16, 32 lanes share one batch row;
- * 0 = choose so that one column slab of the decoder and of the fp32 gradient slab stay in L2),
+/* Tuning knobs, process-wide: "lanes_fwd", "lanes_bwd", "lanes_sharded" (8, 16, 32 lanes share one
+ * batch row; 0 = choose so that one column piece of the decoder and its fp32 gradient slabs stay in
+ * L2; the batch-sharded backward takes wider pieces, see "lanes_sharded"),
  * "l2_budget_mb" (working set one column piece may occupy), "segments"
  * (what flexsae_choose_segments answers; 0 = derive from the shape), "pipeline" (1: the atomic
  * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct",
