@@ -107,3 +107,25 @@ def test_persistent_gradient_table_is_not_overwritten_while_referenced():
     holder.grad = None
     again, _ = ex.take_dweight()
     assert again.data_ptr() == ex.dweight.data_ptr()
+
+
+def test_flag_sequence_restarts_before_a_c_int_would_overflow():
+    """The flag values of the in-kernel exchange count up from call to call and are passed as C ints:
+    long before INT32_MAX every rank restarts them collectively (zeroed flags, sequence 1)."""
+    from flexsae_b200.distributed import PeerExchange
+
+    ex = object.__new__(PeerExchange)          # no GPU, no symmetric memory: only the counting
+    ex.slots = 23
+    ex.seq = PeerExchange.SEQ_RESTART - 3 * ex.slots
+    restarts = []
+
+    def fake_restart():
+        restarts.append(ex.seq)
+        ex.seq = 1
+
+    ex._restart = fake_restart
+    seen = [ex.next_seq() for _ in range(6)]
+    assert len(restarts) == 1
+    assert all(1 <= s and s + ex.slots < 2 ** 31 for s in seen)
+    assert seen[seen.index(1):] == [1 + i * ex.slots for i in range(len(seen) - seen.index(1))]   # contiguous again after it
+    assert seen[:seen.index(1)] == sorted(seen[:seen.index(1)])
