@@ -43,7 +43,7 @@ from flexsae_b200.workloads import CONFIGS, algorithmic_bytes, make_inputs  # no
 FALLBACK_HBM_GBS = 6650.0   # earlier measurement on this pool, used only without MEASURED_PEAKS.json
 # dram__bytes_read + dram__bytes_write per launch of the dominant kernel at the headline workload,
 # from the ncu launch list summarised under profiles/
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {("c3_k128", "hier", "atomic"): 3416.0e6}
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {("c3_k128", "hier", "atomic"): 1239.0e6}
 
 
 # Exchange settings `bench.py` uses when it runs on several GPUs (each can be overridden through the

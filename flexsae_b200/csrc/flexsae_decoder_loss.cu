@@ -742,7 +742,9 @@ static cudaError_t launch_topk_select(const SelectArgs& a, int64_t B, cudaStream
   const size_t per_vec = sizeof(T) == 4 ? 4 : 2;
   const size_t vmax_bytes = (size_t)(a.F / (16 / (int)sizeof(T))) * per_vec;
   if (vmax_bytes <= 32 * 1024) {
-    topk_select_kernel<T, true><<<(unsigned)B, kSelThreads, vmax_bytes, st>>>(a);
+    auto kern = topk_select_kernel<T, true>;  // with its 17 KiB of static shared memory this can pass 48 KiB
+    if (cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024)) return e;
+    kern<<<(unsigned)B, kSelThreads, vmax_bytes, st>>>(a);
   } else {
     topk_select_kernel<T, false><<<(unsigned)B, kSelThreads, 0, st>>>(a);
   }

@@ -418,24 +418,12 @@ __global__ void __launch_bounds__(kSelThreads, FLEXSAE_SEL_MINB) topk_select_ker
   // their index).  Short lists: every thread counts how many entries beat its own -- no barriers;
   // long lists: a bitonic network.
   const unsigned long long* sorted = cand;
-  if (n_cand <= 2 * kSelThreads) {
+  if (n_cand <= kSelThreads) {  // (longer lists: the network below does fewer comparisons)
     constexpr int kOut = kSelCandidates / 2;  // the ranked entries go to the upper half of the list
-    unsigned long long mine[2];
-    int rank[2] = {0, 0};
-#pragma unroll
-    for (int c = 0; c < 2; c++) mine[c] = tid + c * kSelThreads < n_cand ? cand[tid + c * kSelThreads] : 0ull;
-    if (n_cand <= kSelThreads) {
-      for (int j = 0; j < n_cand; j++) rank[0] += cand[j] > mine[0];
-    } else {
-      for (int j = 0; j < n_cand; j++) {
-        const unsigned long long o = cand[j];
-        rank[0] += o > mine[0];
-        rank[1] += o > mine[1];
-      }
-    }
-#pragma unroll
-    for (int c = 0; c < 2; c++)
-      if (tid + c * kSelThreads < n_cand && rank[c] < a.K) cand[kOut + rank[c]] = mine[c];
+    const unsigned long long mine = tid < n_cand ? cand[tid] : 0ull;
+    int rank = 0;
+    for (int j = 0; j < n_cand; j++) rank += cand[j] > mine;
+    if (tid < n_cand && rank < a.K) cand[kOut + rank] = mine;
     __syncthreads();
     sorted = cand + kOut;
   } else {

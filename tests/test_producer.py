@@ -58,6 +58,8 @@ CASES = [  # B, F, K, dtype, kind of data
     (4, 1000, 33, torch.float32, "relu"), (4, 1024, 1024, torch.float16, "normal"), (3, 512, 100, torch.bfloat16, "ties"),
     (2, 131072, 64, torch.float32, "normal"), (1, 8, 1, torch.float16, "ties"), (6, 8192, 256, torch.float16, "relu"),
     (2, 8192, 16, torch.bfloat16, "const"), (2, 16384, 40, torch.float32, "ties"),      # candidate list overflows
+    (2, 32768, 128, torch.float32, "normal"), (2, 131072, 64, torch.float16, "normal"),   # the largest rows whose per-vector maxima are kept
+    (2, 262144, 32, torch.bfloat16, "normal"),                                            # longer: the row is read twice
     (3, 512, 12, torch.float32, "special"), (3, 1024, 20, torch.bfloat16, "special"), (2, 256, 9, torch.float16, "special"),
 ]
 
