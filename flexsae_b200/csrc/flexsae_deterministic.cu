@@ -39,30 +39,102 @@ __global__ void __launch_bounds__(256) sort_hist_kernel(const int64_t* __restric
   for (int d = threadIdx.x; d < radix; d += blockDim.x) counts[(size_t)d * ntiles + blockIdx.x] = hist[d];
 }
 
-// In-place exclusive scan of n ints by one CTA (n up to a few million: a handful of microseconds
-// next to the millisecond-scale passes it serves).
-__global__ void __launch_bounds__(1024) exclusive_scan_kernel(int* __restrict__ data, int n, int* __restrict__ total_out) {
-  __shared__ int part[1024];
-  const int per = (n + 1023) / 1024;
-  const int b = threadIdx.x * per;
-  const int e = min(n, b + per);
-  int s = 0;
-  for (int i = b; i < e; i++) s += data[i];
-  part[threadIdx.x] = s;
+// ---- in-place exclusive scan of n ints ----------------------------------------------------------
+// Blocks of 4096 ints: per-block sums, a scan of those sums by one CTA, then every block scans
+// itself and adds its offset.  (One CTA walking the whole array took 170 us for the 131072
+// digit counts of the headline shape, six times per backward.)
+static constexpr int kScanBlock = 4096;  // 1024 threads x int4
+
+// exclusive scan of up to 4096 ints held as one int4 per thread; returns the four outputs and the block total
+__device__ __forceinline__ int4 scan_block(int4 v, int* warp_sums, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int s = v.x + v.y + v.z + v.w;
+  int incl = s;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += up;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
   __syncthreads();
-  for (int off = 1; off < 1024; off <<= 1) {  // Hillis-Steele inclusive scan of the 1024 partials
-    int v = (threadIdx.x >= off) ? part[threadIdx.x - off] : 0;
-    __syncthreads();
-    part[threadIdx.x] += v;
-    __syncthreads();
+  if (warp == 0) {
+    int w = warp_sums[lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, w, d);
+      if (lane >= d) w += up;
+    }
+    warp_sums[lane] = w;  // inclusive totals of the warps
   }
-  int run = (threadIdx.x == 0) ? 0 : part[threadIdx.x - 1];
-  for (int i = b; i < e; i++) {
-    int v = data[i];
-    data[i] = run;
-    run += v;
+  __syncthreads();
+  const int before = (warp ? warp_sums[warp - 1] : 0) + incl - s;
+  *total = warp_sums[31];
+  __syncthreads();  // warp_sums may be reused at once
+  return make_int4(before, before + v.x, before + v.x + v.y, before + v.x + v.y + v.z);
+}
+
+__device__ __forceinline__ int4 load4(const int* data, int i, int n) {
+  if (i + 3 < n) return *reinterpret_cast<const int4*>(data + i);  // data is 16-byte aligned, i a multiple of 4
+  int4 v = make_int4(0, 0, 0, 0);
+  if (i < n) v.x = data[i];
+  if (i + 1 < n) v.y = data[i + 1];
+  if (i + 2 < n) v.z = data[i + 2];
+  return v;
+}
+
+__device__ __forceinline__ void store4(int* data, int i, int n, int4 v) {
+  if (i + 3 < n) {
+    *reinterpret_cast<int4*>(data + i) = v;
+  } else {
+    if (i < n) data[i] = v.x;
+    if (i + 1 < n) data[i + 1] = v.y;
+    if (i + 2 < n) data[i + 2] = v.z;
   }
-  if (threadIdx.x == 1023 && total_out) *total_out = part[1023];
+}
+
+__global__ void __launch_bounds__(1024) scan_block_sums_kernel(const int* __restrict__ data, int n, int* __restrict__ block_sums) {
+  __shared__ int warp_sums[32];
+  int total;
+  scan_block(load4(data, blockIdx.x * kScanBlock + threadIdx.x * 4, n), warp_sums, &total);
+  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+}
+
+// one CTA, any n: block after block with a running carry (used for the block sums, and for short arrays)
+__global__ void __launch_bounds__(1024) exclusive_scan_kernel(int* __restrict__ data, int n, int* __restrict__ total_out) {
+  __shared__ int warp_sums[32];
+  int carry = 0;
+  for (int base = 0; base < n; base += kScanBlock) {
+    const int i = base + threadIdx.x * 4;
+    int total;
+    int4 o = scan_block(load4(data, i, n), warp_sums, &total);
+    o.x += carry; o.y += carry; o.z += carry; o.w += carry;
+    store4(data, i, n, o);
+    carry += total;
+  }
+  if (threadIdx.x == 0 && total_out) *total_out = carry;
+}
+
+__global__ void __launch_bounds__(1024) scan_apply_kernel(int* __restrict__ data, int n, const int* __restrict__ block_offsets) {
+  __shared__ int warp_sums[32];
+  const int i = blockIdx.x * kScanBlock + threadIdx.x * 4;
+  const int off = block_offsets[blockIdx.x];
+  int total;
+  int4 o = scan_block(load4(data, i, n), warp_sums, &total);
+  o.x += off; o.y += off; o.z += off; o.w += off;
+  store4(data, i, n, o);
+}
+
+static void exclusive_scan(int* data, int n, int* total_out, int* block_sums, cudaStream_t st, int* launches) {
+  const int nb = (n + kScanBlock - 1) / kScanBlock;
+  if (nb <= 1) {
+    exclusive_scan_kernel<<<1, 1024, 0, st>>>(data, n, total_out);
+    *launches += 1;
+    return;
+  }
+  scan_block_sums_kernel<<<nb, 1024, 0, st>>>(data, n, block_sums);
+  exclusive_scan_kernel<<<1, 1024, 0, st>>>(block_sums, nb, total_out);
+  scan_apply_kernel<<<nb, 1024, 0, st>>>(data, n, block_sums);
+  *launches += 3;
 }
 
 // One warp per tile walks its keys in order, 32 at a time; equal digits inside a round are ranked
@@ -144,6 +216,9 @@ size_t det_index_bytes(int64_t n, int64_t F) {
   b += align256((size_t)n * 4);                                      // slot_of
   b += align256((size_t)(F + n / kItemSlots + 2) * 4);               // item_row
   b += 256;                                                          // totals
+  const size_t longest = (size_t)2048 * ((n + kSortTile - 1) / kSortTile) > (size_t)(F + 1)
+                             ? (size_t)2048 * ((n + kSortTile - 1) / kSortTile) : (size_t)(F + 1);
+  b += align256(((longest + kScanBlock - 1) / kScanBlock + 4) * 4);  // block sums of the scans
   return b;
 }
 
@@ -164,6 +239,8 @@ cudaError_t det_prepare(const int64_t* indices, int64_t n64, int64_t F64, char* 
   out->slot_of = (int*)take((size_t)n * 4);
   out->item_row = (int*)take((size_t)(F + n / kItemSlots + 2) * 4);
   int* totals = (int*)take(256);
+  const size_t longest = (size_t)2048 * ntiles > (size_t)(F + 1) ? (size_t)2048 * ntiles : (size_t)(F + 1);
+  int* block_sums = (int*)take(((longest + kScanBlock - 1) / kScanBlock + 4) * 4);
   out->max_items = F + n / kItemSlots + 1;
 
   int bits = 1;
@@ -180,7 +257,7 @@ cudaError_t det_prepare(const int64_t* indices, int64_t n64, int64_t F64, char* 
     } else {
       sort_hist_kernel<false><<<ntiles, 256, sh, st>>>(nullptr, keys[cur], n, F, shift, radix, ntiles, counts);
     }
-    exclusive_scan_kernel<<<1, 1024, 0, st>>>(counts, radix * ntiles, nullptr);
+    exclusive_scan(counts, radix * ntiles, nullptr, block_sums, st, launches);
     if (ps == 0) {
       sort_scatter_kernel<true><<<ntiles, 32, sh, st>>>(indices, nullptr, nullptr, keys[0], vals[0], n, F, shift, radix, ntiles, counts);
       cur = 0;
@@ -189,7 +266,7 @@ cudaError_t det_prepare(const int64_t* indices, int64_t n64, int64_t F64, char* 
                                                          radix, ntiles, counts);
       cur ^= 1;
     }
-    *launches += 3;
+    *launches += 2;
   }
   out->order = vals[cur];
   segment_bounds_kernel<<<(n + 1 + 255) / 256, 256, 0, st>>>(keys[cur], vals[cur], n, F, out->seg_begin, out->slot_of);
@@ -197,10 +274,10 @@ cudaError_t det_prepare(const int64_t* indices, int64_t n64, int64_t F64, char* 
   // scans over F + 1 entries (the extra last entry receives the total)
   cudaMemsetAsync(out->item_begin + F, 0, 4, st);
   cudaMemsetAsync(out->part_begin + F, 0, 4, st);
-  exclusive_scan_kernel<<<1, 1024, 0, st>>>(out->item_begin, F + 1, totals);
-  exclusive_scan_kernel<<<1, 1024, 0, st>>>(out->part_begin, F + 1, totals + 1);
+  exclusive_scan(out->item_begin, F + 1, totals, block_sums, st, launches);
+  exclusive_scan(out->part_begin, F + 1, totals + 1, block_sums, st, launches);
   item_rows_kernel<<<(F + 255) / 256, 256, 0, st>>>(out->item_begin, F, out->item_row);
-  *launches += 5;
+  *launches += 3;
   return cudaGetLastError();
 }
 

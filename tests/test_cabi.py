@@ -184,3 +184,23 @@ def test_sort_entry_rejects_bad_arguments_without_a_gpu():
     assert call(idx=None) == -1 and call(ws=None) == -1 and b"null" in lib.flexsae_last_error()
     assert call(ws=264) == -1 and b"aligned" in lib.flexsae_last_error()
     assert call(ws_bytes=need - 1) == -2 and b"too small" in lib.flexsae_last_error()
+
+
+def test_sharded_backward_plans_wider_pieces_than_the_single_gpu_backward():
+    """The batch-sharded backward has its own lane-width rule (and its own workspace size, asked for
+    with FLEXSAE_DW_ATOMIC_SHARDED); `lanes_sharded` overrides it."""
+    lib = nv.load()
+    for name in ("lanes_bwd", "lanes_sharded"):
+        nv.set_option(name, 0)
+    shape = (65536, 2304, nv.BF16)
+    assert lib.flexsae_shard_slots(*shape) == 18 + 5                      # 16 lanes: 18 pieces of 128 columns
+    single = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, *shape, nv.DW_ATOMIC)
+    sharded = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, *shape, nv.DW_ATOMIC_SHARDED)
+    assert single > 0 and sharded > 0 and single != sharded                # 8 lanes alone: 36 pieces, other slab sizes
+    nv.set_option("lanes_sharded", 8)
+    assert lib.flexsae_shard_slots(*shape) == 36 + 5
+    nv.set_option("lanes_sharded", 0)
+    nv.set_option("lanes_bwd", 32)                                         # a forced backward width applies to both
+    assert lib.flexsae_shard_slots(*shape) == 9 + 5
+    nv.set_option("lanes_bwd", 0)
+    assert lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, *shape, 7) == 0
