@@ -35,7 +35,7 @@ struct Options {
   int lanes_fwd = 0;      // 0 = auto
   int lanes_bwd = 0;      // 0 = auto
   int lanes_sharded = 0;  // batch-sharded backward; 0 = lanes_bwd if that is set, else auto with 1.5 x the L2 budget
-  int l2_budget_mb = 64;  // one piece of decoder columns (+ its fp32 slabs) must fit in this many MiB
+  int l2_budget_mb = 80;  // one piece of decoder columns (+ its fp32 slabs) must fit in this many MiB
   int segments = 0;       // K-segments per batch row in the backward; 0 = auto
   int pipeline = 1;       // 1: all column pieces of the atomic backward in one launch; 0: one launch per piece
   int convert_offset_pct = 60;  // where, inside a piece's unit blocks, the previous piece's converters sit
@@ -180,9 +180,12 @@ struct BwdPlan {
 };
 
 // `sharded`: the plan of flexsae_loss_bwd_sharded.  Its slots carry a cross-GPU hand-shake each, so
-// wider (fewer) pieces pay even when their slabs no longer quite fit: measured on two GPUs at the
-// headline shape, 16 lanes 1.69 ms per step against 1.78 with 8, while one GPU alone prefers 8
-// (1.56 against 1.59).  Hence half as much again of the L2 budget, and its own override.
+// wider (fewer) pieces pay even more than on one GPU: measured on two GPUs at the headline shape,
+// 16 lanes 1.69 ms per step against 1.78 with 8.  Hence half as much again of the L2 budget, and
+// its own override.  (On one GPU, 8 lanes are 1.7 % faster than 16 at the headline shape with its
+// uniform indices -- the slabs then stay in L2 -- but 50 % slower with Zipf indices, where every
+// column piece repeats the serialised reductions into the hot decoder rows: 5.77 against 3.8 ms at
+// config 4.  The default budget therefore admits 16 lanes.)
 static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode, bool sharded = false) {
   BwdPlan p;
   p.stage_bytes = p.part_bytes = 0;
