@@ -48,7 +48,7 @@ NCU_TRAFFIC_BYTES_PER_LAUNCH = {("c3_k128", "hier", "atomic"): 1239.0e6}
 
 # Exchange settings `bench.py` uses when it runs on several GPUs (each can be overridden through the
 # environment, see the module docstring); they are reported in the line's "exchange" object.
-SHARDED_DEFAULTS = {"symmetric_dweight": False, "fused_small_reduce": False, "options": {}}
+SHARDED_DEFAULTS = {"symmetric_dweight": True, "fused_small_reduce": True, "options": {}}
 
 
 def hbm_peak():

@@ -41,10 +41,10 @@ struct Options {
   int convert_offset_pct = 60;  // where, inside a piece's unit blocks, the previous piece's converters sit
   int exchange_blocks = 148;    // sharded backward: blocks per slot for the cross-GPU reduce / broadcast / copy
   int exchange_offset_pct = 0;  // ... and where inside a piece's unit blocks they sit (capped at convert_offset_pct)
-  int scatter_rotate = 0;       // sharded backward: ranks start their scatter sweeps at different row blocks
+  int scatter_rotate = -1;      // sharded backward: ranks start their scatter sweeps at different row blocks (-1: from 4 ranks up)
   int sharded_convert_blocks = 0;       // sharded backward: converting blocks per piece (0 = as on one GPU)
   int sharded_convert_offset_pct = -1;  // sharded backward: their place in the piece (-1 = convert_offset_pct)
-  int flag_fan_out = 0;         // sharded backward: a finished slot is announced by one thread per rank
+  int flag_fan_out = -1;        // sharded backward: a finished slot is announced by one thread per rank (-1: from 4 ranks up)
   int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
   int ticket_order = 0;         // single-launch kernels: blocks take their roles in the order they start (atomic ticket)
   int slabs = 2;                // fp32 accumulation slabs in rotation (2..4)
@@ -363,8 +363,9 @@ static cudaError_t launch_bwd_sharded(const BwdArgs& b, float* const* slabs, int
   sa.exch_blocks = g_opt.exchange_blocks;
   sa.exch_offset = (int)((long long)pa.unit_blocks * g_opt.exchange_offset_pct / 100);
   if (sa.exch_offset > pa.conv_offset) sa.exch_offset = pa.conv_offset;
-  sa.rotate = g_opt.scatter_rotate;
-  sa.fan_out = g_opt.flag_fan_out;
+  // measured: the rotated sweep and the parallel flag updates cost 3 % on two GPUs and gain 3 % on four
+  sa.rotate = g_opt.scatter_rotate >= 0 ? g_opt.scatter_rotate : (sa.world >= 4);
+  sa.fan_out = g_opt.flag_fan_out >= 0 ? g_opt.flag_fan_out : (sa.world >= 4);
   const long long blocks = (long long)pieces * (sa.exch_blocks + pa.unit_blocks + conv) +
                            (long long)(pa.conv_lag + 2) * (sa.exch_blocks + conv);
   if (blocks > 0x7fffffffll) return cudaErrorInvalidConfiguration;
@@ -417,8 +418,8 @@ int flexsae_set_option(const char* name, int64_t value) {
   if (!strcmp(name, "direct_f32") && (value == 0 || value == 1)) { g_opt.direct_f32 = (int)value; return 0; }
   if (!strcmp(name, "exchange_blocks") && value >= 1 && value <= 4096) { g_opt.exchange_blocks = (int)value; return 0; }
   if (!strcmp(name, "exchange_offset_pct") && value >= 0 && value <= 100) { g_opt.exchange_offset_pct = (int)value; return 0; }
-  if (!strcmp(name, "scatter_rotate") && (value == 0 || value == 1)) { g_opt.scatter_rotate = (int)value; return 0; }
-  if (!strcmp(name, "flag_fan_out") && (value == 0 || value == 1)) { g_opt.flag_fan_out = (int)value; return 0; }
+  if (!strcmp(name, "scatter_rotate") && value >= -1 && value <= 1) { g_opt.scatter_rotate = (int)value; return 0; }
+  if (!strcmp(name, "flag_fan_out") && value >= -1 && value <= 1) { g_opt.flag_fan_out = (int)value; return 0; }
   if (!strcmp(name, "sharded_convert_blocks") && value >= 0 && value <= 8192) { g_opt.sharded_convert_blocks = (int)value; return 0; }
   if (!strcmp(name, "sharded_convert_offset_pct") && value >= -1 && value <= 100) { g_opt.sharded_convert_offset_pct = (int)value; return 0; }
   if (!strcmp(name, "wait_limit_ms") && value >= 1 && value <= 600000) { g_opt.wait_limit_ms = (int)value; return 0; }

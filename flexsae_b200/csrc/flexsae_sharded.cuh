@@ -1,9 +1,6 @@
 // Batch-sharded backward: the single-launch pipeline with the cross-GPU sum of dweight done by its
 // own blocks over NVLink peer memory.
 #pragma once
-#ifdef FLEXSAE_VAR_OLDKERNEL
-#include FLEXSAE_VAR_OLDKERNEL
-#else
 
 #include "flexsae_backward.cuh"
 
@@ -498,4 +495,3 @@ __global__ void __launch_bounds__(kThreads, FLEXSAE_BWD_MINB) decoder_loss_bwd_s
 }
 
 }  // namespace flexsae
-#endif  // FLEXSAE_VAR_OLDKERNEL

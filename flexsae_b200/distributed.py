@@ -55,8 +55,8 @@ class config:
     symmetric_dweight: bool = False
     #: sum the scalar loss and dbias over the ranks with the library's own single-launch exchange
     #: over peer memory (``flexsae_small_allreduce``) instead of two NCCL all-reduces, whose latency
-    #: is a visible share of a 2 ms step
-    fused_small_reduce: bool = False
+    #: is a visible share of a 2 ms step (falls back to NCCL where symmetric memory is unavailable)
+    fused_small_reduce: bool = True
 
 
 class PeerExchange:

@@ -73,8 +73,10 @@ const char* flexsae_last_error(void);
  * waits for the piece's last accumulating blocks and nobody waits for the conversion),
  * "exchange_blocks" and "exchange_offset_pct" (sharded backward: how many blocks per column piece
  * do the cross-GPU exchange and how far into the piece's blocks they are placed), "scatter_rotate"
- * (1: each rank starts its scatter at a different owner's rows), "flag_fan_out" (1: a finished
- * slot is announced to all ranks by parallel stores), "sharded_convert_blocks" and
+ * (1: each rank starts its scatter sweeps at a different block of batch rows, so that the ranks do
+ * not push to the same owner at the same moment; 0: off; -1, the default: on from 4 ranks up -- it
+ * costs 3 % on two GPUs and gains 3 % on four), "flag_fan_out" (1: a finished slot is announced to
+ * all ranks by parallel stores; 0 and -1 as before), "sharded_convert_blocks" and
  * "sharded_convert_offset_pct" (sharded backward: number and placement of the converting blocks
  * when they differ from the single-GPU kernel's; 0 / -1 = the same), "wait_limit_ms" (how long any
  * one wait inside a kernel -- for other blocks of the launch, for another GPU -- may last before it
