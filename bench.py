@@ -143,6 +143,9 @@ def workload_config(w, kind, rows, global_rows, world, dweight_mode, **extra):
     cfg = {"workload": w.name, "kind": kind, "B_per_gpu": rows, "global_B": global_rows, "K": w.K, "F": w.F, "D": w.D,
            "storage": f"{w.weight_dtype} weight/bias/target, {w.vals_dtype} vals", "accumulate": "fp32",
            "dweight_mode": dweight_mode,
+           "piece_width": "by index skew (hottest decoder row's share of the batch, measured on the device every "
+                          "16th backward; uniform synthetic indices keep the L2-sized pieces)" if world == 1 else
+                          "fixed (the ranks of a sharded run must agree)",
            "parallelism": f"batch-sharded x{world}, decoder replicated" if world > 1 else "single GPU",
            "l2": "no flush: the decoder alone (302 MB at the headline shape) exceeds the 126 MB L2; the library's "
                  "own fp32 gradient slabs are meant to stay L2-resident between launches"}

@@ -18,7 +18,7 @@ from . import build as _build
 
 F32, BF16, F16 = 0, 1, 2
 TOPK, HIER = 0, 1
-DW_ATOMIC, DW_DETERMINISTIC, DW_ATOMIC_SHARDED = 0, 1, 2
+DW_ATOMIC, DW_DETERMINISTIC, DW_ATOMIC_SHARDED, DW_ATOMIC_WIDE = 0, 1, 2, 3
 STATUS_BAD_INDEX = 1
 STATUS_PIPELINE_TIMEOUT = 2
 
@@ -48,6 +48,8 @@ SIGNATURES = {
     "flexsae_small_allreduce": (_c_int, [_c_vp, _c_vp, _c_i64, _c_int, _c_int, _c_int, _c_int, _c_vp, _c_i64, _c_vp, _c_vp]),
     "flexsae_sort_workspace_bytes": (_c_sz, [_c_i64, _c_i64]),
     "flexsae_sort_by_decoder_row": (_c_int, [_c_vp, _c_i64, _c_i64, _c_vp, _c_sz, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp]),
+    "flexsae_index_skew_workspace_bytes": (_c_sz, [_c_i64]),
+    "flexsae_index_skew": (_c_int, [_c_vp, _c_i64, _c_i64, _c_i64, _c_vp, _c_sz, _c_vp, _c_vp]),
     "flexsae_loss_fwd_static_scratch": (_c_int, [_c_int] + [_c_vp] * 7 + [_c_int] + [_c_i64] * 4 + [_c_int] * 4
                                         + [_c_dbl, _c_vp, _c_vp]),
     "flexsae_loss_bwd": (_c_int, [_c_int] + [_c_vp] * 4 + [_c_int] + [_c_vp] * 5 + [_c_sz] + [_c_i64] * 4

@@ -52,12 +52,16 @@ def build(force: bool = False, verbose: bool = False, trace: bool = False) -> st
     extra = os.environ.get("FLEXSAE_NVCC_EXTRA", "--use_fast_math").split()   # e.g. "-DFLEXSAE_BWD_MINB=8" while tuning
     if trace:
         extra = extra + ["-DFLEXSAE_TRACE"]
-    cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-I", INCLUDE, "-o", out] + _sources()
+    tmp = f"{out}.{os.getpid()}.tmp"
+    cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-I", INCLUDE, "-o", tmp] + _sources()
     res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout)
     if res.returncode != 0:
+        if os.path.exists(tmp):
+            os.remove(tmp)
         raise RuntimeError("nvcc failed:\n" + res.stdout[-4000:])
+    os.replace(tmp, out)    # a reader (another rank, a running job) never sees a half-written library
     return out
 
 

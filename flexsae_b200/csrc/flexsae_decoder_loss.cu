@@ -75,6 +75,7 @@ static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 #include "flexsae_sharded.cuh"
 #include "flexsae_small_allreduce.cuh"
 #include "flexsae_topk_select.cuh"
+#include "flexsae_index_skew.cuh"
 
 namespace flexsae {
 
@@ -186,14 +187,14 @@ struct BwdPlan {
 // uniform indices -- the slabs then stay in L2 -- but 50 % slower with Zipf indices, where every
 // column piece repeats the serialised reductions into the hot decoder rows: 5.77 against 3.8 ms at
 // config 4.  The default budget therefore admits 16 lanes.)
-static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode, bool sharded = false) {
+static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode, bool sharded = false, bool wide = false) {
   BwdPlan p;
   p.stage_bytes = p.part_bytes = 0;
   const int vec = 16 / (int)dtype_size(wdt);
   // deterministic mode keeps no fp32 slab in L2 (its contributions stream through a staging buffer),
   // so only the decoder columns count, and wider pieces mean fewer launches and longer staged rows
   p.G = sharded ? choose_lanes(s.F, wdt, true, g_opt.lanes_sharded ? g_opt.lanes_sharded : g_opt.lanes_bwd, 1.5)
-                : choose_lanes(s.F, wdt, dw_mode == FLEXSAE_DW_ATOMIC, g_opt.lanes_bwd);
+                : choose_lanes(s.F, wdt, dw_mode == FLEXSAE_DW_ATOMIC, g_opt.lanes_bwd ? g_opt.lanes_bwd : (wide ? 32 : 0));
   p.PW = p.G * vec;
   p.pieces = (int)((s.D + p.PW - 1) / p.PW);
   p.rows_per_block = (int)((s.B + kMaxRowBlocks - 1) / kMaxRowBlocks);
@@ -471,6 +472,7 @@ size_t flexsae_bwd_workspace_bytes(int kind, int64_t B, int64_t K, int64_t F, in
   Shape s{B, K, F, D};
   if (check_shape(kind, s, weight_dtype)) return 0;
   if (dw_mode == FLEXSAE_DW_ATOMIC_SHARDED) return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC, true).total;
+  if (dw_mode == FLEXSAE_DW_ATOMIC_WIDE) return plan_bwd(s, weight_dtype, FLEXSAE_DW_ATOMIC, false, true).total;
   if (dw_mode != FLEXSAE_DW_ATOMIC && dw_mode != FLEXSAE_DW_DETERMINISTIC) {
     fail(FLEXSAE_EINVAL, "unknown dweight mode %d", dw_mode);
     return 0;
@@ -542,6 +544,8 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
   if (int rc = check_shape(kind, s, weight_dtype)) return rc;
   if (!dtype_ok(vals_dtype) || !dtype_ok(bias_dtype))
     return fail(FLEXSAE_EINVAL, "unknown dtype code (vals %d, bias %d)", vals_dtype, bias_dtype);
+  const bool wide = dw_mode == FLEXSAE_DW_ATOMIC_WIDE && !peers;
+  if (wide) dw_mode = FLEXSAE_DW_ATOMIC;
   if (dw_mode != FLEXSAE_DW_ATOMIC && dw_mode != FLEXSAE_DW_DETERMINISTIC)
     return fail(FLEXSAE_EINVAL, "unknown dweight mode %d", dw_mode);
   int KS, NS;
@@ -550,7 +554,7 @@ static int loss_bwd_impl(int kind, const int64_t* indices, const void* weight, c
     return fail(FLEXSAE_EINVAL, "null pointer argument");
   if (!aligned16(weight) || !aligned16(state) || !aligned16(dweight) || !aligned16(workspace))
     return fail(FLEXSAE_EINVAL, "weight, state, dweight and workspace must be 16-byte aligned");
-  const BwdPlan p = plan_bwd(s, weight_dtype, dw_mode, peers != nullptr);
+  const BwdPlan p = plan_bwd(s, weight_dtype, dw_mode, peers != nullptr, wide);
   if (workspace_bytes < p.total)
     return fail(FLEXSAE_EWORKSPACE, "backward workspace too small: %zu < %zu bytes", workspace_bytes, p.total);
   if (inv_norm <= 0.0) inv_norm = 1.0 / ((double)B * (double)D * (kind == FLEXSAE_HIER ? (double)K : 1.0));
@@ -869,6 +873,40 @@ int flexsae_sort_by_decoder_row(const int64_t* indices, int64_t n, int64_t F, vo
   if (e == cudaSuccess && seg_begin) e = cudaMemcpyAsync(seg_begin, ix.seg_begin, fb, cudaMemcpyDeviceToDevice, st);
   if (e == cudaSuccess && item_begin) e = cudaMemcpyAsync(item_begin, ix.item_begin, fb, cudaMemcpyDeviceToDevice, st);
   if (e != cudaSuccess) return fail((int)e, "sort launches failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+size_t flexsae_index_skew_workspace_bytes(int64_t F) {
+  if (F < 1 || F > (1ll << 30)) {
+    fail(FLEXSAE_EINVAL, "F = %lld decoder rows outside the supported range", (long long)F);
+    return 0;
+  }
+  return align_up((size_t)F * 4, 256);
+}
+
+int flexsae_index_skew(const int64_t* indices, int64_t B, int64_t K, int64_t F, void* workspace, size_t workspace_bytes,
+                       int32_t* result, void* stream) {
+  t_launches = 0;
+  if (B < 1 || K < 1 || F < 1 || F > (1ll << 30) || B > (1ll << 40) / K)
+    return fail(FLEXSAE_EINVAL, "B = %lld, K = %lld, F = %lld outside the supported range", (long long)B, (long long)K, (long long)F);
+  if (!indices || !workspace || !result) return fail(FLEXSAE_EINVAL, "null pointer argument");
+  const size_t need = align_up((size_t)F * 4, 256);
+  if (workspace_bytes < need) return fail(FLEXSAE_EWORKSPACE, "skew workspace too small: %zu < %zu bytes", workspace_bytes, need);
+  const long long n = (long long)B * K;
+  long long stride = n / kSkewSamples;
+  if (stride < 1) stride = 1;
+  stride |= 1;  // odd: with K a power of two the samples then visit every one of the K columns
+  const int samples = (int)((n + stride - 1) / stride < kSkewSamples ? (n + stride - 1) / stride : kSkewSamples);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, (size_t)F * 4, st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(result, 0, 8, st);
+  if (e == cudaSuccess) {
+    index_skew_kernel<<<(samples + kSkewThreads - 1) / kSkewThreads, kSkewThreads, 0, st>>>(
+        reinterpret_cast<const long long*>(indices), n, stride, samples, (int)F, reinterpret_cast<int*>(workspace), result);
+    ++t_launches;
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) return fail((int)e, "skew launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
 

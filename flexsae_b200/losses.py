@@ -31,11 +31,21 @@ launch_count = 0
 class config:
     """Process-wide switches of the fused losses."""
 
-    #: "atomic" (vectorised fp32 reductions resolved in L2) or "deterministic" (sorted,
-    #: fixed-order sums: bitwise reproducible dweight)
+    #: "atomic" (vectorised fp32 reductions resolved in L2; the piece width follows the index
+    #: distribution, see ``adaptive_pieces``), "atomic_wide" (the same with the widest column pieces
+    #: always) or "deterministic" (sorted, fixed-order sums: bitwise reproducible dweight)
     dweight_mode: str = "atomic"
     #: check the device status word after every forward (forces a host sync; for debugging)
     check_indices: bool = False
+    #: let the atomic backward follow the index distribution: every ``skew_interval``-th backward of
+    #: a decoder shape measures how much of the batch its hottest decoder row takes (one tiny launch,
+    #: read back without a synchronisation), and later backwards take the widest column pieces while
+    #: that share is above ``skew_threshold`` (Zipf-like activations: 20-50 % faster), the L2-sized
+    #: ones otherwise.  Single-GPU backward only: the ranks of a sharded run must agree on the piece
+    #: width, and each sees different indices.
+    adaptive_pieces: bool = True
+    skew_interval: int = 16
+    skew_threshold: float = 1.0 / 1024.0
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -111,6 +121,46 @@ def check_status(device=None) -> None:
             raise IndexError("flexsae_b200: indices outside [0, F) were passed to a fused loss")
 
 
+class _SkewWatch:
+    """Per (device, F): the share of sampled positions held by the hottest decoder row, measured
+    on the device every few backwards and read on the host only once the copy has arrived."""
+
+    def __init__(self, dev: torch.device, F: int, lib) -> None:
+        self.hist = torch.empty(lib.flexsae_index_skew_workspace_bytes(F), dtype=torch.uint8, device=dev)
+        self.result = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self.arrived: Optional[torch.cuda.Event] = None
+        self.calls = 0
+        self.share = 0.0
+
+    def wide(self, lib, indices: torch.Tensor, F: int, stream) -> bool:
+        """True when the next backward should take wide pieces; launches a measurement when due."""
+        global launch_count
+        if self.arrived is not None and self.arrived.query():
+            self.arrived = None
+            hottest, samples = int(self.host[0]), int(self.host[1])
+            self.share = hottest / samples if samples else 0.0
+        due = self.calls % max(1, config.skew_interval) == 0
+        self.calls += 1
+        if due and self.arrived is None:
+            B, K = indices.shape
+            nv.check(lib.flexsae_index_skew(_ptr(indices), B, K, F, _ptr(self.hist), self.hist.numel(),
+                                            _ptr(self.result), stream), "flexsae_index_skew")
+            launch_count += lib.flexsae_last_launch_count()
+            self.host.copy_(self.result, non_blocking=True)
+            self.arrived = torch.cuda.Event()
+            self.arrived.record()
+        return self.share > config.skew_threshold
+
+
+def _skew_watch(dev: torch.device, F: int, lib) -> _SkewWatch:
+    cache: Dict[tuple, _SkewWatch] = _tls.__dict__.setdefault("skew", {})
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), F)
+    if key not in cache:
+        cache[key] = _SkewWatch(dev, F, lib)
+    return cache[key]
+
+
 def fused_forward(kind: int, indices, weight, vals, bias, target, inv_norm: float = 0.0):
     """Runs the forward kernels; returns (loss 0-dim float32, (state, segments), prepared inputs)."""
     B, K, F, D = _validate(indices, weight, vals, bias, target)
@@ -149,8 +199,13 @@ def fused_backward(kind: int, indices, weight, vals, saved, grad_out, bias_dtype
     lib = nv.load()
     dev = weight.device
     wdt = nv.DTYPE_CODES[weight.dtype]
-    mode = {"atomic": nv.DW_ATOMIC, "deterministic": nv.DW_DETERMINISTIC}[dweight_mode or config.dweight_mode]
+    mode = {"atomic": nv.DW_ATOMIC, "atomic_wide": nv.DW_ATOMIC_WIDE,
+            "deterministic": nv.DW_DETERMINISTIC}[dweight_mode or config.dweight_mode]
     with torch.cuda.device(dev):
+        if (mode == nv.DW_ATOMIC and peers is None and config.adaptive_pieces
+                and not torch.cuda.is_current_stream_capturing()
+                and _skew_watch(dev, F, lib).wide(lib, indices, F, torch.cuda.current_stream(dev).cuda_stream)):
+            mode = nv.DW_ATOMIC_WIDE
         go = grad_out.detach().to(device=dev, dtype=torch.float32).reshape(1).contiguous()
         need = lib.flexsae_bwd_workspace_bytes(kind, B, K, F, D, wdt, nv.DW_ATOMIC_SHARDED if peers is not None else mode)
         if need == 0:

@@ -41,6 +41,8 @@ extern "C" {
 #define FLEXSAE_DW_ATOMIC 0        /* vectorised red.global.add.f32 into an L2-resident slab */
 #define FLEXSAE_DW_DETERMINISTIC 1 /* stable sort by decoder row + fixed-order segmented sums */
 #define FLEXSAE_DW_ATOMIC_SHARDED 2 /* only for flexsae_bwd_workspace_bytes: what flexsae_loss_bwd_sharded needs */
+#define FLEXSAE_DW_ATOMIC_WIDE 3    /* as FLEXSAE_DW_ATOMIC with the widest column pieces (32 lanes per batch row unless
+                                       "lanes_bwd" says otherwise): for heavily skewed indices, see flexsae_index_skew */
 
 /* error codes */
 #define FLEXSAE_EINVAL (-1)      /* bad shape, dtype code, null pointer or misaligned pointer */
@@ -136,7 +138,7 @@ int flexsae_loss_fwd(int kind, const int64_t* indices, const void* weight, const
  *   grad_out   one float32 ON THE DEVICE: the upstream gradient of the scalar loss
  *   dweight    [F,D] in weight_dtype, fully overwritten (untouched rows become 0)
  *   dvals      [B,K] in vals_dtype, dbias [D] in bias_dtype, fully overwritten
- *   dw_mode    FLEXSAE_DW_ATOMIC or FLEXSAE_DW_DETERMINISTIC
+ *   dw_mode    FLEXSAE_DW_ATOMIC, FLEXSAE_DW_ATOMIC_WIDE or FLEXSAE_DW_DETERMINISTIC
  * kind = FLEXSAE_HIER replaces _hierarchical_sae_backward + hierarchical_sae_backward_kernel and
  *   the dW.mul_(grad) passes (torch-ext/flex_sae/hierarchical_kernels.py:92-187,230-270,288-299);
  * kind = FLEXSAE_TOPK replaces embedding_bag_backward with its three kernels and the autograd
@@ -226,6 +228,21 @@ int flexsae_topk_select(const void* acts, int acts_dtype, int64_t B, int64_t F, 
 int flexsae_small_allreduce_bytes(int world, int64_t capacity, size_t* bytes);
 int flexsae_small_allreduce(const void* in, void* out, int64_t n, int dtype, int world, int rank, int seq,
                             void* const* buf_ptrs, int64_t capacity, int32_t* status, void* stream);
+
+/*
+ * How unevenly indices[B,K] use the decoder rows.  Takes up to 65536 positions at an odd stride,
+ * counts them per decoder row and writes result[0] = the largest count, result[1] = the number of
+ * positions taken (device int32[2]).  One launch and two memsets, asynchronous on `stream`; the
+ * workspace holds F int32.  When one decoder row takes more than about 1/1024 of the positions
+ * (config 4's Zipf indices: 1/64, its hottest rows being named by every batch row; uniform indices
+ * at F=65536: 1/10000), FLEXSAE_DW_ATOMIC_WIDE is the faster backward (measured 2.99 against
+ * 3.85 ms at config 4), otherwise FLEXSAE_DW_ATOMIC
+ * (1.575 against 1.65 ms at config 3).  The reference has no counterpart: its tile sizes are
+ * literals (torch-ext/flex_sae/hierarchical_kernels.py:263-267).
+ */
+size_t flexsae_index_skew_workspace_bytes(int64_t F);
+int flexsae_index_skew(const int64_t* indices, int64_t B, int64_t K, int64_t F, void* workspace,
+                       size_t workspace_bytes, int32_t* result, void* stream);
 
 /*
  * The integer part of the deterministic dweight mode on its own: the n = B*K positions (b*K + k) of

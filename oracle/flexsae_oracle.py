@@ -128,3 +128,20 @@ def topk_select(acts, k: int, relu: bool = True):
     if relu:
         vals = np.maximum(vals, 0.0)
     return order.astype(np.int64), vals
+
+
+def index_skew(indices, F: int, max_samples: int = 65536):
+    """The statistic ``flexsae_index_skew`` computes: up to ``max_samples`` positions of the
+    flattened ``indices[B,K]`` at an odd stride, counted per decoder row (entries outside [0, F) are
+    left out); returns (largest count, positions taken).  The reference has no counterpart (its
+    tile sizes are literals, torch-ext/flex_sae/hierarchical_kernels.py:263-267); this restates the
+    library's own definition for the tests."""
+    flat = np.asarray(indices).reshape(-1)
+    n = flat.size
+    stride = max(1, n // max_samples) | 1
+    samples = min((n + stride - 1) // stride, max_samples)
+    taken = flat[np.arange(samples, dtype=np.int64) * stride]
+    taken = taken[(taken >= 0) & (taken < F)]
+    hottest = int(np.bincount(taken, minlength=1).max()) if taken.size else 0
+    return hottest, samples
+

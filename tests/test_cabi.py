@@ -186,6 +186,34 @@ def test_sort_entry_rejects_bad_arguments_without_a_gpu():
     assert call(ws_bytes=need - 1) == -2 and b"too small" in lib.flexsae_last_error()
 
 
+def test_index_skew_entry_and_wide_mode_without_a_gpu():
+    """Argument checks of flexsae_index_skew, and the workspace of the wide-piece backward: 32 lanes
+    (two 67 MB slabs at the headline shape) unless `lanes_bwd` fixes the width."""
+    lib = nv.load()
+    assert lib.flexsae_index_skew_workspace_bytes(65536) >= 65536 * 4
+    assert lib.flexsae_index_skew_workspace_bytes(0) == 0
+
+    def call(idx=64, B=8, K=4, F=64, ws=256, ws_bytes=256, res=512):
+        return lib.flexsae_index_skew(idx, B, K, F, ws, ws_bytes, res, None)
+
+    assert call(B=0) == -1 and call(K=0) == -1 and call(F=0) == -1
+    assert call(idx=None) == -1 and call(ws=None) == -1 and call(res=None) == -1
+    assert call(ws_bytes=255) == -2 and b"too small" in lib.flexsae_last_error()
+
+    nv.set_option("lanes_bwd", 0)
+    shape = (nv.HIER, 4096, 128, 65536, 2304, nv.BF16)
+    normal = lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC)
+    wide = lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC_WIDE)
+    # two slabs of 256 instead of 128 columns (+67 MB), nine instead of 18 pieces of dvals partials (-19 MB)
+    assert abs((wide - normal) - (2 * 65536 * 128 * 4 - 9 * 4096 * 128 * 4)) < 4096     # counters, alignment
+    nv.set_option("lanes_bwd", 8)
+    try:
+        assert lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC_WIDE) == lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC)
+    finally:
+        nv.set_option("lanes_bwd", 0)
+    assert lib.flexsae_bwd_workspace_bytes(*shape, 7) == 0
+
+
 def test_sharded_backward_plans_wider_pieces_than_the_single_gpu_backward():
     """The batch-sharded backward has its own lane-width rule (and its own workspace size, asked for
     with FLEXSAE_DW_ATOMIC_SHARDED); `lanes_sharded` overrides it."""

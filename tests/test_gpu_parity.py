@@ -411,6 +411,69 @@ def test_sort_tables_match_stable_argsort(w):
     assert np.array_equal(item_begin.cpu().numpy(), np.concatenate([[0], np.cumsum(items)]))
 
 
+def _index_skew_on_gpu(idx, F):
+    lib = nv.load()
+    B, K = idx.shape
+    ws = torch.empty(lib.flexsae_index_skew_workspace_bytes(F), dtype=torch.uint8, device="cuda")
+    res = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    rc = lib.flexsae_index_skew(idx.data_ptr(), B, K, F, ws.data_ptr(), ws.numel(), res.data_ptr(),
+                                torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.flexsae_last_error()
+    return tuple(int(v) for v in res.cpu())
+
+
+@pytest.mark.parametrize("w", [CONFIGS["c1"], CONFIGS["c3_k128"], CONFIGS["c4"], CONFIGS["c3_k32"].replace(B=3, K=5, F=11),
+                               CONFIGS["c5"].replace(B=4096)], ids=lambda w: f"{w.name}_{w.B}")
+def test_index_skew_matches_oracle(w):
+    """The hottest decoder row's count over the sampled positions, bit for bit against numpy; out-of-
+    range entries are left out; config 4's Zipf indices are far above the wide-piece threshold,
+    uniform ones far below."""
+    idx = make_inputs(w, "cuda", with_weight=False)["indices"].contiguous()
+    if idx.numel() > 8:
+        idx.view(-1)[0], idx.view(-1)[-1] = w.F, -1
+    got = _index_skew_on_gpu(idx, w.F)
+    assert got == orc.index_skew(idx.cpu().numpy(), w.F)
+    share = got[0] / got[1]
+    if w.name == "c4":
+        assert share > 4 * fx.config.skew_threshold
+    if w.name == "c3_k128":
+        assert share < fx.config.skew_threshold / 16
+
+
+def test_piece_width_follows_the_index_skew():
+    """Zipf indices: the first backward measures, the following ones take the wide pieces; uniform
+    indices on the same decoder shape turn them off again; results agree with the fixed widths."""
+    from flexsae_b200 import losses
+
+    w = CONFIGS["c4"].replace(B=2048)
+    watch_key = (torch.cuda.current_device(), w.F)
+    losses._tls.__dict__.get("skew", {}).pop(watch_key, None)
+    x = make_inputs(w, "cuda")
+    interval = fx.config.skew_interval
+    fx.config.skew_interval = 1
+    try:
+        first = run_fused("hier", x)
+        torch.cuda.synchronize()
+        second = run_fused("hier", x)                   # reads the first measurement
+        watch = losses._tls.__dict__["skew"][watch_key]
+        assert watch.share > fx.config.skew_threshold
+        fx.config.dweight_mode = "atomic_wide"
+        wide = run_fused("hier", x)
+        fx.config.dweight_mode = "atomic"
+        for k in ("dweight", "dvals", "dbias"):
+            assert rel_err(second[k], first[k]) < 6e-3, k
+            assert rel_err(second[k], wide[k]) < 6e-3, k
+        assert np.array_equal(second["dvals"], wide["dvals"]) or rel_err(second["dvals"], wide["dvals"]) < 1e-6
+        u = make_inputs(w.replace(indices="distinct"), "cuda")
+        run_fused("hier", u)
+        torch.cuda.synchronize()
+        run_fused("hier", u)
+        assert watch.share < fx.config.skew_threshold
+    finally:
+        fx.config.skew_interval = interval
+        fx.config.dweight_mode = "atomic"
+
+
 def test_atomic_and_deterministic_modes_agree():
     w = CONFIGS["c3_k32"].replace(B=1024, F=16384)
     x = make_inputs(w, "cuda")
