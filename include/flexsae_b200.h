@@ -233,11 +233,12 @@ int flexsae_small_allreduce(const void* in, void* out, int64_t n, int dtype, int
  * How unevenly indices[B,K] use the decoder rows.  Takes up to 65536 positions at an odd stride,
  * counts them per decoder row and writes result[0] = the largest count, result[1] = the number of
  * positions taken (device int32[2]).  One launch and two memsets, asynchronous on `stream`; the
- * workspace holds F int32.  When one decoder row takes more than about 1/1024 of the positions
- * (config 4's Zipf indices: 1/64, its hottest rows being named by every batch row; uniform indices
- * at F=65536: 1/10000), FLEXSAE_DW_ATOMIC_WIDE is the faster backward (measured 2.99 against
- * 3.85 ms at config 4), otherwise FLEXSAE_DW_ATOMIC
- * (1.575 against 1.65 ms at config 3).  The reference has no counterpart: its tile sizes are
+ * workspace holds F int32.  When one decoder row takes more than about 1/144 of the positions
+ * FLEXSAE_DW_ATOMIC_WIDE is the faster backward, otherwise FLEXSAE_DW_ATOMIC.  Measured at F=65536,
+ * D=2304, bf16 (ms per fwd+bwd, L2-sized / wide pieces): uniform indices, share 1/8000: 1.55 / 1.78
+ * (B=4096, K=128) and 2.45 / 2.78 (B=16384, K=64); Zipf 0.6, share 1/240: 2.49 / 2.68; Zipf 0.8,
+ * share 1/81: 3.30 / 2.92; Zipf 1.1 (config 4), share 1/65, its hottest rows being named by every
+ * batch row: 3.71 / 2.98.  The reference has no counterpart: its tile sizes are
  * literals (torch-ext/flex_sae/hierarchical_kernels.py:263-267).
  */
 size_t flexsae_index_skew_workspace_bytes(int64_t F);

@@ -435,9 +435,9 @@ def test_index_skew_matches_oracle(w):
     assert got == orc.index_skew(idx.cpu().numpy(), w.F)
     share = got[0] / got[1]
     if w.name == "c4":
-        assert share > 4 * fx.config.skew_threshold
+        assert share > 2 * fx.config.skew_threshold
     if w.name == "c3_k128":
-        assert share < fx.config.skew_threshold / 16
+        assert share < fx.config.skew_threshold / 16         # about 8 of 65536 samples
 
 
 def test_piece_width_follows_the_index_skew():
@@ -447,7 +447,7 @@ def test_piece_width_follows_the_index_skew():
 
     w = CONFIGS["c4"].replace(B=2048)
     watch_key = (torch.cuda.current_device(), w.F)
-    losses._tls.__dict__.get("skew", {}).pop(watch_key, None)
+    losses._skew_watches.pop(watch_key, None)
     x = make_inputs(w, "cuda")
     interval = fx.config.skew_interval
     fx.config.skew_interval = 1
@@ -455,7 +455,7 @@ def test_piece_width_follows_the_index_skew():
         first = run_fused("hier", x)
         torch.cuda.synchronize()
         second = run_fused("hier", x)                   # reads the first measurement
-        watch = losses._tls.__dict__["skew"][watch_key]
+        watch = losses._skew_watches[watch_key]
         assert watch.share > fx.config.skew_threshold
         fx.config.dweight_mode = "atomic_wide"
         wide = run_fused("hier", x)
