@@ -121,6 +121,14 @@ static int choose_lanes(int64_t F, int wdt, bool with_slab, int forced, double b
   return bytes(8) <= 2.0 * budget ? 8 : 32;
 }
 
+// Share of the L2 budget the single-GPU atomic backward may use.  The dense cost of a column piece
+// (clearing and converting its fp32 slab, and the slab lines that spill to HBM once two slabs exceed
+// about half the L2) does not depend on the batch; the cost per contribution falls with wider
+// pieces.  Measured at F=65536, D=2304, bf16, uniform indices, 8 / 16 lanes in ms per fwd+bwd:
+// B*K/F = 2: 0.75 / 0.87; 4: 1.02 / 1.15; 8: 1.54 / 1.56; 16: 2.70 / 2.47; 32: 4.78 / 4.34.  So up
+// to 8 contributions per decoder row the slabs have to fit 4/5 of the budget (64 of 80 MiB).
+static double bwd_budget_scale(const Shape& s) { return (double)s.B * (double)s.K > 8.0 * (double)s.F ? 1.0 : 0.8; }
+
 static int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
 // segment length for a requested number of K-segments, and the count that length gives
@@ -135,7 +143,7 @@ static void segment_layout(int K, int want, int* KS, int* NS) {
 static int choose_segments(const Shape& s, int wdt) {
   int want = g_opt.segments;
   if (want <= 0) {
-    const int G = choose_lanes(s.F, wdt, true, g_opt.lanes_bwd);
+    const int G = choose_lanes(s.F, wdt, true, g_opt.lanes_bwd, bwd_budget_scale(s));
     const double warps = (double)s.B * G / 32.0;
     const double target = 148.0 * 32.0;
     want = (int)((target + warps - 1) / warps);
@@ -183,10 +191,9 @@ struct BwdPlan {
 // `sharded`: the plan of flexsae_loss_bwd_sharded.  Its slots carry a cross-GPU hand-shake each, so
 // wider (fewer) pieces pay even more than on one GPU: measured on two GPUs at the headline shape,
 // 16 lanes 1.69 ms per step against 1.78 with 8.  Hence half as much again of the L2 budget, and
-// its own override.  (On one GPU, 8 lanes are 1.7 % faster than 16 at the headline shape with its
-// uniform indices -- the slabs then stay in L2 -- but 50 % slower with Zipf indices, where every
-// column piece repeats the serialised reductions into the hot decoder rows: 5.77 against 3.8 ms at
-// config 4.  The default budget therefore admits 16 lanes.)
+// its own override.  `wide`: 32 lanes whatever fits (FLEXSAE_DW_ATOMIC_WIDE, for skewed indices: with
+// Zipf indices every column piece repeats the serialised reductions into the hot decoder rows, 5.8 ms
+// with 8 lanes against 3.7 with 16 and 3.0 with 32 at config 4).
 static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode, bool sharded = false, bool wide = false) {
   BwdPlan p;
   p.stage_bytes = p.part_bytes = 0;
@@ -194,7 +201,8 @@ static BwdPlan plan_bwd(const Shape& s, int wdt, int dw_mode, bool sharded = fal
   // deterministic mode keeps no fp32 slab in L2 (its contributions stream through a staging buffer),
   // so only the decoder columns count, and wider pieces mean fewer launches and longer staged rows
   p.G = sharded ? choose_lanes(s.F, wdt, true, g_opt.lanes_sharded ? g_opt.lanes_sharded : g_opt.lanes_bwd, 1.5)
-                : choose_lanes(s.F, wdt, dw_mode == FLEXSAE_DW_ATOMIC, g_opt.lanes_bwd ? g_opt.lanes_bwd : (wide ? 32 : 0));
+                : choose_lanes(s.F, wdt, dw_mode == FLEXSAE_DW_ATOMIC, g_opt.lanes_bwd ? g_opt.lanes_bwd : (wide ? 32 : 0),
+                               dw_mode == FLEXSAE_DW_ATOMIC ? bwd_budget_scale(s) : 1.0);
   p.PW = p.G * vec;
   p.pieces = (int)((s.D + p.PW - 1) / p.PW);
   p.rows_per_block = (int)((s.B + kMaxRowBlocks - 1) / kMaxRowBlocks);

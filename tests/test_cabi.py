@@ -201,11 +201,11 @@ def test_index_skew_entry_and_wide_mode_without_a_gpu():
     assert call(ws_bytes=255) == -2 and b"too small" in lib.flexsae_last_error()
 
     nv.set_option("lanes_bwd", 0)
-    shape = (nv.HIER, 4096, 128, 65536, 2304, nv.BF16)
-    normal = lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC)
+    shape = (nv.HIER, 8192, 128, 65536, 2304, nv.BF16)
+    normal = lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC)            # 16 lanes at this batch size
     wide = lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC_WIDE)
-    # two slabs of 256 instead of 128 columns (+67 MB), nine instead of 18 pieces of dvals partials (-19 MB)
-    assert abs((wide - normal) - (2 * 65536 * 128 * 4 - 9 * 4096 * 128 * 4)) < 4096     # counters, alignment
+    # two slabs of 256 instead of 128 columns (+67 MB), nine instead of 18 pieces of dvals partials (-38 MB)
+    assert abs((wide - normal) - (2 * 65536 * 128 * 4 - 9 * 8192 * 128 * 4)) < 4096     # counters, alignment
     nv.set_option("lanes_bwd", 8)
     try:
         assert lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC_WIDE) == lib.flexsae_bwd_workspace_bytes(*shape, nv.DW_ATOMIC)
@@ -224,7 +224,18 @@ def test_sharded_backward_plans_wider_pieces_than_the_single_gpu_backward():
     assert lib.flexsae_shard_slots(*shape) == 18 + 5                      # 16 lanes: 18 pieces of 128 columns
     single = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, *shape, nv.DW_ATOMIC)
     sharded = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, *shape, nv.DW_ATOMIC_SHARDED)
-    assert single > 0 and sharded == single                                # both 16 lanes at this shape
+    nv.set_option("lanes_bwd", 16)
+    forced16 = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, *shape, nv.DW_ATOMIC)
+    nv.set_option("lanes_bwd", 8)
+    forced8 = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4096, 128, *shape, nv.DW_ATOMIC)
+    nv.set_option("lanes_bwd", 0)
+    # one GPU, 8 contributions per decoder row (B*K = 8*F): 8 lanes, whose slabs stay in L2; sharded: 16
+    assert single == forced8 and sharded == forced16 and forced16 != forced8 and min(forced8, forced16) > 0
+    # above 8 contributions per decoder row the single-GPU backward takes 16 lanes as well
+    nv.set_option("lanes_bwd", 16)
+    dense16 = lib.flexsae_bwd_workspace_bytes(nv.HIER, 4097, 128, *shape, nv.DW_ATOMIC)
+    nv.set_option("lanes_bwd", 0)
+    assert lib.flexsae_bwd_workspace_bytes(nv.HIER, 4097, 128, *shape, nv.DW_ATOMIC) == dense16
     nv.set_option("lanes_sharded", 8)
     assert lib.flexsae_shard_slots(*shape) == 36 + 5
     nv.set_option("lanes_sharded", 0)
