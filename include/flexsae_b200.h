@@ -64,7 +64,8 @@ const char* flexsae_last_error(void);
 /* Tuning knobs, process-wide: "lanes_fwd", "lanes_bwd", "lanes_sharded" (8, 16, 32 lanes share one
  * batch row; 0 = choose so that one column piece of the decoder and its fp32 gradient slabs stay in
  * L2; the batch-sharded backward takes wider pieces, see "lanes_sharded"),
- * "l2_budget_mb" (working set one column piece may occupy), "segments"
+ * "l2_budget_mb" (working set one column piece may occupy; the single-GPU atomic backward uses 4/5 of
+ * it while a decoder row receives at most 8 contributions on average, B*K <= 8*F), "segments"
  * (what flexsae_choose_segments answers; 0 = derive from the shape), "pipeline" (1: the atomic
  * backward runs all column pieces in one launch; 0: one launch per piece), "convert_offset_pct",
  * "direct_f32" (1: with an fp32 decoder the reductions go straight into dweight),
