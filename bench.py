@@ -357,14 +357,14 @@ def main():
         scale = float(ref_dw.abs().max())
         errs = torch.tensor([abs(got_loss - ref_loss) / abs(ref_loss), float((got_dw - ref_dw).abs().max()) / scale,
                              float((got_db - ref_db).abs().max()) / float(ref_db.abs().max()),
-                             0.0 if torch.equal(got_dv, ref_dv) else 1.0], device=dev, dtype=torch.float64)
+                             float((got_dv - ref_dv).abs().max()) / float(ref_dv.abs().max())], device=dev, dtype=torch.float64)
         dist.all_reduce(errs, op=dist.ReduceOp.MAX)
         parity = {"against": "per-rank kernels + NCCL all-reduce of dweight, dbias and loss, same inputs",
                   "loss_rel": float(errs[0]), "dweight_rel_of_max": float(errs[1]), "dbias_rel_of_max": float(errs[2]),
-                  "dvals_bit_equal": float(errs[3]) == 0.0}
+                  "dvals_rel_of_max": float(errs[3])}      # per-piece dot products: the two paths cut D into different pieces
         del ref_dw, got_dw
         ok = kernels_ok() and parity["loss_rel"] < 1e-5 and parity["dweight_rel_of_max"] < 1e-2 and \
-            parity["dbias_rel_of_max"] < 1e-2 and parity["dvals_bit_equal"]
+            parity["dbias_rel_of_max"] < 1e-2 and parity["dvals_rel_of_max"] < (1e-4 if w.vals_dtype == "float32" else 1e-2)
         if not ok:
             raise SystemExit(f"bench.py: the fused cross-GPU gradient sum disagrees with the NCCL all-reduce: {parity}; "
                              "no number is reported")
