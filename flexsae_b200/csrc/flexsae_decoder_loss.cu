@@ -43,7 +43,8 @@ struct Options {
   int exchange_offset_pct = 0;  // ... and where inside a piece's unit blocks they sit (capped at convert_offset_pct)
   int scatter_rotate = -1;      // sharded backward: ranks start their scatter sweeps at different row blocks (-1: from 4 ranks up)
   int sharded_convert_blocks = 0;       // sharded backward: converting blocks per piece (0 = as on one GPU)
-  int sharded_convert_offset_pct = -1;  // sharded backward: their place in the piece (-1 = convert_offset_pct)
+  int sharded_convert_offset_pct = 45;  // sharded backward: their place in the piece (-1 = convert_offset_pct); their work
+                                        // includes the NVLink stores, so they start earlier: 1.3 % per step at 2 and 4 GPUs
   int flag_fan_out = -1;        // sharded backward: a finished slot is announced by one thread per rank (-1: from 4 ranks up)
   int direct_f32 = 1;           // fp32 decoder: reduce straight into dweight instead of slab + copy
   int ticket_order = 0;         // single-launch kernels: blocks take their roles in the order they start (atomic ticket)

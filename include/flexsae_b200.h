@@ -81,7 +81,7 @@ const char* flexsae_last_error(void);
  * costs 3 % on two GPUs and gains 3 % on four), "flag_fan_out" (1: a finished slot is announced to
  * all ranks by parallel stores; 0 and -1 as before), "sharded_convert_blocks" and
  * "sharded_convert_offset_pct" (sharded backward: number and placement of the converting blocks
- * when they differ from the single-GPU kernel's; 0 / -1 = the same), "wait_limit_ms" (how long any
+ * when they differ from the single-GPU kernel's; 0 / -1 = the same; the placement defaults to 45), "wait_limit_ms" (how long any
  * one wait inside a kernel -- for other blocks of the launch, for another GPU -- may last before it
  * gives up and sets FLEXSAE_STATUS_PIPELINE_TIMEOUT; 5000 by default, measured on the GPU's own
  * nanosecond timer; a rank of a sharded run that enqueues its backward later than that after the
