@@ -26,6 +26,7 @@ FLEXSAE_SYMMETRIC_DWEIGHT, FLEXSAE_FUSED_SMALL_REDUCE (0/1: flexsae_b200.distrib
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -322,10 +323,15 @@ def main():
         """n steps between two events; returns (ms per step, per-step (fwd, bwd, whole) ms lists), max over ranks."""
         marks = []
         start, stop = ev(), ev()
-        start.record()
-        for _ in range(n):
-            step(fn, marks)
-        stop.record()
+        gc.collect()
+        gc.disable()          # a collection pause on the host can let the launch queue run dry for a step
+        try:
+            start.record()
+            for _ in range(n):
+                step(fn, marks)
+            stop.record()
+        finally:
+            gc.enable()
         barrier()
         total = start.elapsed_time(stop)
         fwd = [a.elapsed_time(b) for a, b, _ in marks]
