@@ -33,8 +33,9 @@ def test_fake_implementations_give_the_real_shapes(kind, shape):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("backend", ["aot_eager", "inductor"])     # the reference's example compiles with the default backend (example.py:15)
 @pytest.mark.parametrize("kind", ["topk", "hier"])
-def test_fullgraph_compile_matches_eager(kind):
+def test_fullgraph_compile_matches_eager(kind, backend):
     w = Workload("cmp", B=96, K=32, F=1024, D=768, weight_dtype="bfloat16", indices="distinct", sort_vals=True,
                  normalise_weight=True, seed=61)
     x = make_inputs(w, "cuda")
@@ -44,12 +45,15 @@ def test_fullgraph_compile_matches_eager(kind):
         return fn(i, wt, v, b, t) * 3.0
 
     outs = []
-    for f in (step, torch.compile(step, fullgraph=True, backend="aot_eager")):
+    for f in (step, torch.compile(step, fullgraph=True, backend=backend)):
         wt = x["weight"].clone().requires_grad_(True)
         v = x["vals"].clone().requires_grad_(True)
         b = x["bias"].clone().requires_grad_(True)
-        loss = f(x["indices"], wt, v, b, x["target"])
-        loss.backward()
+        try:
+            loss = f(x["indices"], wt, v, b, x["target"])
+            loss.backward()
+        except torch._inductor.exc.InductorError as e:        # no working Triton / C++ toolchain for inductor's own code
+            pytest.skip(f"inductor cannot generate code on this machine: {str(e)[:200]}")
         outs.append((loss.detach(), wt.grad, v.grad, b.grad))
     (l0, w0, v0, b0), (l1, w1, v1, b1) = outs
     assert torch.equal(l0, l1) and torch.equal(v0, v1) and torch.equal(b0, b1)   # fixed-order sums
