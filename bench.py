@@ -61,42 +61,50 @@ def hbm_peak():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML (read-only) while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs.
+
+    One sampler per job: rank 0 reads all the GPUs of the run.  (A sampler in every rank -- eight
+    threads querying NVML every 4 ms next to eight launch loops -- delayed the ranks' launches against
+    each other: at 8 GPUs the forward, which ends in a cross-rank sum, measured 0.85 instead of 0.33 ms.)"""
 
     REASONS = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
                0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
                0x100: "display_clock_setting"}
 
-    def __init__(self, index: int, period_s: float = 0.004):
+    def __init__(self, indices, period_s: float = 0.004):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
         self.period = period_s
+        self.handles = []
         try:
             import pynvml
             pynvml.nvmlInit()
             self.nvml = pynvml
             visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
-            self.h = pynvml.nvmlDeviceGetHandleByIndex(phys)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            for index in indices:
+                phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+                self.handles.append(pynvml.nvmlDeviceGetHandleByIndex(phys))
+            if self.handles:
+                self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handles[0], pynvml.NVML_CLOCK_SM)
         except Exception:
             self.nvml = None
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                self.samples.append(self.nvml.nvmlDeviceGetClockInfo(self.h, self.nvml.NVML_CLOCK_SM))
-                bits = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(self.h)
-                for b, name in self.REASONS.items():
-                    if bits & b:
-                        self.reasons.add(name)
+                for h in self.handles:
+                    self.samples.append(self.nvml.nvmlDeviceGetClockInfo(h, self.nvml.NVML_CLOCK_SM))
+                    bits = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(h)
+                    for b, name in self.REASONS.items():
+                        if bits & b:
+                            self.reasons.add(name)
             except Exception:
                 pass
             self._stop.wait(self.period)
 
     def __enter__(self):
-        if self.nvml is not None:
+        if self.nvml is not None and self.handles:
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
         return self
@@ -109,8 +117,8 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
-        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+        return {"sm_mhz": statistics.median(self.samples), "sm_min_mhz": min(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples), "gpus_sampled": len(self.handles)}
 
 
 def cpu_reference_rate(w, kind, budget_s: float, chunk_rows: int = 256, repeats: int = 1):
@@ -421,7 +429,8 @@ def main():
     if not kernels_ok():
         raise SystemExit("bench.py: a kernel reported a timed-out wait during warm-up; no number is reported")
     losses.launch_count = 0
-    with ClockSampler(local_rank) as clocks:
+    # rank 0 samples every GPU of the run (local ranks 0..world-1 of this one node), less often when there are several
+    with ClockSampler(range(world) if rank == 0 else [], 0.004 if world == 1 else 0.015) as clocks:
         ms_per_step, fwd_ms, bwd_ms, median_ms, min_ms = timed(loss_fn, args.steps)
     launches = losses.launch_count
     if not kernels_ok():
