@@ -26,12 +26,10 @@ FLEXSAE_SYMMETRIC_DWEIGHT, FLEXSAE_FUSED_SMALL_REDUCE (0/1: flexsae_b200.distrib
 from __future__ import annotations
 
 import argparse
-import gc
 import json
 import os
 import statistics
 import sys
-import threading
 import time
 
 import torch
@@ -61,64 +59,93 @@ def hbm_peak():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs.
+    """SM clocks and throttle reasons of the run's GPUs while the timed region runs (read-only).
 
-    One sampler per job: rank 0 reads all the GPUs of the run.  (A sampler in every rank -- eight
-    threads querying NVML every 4 ms next to eight launch loops -- delayed the ranks' launches against
-    each other: at 8 GPUs the forward, which ends in a cross-rank sum, measured 0.85 instead of 0.33 ms.)"""
+    The samples come from one `nvidia-smi -lms` child process of rank 0, started before the warm-up
+    steps; the timed region only notes its wall-clock start and end, and the samples whose time stamps
+    fall between them are the ones reported.  (Sampling through NVML from a thread of the benchmark
+    process itself -- one per rank, or rank 0 for all GPUs -- stalled the launch loops: every query
+    cost about 0.2 ms of step time, and at 8 GPUs the forward, which ends in a cross-rank sum,
+    measured 0.85 instead of 0.33 ms.)"""
 
     REASONS = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
                0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
                0x100: "display_clock_setting"}
 
-    def __init__(self, indices, period_s: float = 0.004):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
-        self.period = period_s
-        self.handles = []
+    def __init__(self, indices, period_ms: int = 20):
+        self.proc, self.path, self.t0, self.t1 = None, None, None, None
+        self.n_gpus = len(list(indices))
+        if not self.n_gpus:
+            return
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        ids = []
+        for index in indices:
+            ids.append(visible.split(",")[index] if visible and len(visible.split(",")) > index else str(index))
+        import subprocess
+        import tempfile
         try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nvml = pynvml
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            for index in indices:
-                phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
-                self.handles.append(pynvml.nvmlDeviceGetHandleByIndex(phys))
-            if self.handles:
-                self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handles[0], pynvml.NVML_CLOCK_SM)
+            fd, self.path = tempfile.mkstemp(prefix="flexsae_clocks_", suffix=".csv")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", ",".join(ids),
+                 "--query-gpu=timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.active",
+                 "--format=csv,noheader,nounits", "-lms", str(period_ms)], stdout=fd, stderr=subprocess.DEVNULL)
+            os.close(fd)
+            import atexit
+            atexit.register(self.proc.kill)          # never outlives the benchmark, whatever way it ends
         except Exception:
-            self.nvml = None
-
-    def _run(self):
-        while not self._stop.is_set():
-            try:
-                for h in self.handles:
-                    self.samples.append(self.nvml.nvmlDeviceGetClockInfo(h, self.nvml.NVML_CLOCK_SM))
-                    bits = self.nvml.nvmlDeviceGetCurrentClocksEventReasons(h)
-                    for b, name in self.REASONS.items():
-                        if bits & b:
-                            self.reasons.add(name)
-            except Exception:
-                pass
-            self._stop.wait(self.period)
+            self.proc = None
 
     def __enter__(self):
-        if self.nvml is not None and self.handles:
-            self._thread = threading.Thread(target=self._run, daemon=True)
-            self._thread.start()
+        self.t0 = time.time()
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
+        self.t1 = time.time()
+        if self.proc is not None:            # the legs that follow run without it
+            self.proc.terminate()
 
     def summary(self):
-        if not self.samples:
-            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unavailable"]}
-        return {"sm_mhz": statistics.median(self.samples), "sm_min_mhz": min(self.samples), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples), "gpus_sampled": len(self.handles)}
+        """Reports the samples taken inside the timed region."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        try:
+            with open(self.path) as f:
+                text = f.read()
+            os.remove(self.path)
+        except Exception:
+            text = ""
+        out = self.parse(text, self.t0, self.t1)
+        out["gpus_sampled"] = self.n_gpus
+        return out
+
+    @classmethod
+    def parse(cls, text: str, t0: float, t1: float):
+        """`nvidia-smi --query-gpu=timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.active
+        --format=csv,noheader,nounits` lines -> the summary of those stamped between t0 and t1 (Unix
+        seconds; nvidia-smi stamps a sample when it starts reading it, so samples up to 20 ms outside
+        count when none lies inside, and are reported separately)."""
+        import datetime
+        inside, around, reasons, max_mhz = [], [], set(), None
+        for line in text.splitlines():
+            row = [c.strip() for c in line.split(",")]
+            try:
+                stamp = datetime.datetime.strptime(row[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                mhz, max_mhz, bits = int(row[1]), int(row[2]), int(row[3], 16)
+            except (ValueError, IndexError):
+                continue
+            if t0 - 0.02 <= stamp <= t1 + 0.02:
+                (inside if t0 <= stamp <= t1 else around).append(mhz)
+                reasons.update(name for b, name in cls.REASONS.items() if bits & b)
+        used = inside or around
+        if not used:
+            return {"sm_mhz": None, "sm_max_mhz": max_mhz, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(used), "sm_min_mhz": min(used), "sm_max_mhz": max_mhz, "reasons": sorted(reasons),
+                "samples": len(inside), "samples_within_20ms": len(around),
+                "source": "nvidia-smi -lms child process of rank 0"}
 
 
 def cpu_reference_rate(w, kind, budget_s: float, chunk_rows: int = 256, repeats: int = 1):
@@ -247,6 +274,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     distributed = world > 1
+    # one child process of rank 0 samples the clocks of every GPU of the run (local ranks 0..world-1
+    # of this one node); started here so that its own start-up is long over when the timed region begins
+    clocks = ClockSampler(range(world) if rank == 0 else [], 10 if world == 1 else 20)
     if distributed:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
@@ -331,15 +361,10 @@ def main():
         """n steps between two events; returns (ms per step, per-step (fwd, bwd, whole) ms lists), max over ranks."""
         marks = []
         start, stop = ev(), ev()
-        gc.collect()
-        gc.disable()          # a collection pause on the host can let the launch queue run dry for a step
-        try:
-            start.record()
-            for _ in range(n):
-                step(fn, marks)
-            stop.record()
-        finally:
-            gc.enable()
+        start.record()
+        for _ in range(n):
+            step(fn, marks)
+        stop.record()
         barrier()
         total = start.elapsed_time(stop)
         fwd = [a.elapsed_time(b) for a, b, _ in marks]
@@ -429,8 +454,7 @@ def main():
     if not kernels_ok():
         raise SystemExit("bench.py: a kernel reported a timed-out wait during warm-up; no number is reported")
     losses.launch_count = 0
-    # rank 0 samples every GPU of the run (local ranks 0..world-1 of this one node), less often when there are several
-    with ClockSampler(range(world) if rank == 0 else [], 0.004 if world == 1 else 0.015) as clocks:
+    with clocks:
         ms_per_step, fwd_ms, bwd_ms, median_ms, min_ms = timed(loss_fn, args.steps)
     launches = losses.launch_count
     if not kernels_ok():
