@@ -482,8 +482,9 @@ def main():
     bufs = [{k: torch.empty_like(x[k].detach()) for k in host} for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
-    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(2)]
-    loss_there = [torch.cuda.Event() for _ in range(2)]
+    lag = 8     # the host reads the loss of step i - lag at step i: it may run that far ahead of the GPU
+    loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(lag)]
+    loss_there = [torch.cuda.Event() for _ in range(lag)]
 
     def upload(slot):
         with torch.cuda.stream(copy_stream):
@@ -494,8 +495,9 @@ def main():
 
     def e2e_loop(n):
         """Every step: its inputs come from pinned host memory (uploaded while the previous step
-        computes) and its loss goes back to the host, where it is read one step later so that the
-        host can already enqueue the next step."""
+        computes) and its loss goes back to the host, where it is read `lag` steps later so that the
+        host can already enqueue the next steps (with several ranks a host that is not ahead of its GPU
+        makes every rank wait at the cross-GPU sums)."""
         for c in consumed:
             c.record()
         upload(0)
@@ -510,14 +512,15 @@ def main():
             loss = loss_fn(bufs[slot]["indices"], weight, v, bias, bufs[slot]["target"])
             loss.backward()
             consumed[slot].record()
-            if i >= 2:                                # the buffer about to be overwritten: read it first
-                loss_there[slot].synchronize()
-                seen.append(float(loss_host[slot][0]))
-            loss_host[slot].copy_(loss.detach().reshape(1), non_blocking=True)    # device -> host read of the step's result
-            loss_there[slot].record()
-        for i in range(max(0, n - 2), n):
-            loss_there[i & 1].synchronize()
-            seen.append(float(loss_host[i & 1][0]))
+            ls = i % lag
+            if i >= lag:                              # the buffer about to be overwritten: read it first
+                loss_there[ls].synchronize()
+                seen.append(float(loss_host[ls][0]))
+            loss_host[ls].copy_(loss.detach().reshape(1), non_blocking=True)    # device -> host read of the step's result
+            loss_there[ls].record()
+        for i in range(max(0, n - lag), n):
+            loss_there[i % lag].synchronize()
+            seen.append(float(loss_host[i % lag][0]))
         return seen
 
     e2e_loop(min(5, e2e_steps))
