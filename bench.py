@@ -255,6 +255,7 @@ def main():
     ap.add_argument("--topk-steps", type=int, default=-1,
                     help="steps of the extra TopK leg that gives hier_topk_ratio (0 = skip; default: min(steps, 50))")
     ap.add_argument("--e2e-steps", type=int, default=0, help="0 = same as --steps")
+    ap.add_argument("--e2e-lag", type=int, default=2, help="end-to-end loop: the host reads the loss of step i - lag at step i")
     ap.add_argument("--scaling", default="auto", choices=["auto", "weak", "strong"],
                     help="weak: every rank keeps the workload's B rows; strong: the workload's B rows are split over "
                          "the ranks; auto: strong for c5 (its B is the global batch), weak otherwise")
@@ -482,7 +483,7 @@ def main():
     bufs = [{k: torch.empty_like(x[k].detach()) for k in host} for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
-    lag = 8     # the host reads the loss of step i - lag at step i: it may run that far ahead of the GPU
+    lag = max(1, args.e2e_lag)     # the host reads the loss of step i - lag at step i: it may run that far ahead of the GPU
     loss_host = [torch.zeros(1, dtype=torch.float32).pin_memory() for _ in range(lag)]
     loss_there = [torch.cuda.Event() for _ in range(lag)]
 
