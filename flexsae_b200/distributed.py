@@ -334,7 +334,7 @@ class _ShardedDecoderLoss(torch.autograd.Function):
         _, bwd = ctx.impl
         world = dist.get_world_size(ctx.group)
         fused_peer = (ctx.impl is FUSED_IMPL and config.peer_reduce and 2 <= world <= 8
-                      and _losses.config.dweight_mode == "atomic")
+                      and _losses.config.dweight_mode in ("atomic", "atomic_wide"))   # the sharded kernel has its own piece width
         if fused_peer:
             dweight, dvals, dbias = _fused_backward_with_peer_reduce(ctx.kind, ctx.saved, grad, ctx.bias_dtype,
                                                                      ctx.inv_norm, ctx.group)
